@@ -1,0 +1,323 @@
+"""Host-side mirror of the reference's quantized-decode operators on top of the
+C ABI of ``libkdnn_b200.so`` (include/kdnn_b200.h).
+
+Names, argument meaning and error behaviour follow the reference's C++ operators
+(``KokkosDNN::Gguf::quant_gemv``, ``quant_gemm``, ``quant_moe_decode``,
+``make_quant_weight_table``, ``KokkosDNN::moe_route`` ...), with torch CUDA
+tensors standing in for ``Kokkos::View`` and ``torch.cuda.current_stream()`` for
+the execution-space instance. torch is plumbing only (device memory, streams);
+every computation happens in the library's own CUDA kernels. There is no CPU or
+library fallback: a missing ``libkdnn_b200.so`` raises at import.
+
+The directory name has a hyphen, so import it through ``__graft_entry__.load_package()``
+(which registers it as ``dnn_for_kokkos_b200``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import ggml_pack  # noqa: F401  (re-exported: encoders for synthetic weights)
+from .ggml_pack import Q4_K, Q5_K, Q6_K, Q8_0, row_bytes as ggml_row_bytes  # noqa: F401
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkdnn_b200.so")
+
+KDNN_OK, KDNN_DECLINED = 0, 1
+KDNN_ERR_INVALID, KDNN_ERR_UNSUPPORTED, KDNN_ERR_CUDA, KDNN_ERR_DEVICE_WAIT = -1, -2, -3, -4
+F32, BF16 = 0, 1
+
+# every symbol include/kdnn_b200.h declares (checked by the CPU test-suite)
+EXPORTS = [
+    "kdnn_b200_last_error", "kdnn_b200_device_status", "kdnn_b200_gemv_scratch_bytes",
+    "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quantize_act_q8",
+    "kdnn_b200_unit_dots", "kdnn_b200_gemm_workspace_bytes", "kdnn_b200_quant_gemm",
+    "kdnn_b200_moe_route", "kdnn_b200_moe_workspace_bytes", "kdnn_b200_moe_ffn",
+]
+
+
+class Declined(RuntimeError):
+    """The int8 fast path does not cover this call and launched nothing (the
+    reference would now run its own portable kernel)."""
+
+
+class WeightTableC(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("ggml_type", C.c_uint32), ("rows", C.c_size_t),
+                ("cols", C.c_size_t), ("row_bytes", C.c_size_t), ("n_experts", C.c_size_t)]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python {os.path.join(_HERE, 'build.py')}` "
+            "(there is no CPU or PyTorch fallback)")
+    lib = C.CDLL(LIB_PATH)
+    lib.kdnn_b200_last_error.restype = C.c_char_p
+    lib.kdnn_b200_gemv_scratch_bytes.restype = C.c_size_t
+    lib.kdnn_b200_gemv_scratch_bytes.argtypes = [C.c_size_t]
+    lib.kdnn_b200_gemv_supported.argtypes = [C.c_uint32, C.c_size_t, C.c_int]
+    lib.kdnn_b200_quant_gemv.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
+                                         C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_quantize_act_q8.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t,
+                                              C.c_void_p]
+    lib.kdnn_b200_unit_dots.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
+                                        C.c_void_p, C.c_void_p]
+    lib.kdnn_b200_gemm_workspace_bytes.restype = C.c_size_t
+    lib.kdnn_b200_gemm_workspace_bytes.argtypes = [C.c_size_t, C.c_size_t]
+    lib.kdnn_b200_quant_gemm.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
+                                         C.c_size_t, C.c_size_t, C.c_int, C.c_void_p, C.c_size_t, C.c_int,
+                                         C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_moe_route.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int,
+                                        C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p,
+                                        C.c_void_p, C.c_void_p]
+    lib.kdnn_b200_moe_workspace_bytes.restype = C.c_size_t
+    lib.kdnn_b200_moe_workspace_bytes.argtypes = [C.c_size_t] * 5
+    lib.kdnn_b200_moe_ffn.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_int,
+                                      C.POINTER(WeightTableC), C.POINTER(WeightTableC),
+                                      C.POINTER(WeightTableC), C.c_void_p, C.c_void_p, C.c_size_t,
+                                      C.c_void_p, C.c_size_t, C.c_int, C.c_size_t, C.c_size_t,
+                                      C.c_void_p, C.c_size_t, C.c_void_p]
+    return lib
+
+
+lib = _load()
+
+
+def last_error() -> str:
+    return lib.kdnn_b200_last_error().decode()
+
+
+def device_status() -> int:
+    return int(lib.kdnn_b200_device_status())
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == KDNN_OK:
+        return
+    if rc == KDNN_DECLINED:
+        raise Declined(f"{what}: declined by the int8 fast path")
+    if rc == KDNN_ERR_INVALID:
+        raise ValueError(last_error())          # std::invalid_argument in the reference
+    raise RuntimeError(f"{what}: {last_error()} (status {rc})")
+
+
+def _scalar(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise ValueError(f"Scalar must be float32 or bfloat16, got {t.dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{what} must live on the CUDA device")
+
+
+# ---------------------------------------------------------------------------
+@dataclass
+class QuantWeight:
+    """Packed rows in ggml block order on the device
+    (Gguf::QuantWeight, src/KokkosDNN_GGUF.hpp:851-860)."""
+    data: torch.Tensor   # uint8 [rows * row_bytes]
+    dtype: int           # ggml type id
+    rows: int
+    cols: int
+
+    def row_bytes(self) -> int:
+        return ggml_row_bytes(self.dtype, self.cols)
+
+    def bytes(self) -> int:
+        return self.rows * self.row_bytes()
+
+    @staticmethod
+    def from_numpy(packed, dtype: int, rows: int, cols: int, device="cuda") -> "QuantWeight":
+        t = torch.from_numpy(packed.reshape(-1)).to(device)
+        return QuantWeight(t, dtype, rows, cols)
+
+
+def _quant_check(w: QuantWeight, what: str) -> None:
+    # Impl::quant_check, src/KokkosDNN_GGUF.hpp:1993-2006
+    if w.dtype not in (Q8_0, Q4_K, Q5_K, Q6_K):
+        raise ValueError(f"{what}: unsupported dtype {w.dtype}")
+    want = w.rows * ggml_row_bytes(w.dtype, w.cols)    # raises ValueError on a ragged K
+    if w.data.numel() != want:
+        raise ValueError(f"{what}: payload size {w.data.numel()} != {want}")
+
+
+def quant_gemv_int8_scratch_bytes(K: int) -> int:
+    return int(lib.kdnn_b200_gemv_scratch_bytes(K))
+
+
+def quant_gemv_int8_supported(dtype: int, K: int, scalar: torch.dtype = torch.float32) -> bool:
+    s = F32 if scalar == torch.float32 else BF16 if scalar == torch.bfloat16 else -1
+    return bool(lib.kdnn_b200_gemv_supported(dtype, K, s))
+
+
+def quant_gemv(x: torch.Tensor, w: QuantWeight, y: torch.Tensor, act_scratch: torch.Tensor) -> None:
+    """y[N] = W[N,K] x[K] on the int8 path (Gguf::quant_gemv(handle, x, w, y,
+    act_scratch), src/KokkosDNN_GGUF.hpp:2531-2551). Raises ValueError where the
+    reference throws std::invalid_argument and Declined where its launcher returns
+    false."""
+    if x.numel() != w.cols or y.numel() != w.rows:
+        raise ValueError("quant_gemv: dimension mismatch")
+    _quant_check(w, "quant_gemv")
+    if w.rows == 0 or w.cols == 0:
+        return
+    for t, n in ((x, "x"), (y, "y"), (w.data, "w"), (act_scratch, "act_scratch")):
+        _cuda(t, n)
+    if x.stride(0) != 1 or y.stride(0) != 1:
+        raise Declined("quant_gemv: non-unit stride")
+    rc = lib.kdnn_b200_quant_gemv(w.dtype, w.data.data_ptr(), w.rows, w.cols, x.data_ptr(), _scalar(x),
+                                  y.data_ptr(), _scalar(y), act_scratch.data_ptr(), act_scratch.numel(),
+                                  _stream())
+    _check(rc, "quant_gemv")
+
+
+def quantize_act_q8(x: torch.Tensor, scratch: torch.Tensor) -> None:
+    rc = lib.kdnn_b200_quantize_act_q8(x.data_ptr(), _scalar(x), x.numel(), scratch.data_ptr(),
+                                       scratch.numel(), _stream())
+    _check(rc, "quantize_act_q8")
+
+
+def unit_dots(w: QuantWeight, staged_scratch: torch.Tensor) -> torch.Tensor:
+    out = torch.empty((w.rows, w.cols // 32, 2), dtype=torch.int32, device=w.data.device)
+    rc = lib.kdnn_b200_unit_dots(w.dtype, w.data.data_ptr(), w.rows, w.cols, staged_scratch.data_ptr(),
+                                 out.data_ptr(), _stream())
+    _check(rc, "unit_dots")
+    return out
+
+
+def quant_gemm_workspace_bytes(M: int, K: int) -> int:
+    return int(lib.kdnn_b200_gemm_workspace_bytes(M, K))
+
+
+def quant_gemm(X: torch.Tensor, w: QuantWeight, Y: torch.Tensor, workspace: torch.Tensor) -> None:
+    """Y[M,N] = X[M,K] W[N,K]^T, int8 activations per row
+    (Gguf::quant_gemm, src/KokkosDNN_GGUF.hpp:2564-2593)."""
+    M, K = X.shape
+    if w.cols != K or Y.shape[0] != M or Y.shape[1] != w.rows:
+        raise ValueError("quant_gemm: dimension mismatch")
+    _quant_check(w, "quant_gemm")
+    if X.stride(1) != 1 or Y.stride(1) != 1:
+        raise Declined("quant_gemm: non-unit inner stride")
+    rc = lib.kdnn_b200_quant_gemm(w.dtype, w.data.data_ptr(), w.rows, K, X.data_ptr(), X.stride(0), M,
+                                  _scalar(X), Y.data_ptr(), Y.stride(0), _scalar(Y),
+                                  workspace.data_ptr(), workspace.numel(), _stream())
+    _check(rc, "quant_gemm")
+
+
+def moe_route(logits: torch.Tensor, expert_bias: Optional[torch.Tensor], top_k: int, norm_topk: bool,
+              routed_scale: float, top_idx: torch.Tensor, top_w: torch.Tensor,
+              sigmoid: bool = False) -> None:
+    """KokkosDNN::moe_route / moe_route_sigmoid (src/KokkosDNN_MoE.hpp:240-304)."""
+    T, E = logits.shape
+    K = max(top_k, 0)
+    have_bias = expert_bias is not None and expert_bias.numel() != 0
+    name = "moe_route_sigmoid" if sigmoid else "moe_route"
+    if have_bias and expert_bias.numel() != E:
+        raise ValueError(f"{name}: expert_bias extent must be E")
+    if tuple(top_idx.shape) != (T, K) or tuple(top_w.shape) != (T, K):
+        raise ValueError(f"{name}: output dimension mismatch")
+    if T == 0:
+        return
+    if top_k <= 0 or K > E:
+        raise ValueError(f"{name}: need 1 <= top_k <= E")
+    if have_bias and expert_bias.dtype != logits.dtype:
+        raise ValueError(f"{name}: bias and logits must share one Scalar")
+    rc = lib.kdnn_b200_moe_route(logits.data_ptr(), logits.stride(0), T, E, _scalar(logits),
+                                 expert_bias.data_ptr() if have_bias else None, top_k, int(norm_topk),
+                                 float(routed_scale), int(sigmoid), top_idx.data_ptr(), top_w.data_ptr(),
+                                 _stream())
+    _check(rc, name)
+
+
+@dataclass
+class QuantWeightTable:
+    """Device array of per-expert payload pointers plus the shared shape
+    (Gguf::QuantWeightTable, src/KokkosDNN_GGUF.hpp:2020-2029)."""
+    base: torch.Tensor   # int64 [n_experts] device addresses
+    dtype: int
+    rows: int
+    cols: int
+    row_bytes: int
+    keepalive: Sequence[QuantWeight] = ()
+
+    def size(self) -> int:
+        return int(self.base.numel())
+
+    def c_struct(self) -> WeightTableC:
+        return WeightTableC(self.base.data_ptr(), self.dtype, self.rows, self.cols, self.row_bytes,
+                            self.size())
+
+
+def make_quant_weight_table(ws: List[QuantWeight], what: str = "table") -> QuantWeightTable:
+    """Gguf::make_quant_weight_table (src/KokkosDNN_GGUF.hpp:2031-2053)."""
+    if not ws:
+        return QuantWeightTable(torch.empty(0, dtype=torch.int64), 0, 0, 0, 0)
+    w0 = ws[0]
+    for w in ws:
+        if w.dtype != w0.dtype or w.rows != w0.rows or w.cols != w0.cols:
+            raise ValueError(f"{what}: entries must share dtype and shape")
+        _quant_check(w, what)
+    base = torch.tensor([w.data.data_ptr() for w in ws], dtype=torch.int64, device=w0.data.device)
+    return QuantWeightTable(base, w0.dtype, w0.rows, w0.cols, w0.row_bytes(), tuple(ws))
+
+
+def moe_ffn_workspace_bytes(T: int, S: int, H: int, F: int, n_experts: int) -> int:
+    return int(lib.kdnn_b200_moe_workspace_bytes(T, S, H, F, n_experts))
+
+
+def moe_ffn(X: torch.Tensor, gate: QuantWeightTable, up: QuantWeightTable, down: QuantWeightTable,
+            idx: torch.Tensor, wts: torch.Tensor, Y: torch.Tensor, workspace: torch.Tensor,
+            expert_first: int = 0, expert_count: Optional[int] = None) -> None:
+    """Batched expert feed-forward with int8 activations (see kdnn_b200_moe_ffn)."""
+    T, H = X.shape
+    S = idx.shape[1] if idx.dim() == 2 and idx.shape[0] else 0
+    if tuple(Y.shape) != (T, H):
+        raise ValueError("moe_ffn: dimension mismatch")
+    if idx.shape[0] != T or tuple(wts.shape) != tuple(idx.shape):
+        raise ValueError("moe_ffn: routing dimension mismatch")
+    if idx.dtype != torch.int32 or wts.dtype != torch.float32:
+        raise ValueError("moe_ffn: idx must be int32 and wts float32")
+    if X.stride(1) != 1 or Y.stride(1) != 1 or not idx.is_contiguous() or not wts.is_contiguous():
+        raise ValueError("moe_ffn: rows must be contiguous")
+    g, u, d = gate.c_struct(), up.c_struct(), down.c_struct()
+    n = gate.size() if expert_count is None else expert_count
+    rc = lib.kdnn_b200_moe_ffn(X.data_ptr(), X.stride(0), T, _scalar(X), C.byref(g), C.byref(u),
+                               C.byref(d), idx.data_ptr(), wts.data_ptr(), S, Y.data_ptr(), Y.stride(0),
+                               _scalar(Y), expert_first, n, workspace.data_ptr(), workspace.numel(),
+                               _stream())
+    _check(rc, "moe_ffn")
+
+
+def quant_moe_decode(X: torch.Tensor, gate: QuantWeightTable, up: QuantWeightTable,
+                     down: QuantWeightTable, idx: torch.Tensor, wts: torch.Tensor, act: torch.Tensor,
+                     Y: torch.Tensor, workspace: torch.Tensor) -> None:
+    """One decoded token (Gguf::quant_moe_decode, src/KokkosDNN_GGUF.hpp:2335-2391):
+    same argument checks and messages; `act` is accepted for signature parity (the
+    kernels keep the activations in `workspace`)."""
+    if X.shape[0] != 1 or Y.shape[0] != 1:
+        raise ValueError("quant_moe_decode: expected one row")
+    K, MI = X.shape[1], gate.rows
+    S = 0 if idx.shape[0] == 0 else idx.shape[1]
+    if gate.cols != K or up.cols != K or up.rows != MI or down.rows != K or down.cols != MI \
+            or Y.shape[1] != K:
+        raise ValueError("quant_moe_decode: dimension mismatch")
+    if gate.size() == 0 or gate.size() != up.size() or gate.size() != down.size():
+        raise ValueError("quant_moe_decode: expert table mismatch")
+    if idx.shape[0] != 1 or wts.shape[0] != 1 or wts.shape[1] != S:
+        raise ValueError("quant_moe_decode: routing dimension mismatch")
+    if act.shape[0] < S or (S > 0 and act.shape[1] != MI):
+        raise ValueError("quant_moe_decode: act scratch too small")
+    if S == 0 or K == 0 or MI == 0:
+        return
+    moe_ffn(X, gate, up, down, idx, wts, Y, workspace)

@@ -1,0 +1,205 @@
+// extern "C" entry points of libkdnn_b200.so (declared in include/kdnn_b200.h):
+// argument validation with the reference's decline / throw split, then the
+// kernel launchers of kdnn_gemv.cu, kdnn_gemm.cu and kdnn_moe.cu.
+#include "kdnn_common.cuh"
+
+#include <limits.h>
+#include <stdio.h>
+#include <string>
+
+namespace kdnn {
+cudaError_t gemv_launch(uint32_t dt, const void* w, size_t rows, size_t cols, const void* x, int xs,
+                        void* y, int ys, void* scratch, int force_generic, cudaStream_t stream);
+cudaError_t quantize_act_launch(const void* x, int xs, size_t K, void* scratch, cudaStream_t st);
+cudaError_t unit_dots_launch(uint32_t dt, const void* w, size_t rows, size_t cols,
+                             const void* scratch, int32_t* out, cudaStream_t st);
+int gemv_take_status();
+
+size_t gemm_workspace_bytes(size_t M, size_t K);
+cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const void* X, size_t ldx,
+                        size_t M, int xs, void* Y, size_t ldy, int ys, void* ws, cudaStream_t st);
+
+cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, int scalar,
+                             const void* bias, int top_k, int norm_topk, float routed_scale,
+                             int sigmoid, int32_t* top_idx, float* top_w, cudaStream_t st);
+size_t moe_workspace_bytes(size_t T, size_t S, size_t H, size_t F, size_t n_experts);
+cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
+                           const kdnn_b200_weight_table* gate, const kdnn_b200_weight_table* up,
+                           const kdnn_b200_weight_table* down, const int32_t* idx, const float* wts,
+                           size_t S, void* Y, size_t ldy, int ys, size_t e_first, size_t e_count,
+                           void* ws, cudaStream_t st);
+int moe_take_status();
+}  // namespace kdnn
+
+namespace {
+thread_local std::string g_last_error;
+
+int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+int cuda_result(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return KDNN_OK;
+  return fail(KDNN_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+bool scalar_ok(int s) { return s == KDNN_F32 || s == KDNN_BF16; }
+bool int8_type(uint32_t t) {
+  return t == KDNN_GGML_Q4_K || t == KDNN_GGML_Q6_K || t == KDNN_GGML_Q8_0;
+}
+// KDNN_FORCE_GENERIC=1 routes every GEMV through the plain-load kernels (debug aid).
+int force_generic() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("KDNN_FORCE_GENERIC");
+    v             = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v;
+}
+}  // namespace
+
+extern "C" {
+
+const char* kdnn_b200_last_error(void) { return g_last_error.c_str(); }
+
+int kdnn_b200_device_status(void) {
+  const int a = kdnn::gemv_take_status();
+  const int b = kdnn::moe_take_status();
+  return a != 0 ? a : b;
+}
+
+size_t kdnn_b200_gemv_scratch_bytes(size_t K) { return kdnn::act_bytes(K); }
+
+int kdnn_b200_gemv_supported(uint32_t ggml_type, size_t K, int scalar) {
+  return scalar_ok(scalar) && int8_type(ggml_type) && kdnn::act_bytes(K) != 0 &&
+         kdnn::block_aligned(ggml_type, K);
+}
+
+int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                         const void* x, int x_scalar, void* y, int y_scalar, void* act_scratch,
+                         size_t act_scratch_bytes, void* stream) {
+  if (!scalar_ok(x_scalar) || !scalar_ok(y_scalar))
+    return fail(KDNN_ERR_INVALID, "quant_gemv: scalar must be KDNN_F32 or KDNN_BF16");
+  // the reference launcher's decline list, src/KokkosDNN_GGUFGemvInt8.hpp:724-745
+  if (!int8_type(ggml_type)) return KDNN_DECLINED;
+  if (w == nullptr || act_scratch == nullptr || x == nullptr || y == nullptr) return KDNN_DECLINED;
+  if (!kdnn::block_aligned(ggml_type, cols)) return KDNN_DECLINED;
+  if (rows == 0 || rows > static_cast<size_t>(INT_MAX)) return KDNN_DECLINED;
+  if (cols > static_cast<size_t>(INT_MAX)) return KDNN_DECLINED;
+  if (act_scratch_bytes < kdnn::act_bytes(cols)) return KDNN_DECLINED;
+  if ((reinterpret_cast<uintptr_t>(act_scratch) & 15u) != 0u) return KDNN_DECLINED;
+  if ((reinterpret_cast<uintptr_t>(w) & 1u) != 0u) return KDNN_DECLINED;
+  if (ggml_type == KDNN_GGML_Q4_K && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u)
+    return KDNN_DECLINED;
+  return cuda_result(kdnn::gemv_launch(ggml_type, w, rows, cols, x, x_scalar, y, y_scalar,
+                                       act_scratch, force_generic(),
+                                       static_cast<cudaStream_t>(stream)),
+                     "quant_gemv");
+}
+
+int kdnn_b200_quantize_act_q8(const void* x, int x_scalar, size_t K, void* scratch,
+                              size_t scratch_bytes, void* stream) {
+  if (!scalar_ok(x_scalar)) return fail(KDNN_ERR_INVALID, "quantize_act_q8: bad scalar");
+  if (K == 0 || K % 32 != 0 || K > static_cast<size_t>(INT_MAX)) return KDNN_DECLINED;
+  if (x == nullptr || scratch == nullptr || scratch_bytes < kdnn::act_bytes(K) ||
+      (reinterpret_cast<uintptr_t>(scratch) & 15u) != 0u)
+    return KDNN_DECLINED;
+  return cuda_result(
+      kdnn::quantize_act_launch(x, x_scalar, K, scratch, static_cast<cudaStream_t>(stream)),
+      "quantize_act_q8");
+}
+
+int kdnn_b200_unit_dots(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                        const void* staged_scratch, int32_t* out, void* stream) {
+  if (!int8_type(ggml_type) || !kdnn::block_aligned(ggml_type, cols))
+    return fail(KDNN_ERR_INVALID, "unit_dots: unsupported dtype or K not block aligned");
+  if (!w || !staged_scratch || !out || rows == 0 || rows > INT_MAX || cols > INT_MAX)
+    return fail(KDNN_ERR_INVALID, "unit_dots: bad argument");
+  if ((reinterpret_cast<uintptr_t>(staged_scratch) & 15u) || (reinterpret_cast<uintptr_t>(w) & 1u))
+    return fail(KDNN_ERR_INVALID, "unit_dots: misaligned buffer");
+  return cuda_result(kdnn::unit_dots_launch(ggml_type, w, rows, cols, staged_scratch, out,
+                                            static_cast<cudaStream_t>(stream)),
+                     "unit_dots");
+}
+
+size_t kdnn_b200_gemm_workspace_bytes(size_t M, size_t K) {
+  return kdnn::gemm_workspace_bytes(M, K);
+}
+
+int kdnn_b200_quant_gemm(uint32_t ggml_type, const void* w, size_t N, size_t K, const void* X,
+                         size_t ldx, size_t M, int x_scalar, void* Y, size_t ldy, int y_scalar,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+  if (!scalar_ok(x_scalar) || !scalar_ok(y_scalar))
+    return fail(KDNN_ERR_INVALID, "quant_gemm: scalar must be KDNN_F32 or KDNN_BF16");
+  if (M == 0 || N == 0 || K == 0) return KDNN_OK;  // src/KokkosDNN_GGUF.hpp:2576
+  if (ldx < K || ldy < N) return fail(KDNN_ERR_INVALID, "quant_gemm: dimension mismatch");
+  if (M * N > static_cast<size_t>(INT_MAX)) return fail(KDNN_ERR_INVALID, "quant_gemm: M*N too large");
+  if (!int8_type(ggml_type) || !kdnn::block_aligned(ggml_type, K)) return KDNN_DECLINED;
+  if (!w || !X || !Y || !workspace) return KDNN_DECLINED;
+  if (workspace_bytes < kdnn::gemm_workspace_bytes(M, K)) return KDNN_DECLINED;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15u) || (reinterpret_cast<uintptr_t>(w) & 1u))
+    return KDNN_DECLINED;
+  return cuda_result(kdnn::gemm_launch(ggml_type, w, N, K, X, ldx, M, x_scalar, Y, ldy, y_scalar,
+                                       workspace, static_cast<cudaStream_t>(stream)),
+                     "quant_gemm");
+}
+
+int kdnn_b200_moe_route(const void* logits, size_t ld, size_t T, size_t E, int scalar,
+                        const void* bias, int top_k, int norm_topk, float routed_scale,
+                        int sigmoid, int32_t* top_idx, float* top_w, void* stream) {
+  if (!scalar_ok(scalar)) return fail(KDNN_ERR_INVALID, "moe_route: bad scalar");
+  if (T == 0) return KDNN_OK;  // src/KokkosDNN_MoE.hpp:256
+  if (top_k <= 0 || static_cast<size_t>(top_k) > E)
+    return fail(KDNN_ERR_INVALID, "moe_route: need 1 <= top_k <= E");  // :257-258
+  if (!logits || !top_idx || !top_w || ld < E || T > INT_MAX || E > INT_MAX)
+    return fail(KDNN_ERR_INVALID, "moe_route: bad argument");
+  return cuda_result(kdnn::moe_route_launch(logits, ld, T, E, scalar, bias, top_k, norm_topk,
+                                            routed_scale, sigmoid, top_idx, top_w,
+                                            static_cast<cudaStream_t>(stream)),
+                     "moe_route");
+}
+
+size_t kdnn_b200_moe_workspace_bytes(size_t T, size_t S, size_t H, size_t F, size_t n_experts) {
+  return kdnn::moe_workspace_bytes(T, S, H, F, n_experts);
+}
+
+int kdnn_b200_moe_ffn(const void* X, size_t ldx, size_t T, int x_scalar,
+                      const kdnn_b200_weight_table* gate, const kdnn_b200_weight_table* up,
+                      const kdnn_b200_weight_table* down, const int32_t* idx, const float* wts,
+                      size_t S, void* Y, size_t ldy, int y_scalar, size_t expert_first,
+                      size_t expert_count, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!scalar_ok(x_scalar) || !scalar_ok(y_scalar))
+    return fail(KDNN_ERR_INVALID, "moe_ffn: scalar must be KDNN_F32 or KDNN_BF16");
+  if (!gate || !up || !down) return fail(KDNN_ERR_INVALID, "moe_ffn: null weight table");
+  const size_t H = gate->cols, F = gate->rows;
+  // src/KokkosDNN_GGUF.hpp:2352-2357
+  if (up->cols != H || up->rows != F || down->rows != H || down->cols != F)
+    return fail(KDNN_ERR_INVALID, "moe_ffn: dimension mismatch");
+  if (gate->n_experts == 0 || gate->n_experts != up->n_experts || gate->n_experts != down->n_experts)
+    return fail(KDNN_ERR_INVALID, "moe_ffn: expert table mismatch");
+  if (T == 0 || S == 0 || H == 0 || F == 0) return KDNN_OK;  // :2362
+  if (ldx < H || ldy < H) return fail(KDNN_ERR_INVALID, "moe_ffn: dimension mismatch");
+  if (!int8_type(gate->ggml_type) || !int8_type(up->ggml_type) || !int8_type(down->ggml_type))
+    return KDNN_DECLINED;
+  // :2369-2381
+  if (H % 256 != 0 || F % 256 != 0)
+    return fail(KDNN_ERR_INVALID, "moe_ffn: K-quant rows must be a multiple of 256 elements");
+  if (gate->row_bytes != kdnn::row_bytes_of(gate->ggml_type, H) ||
+      up->row_bytes != kdnn::row_bytes_of(up->ggml_type, H) ||
+      down->row_bytes != kdnn::row_bytes_of(down->ggml_type, F))
+    return fail(KDNN_ERR_INVALID, "moe_ffn: bad packed row");
+  if (!X || !Y || !idx || !wts || !workspace || !gate->base || !up->base || !down->base)
+    return fail(KDNN_ERR_INVALID, "moe_ffn: null argument");
+  if (expert_first + expert_count > gate->n_experts)
+    return fail(KDNN_ERR_INVALID, "moe_ffn: expert range outside the table");
+  if (workspace_bytes < kdnn::moe_workspace_bytes(T, S, H, F, gate->n_experts) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return fail(KDNN_ERR_INVALID, "moe_ffn: workspace too small or not 256-byte aligned");
+  if (T * S > static_cast<size_t>(INT_MAX) / 4)
+    return fail(KDNN_ERR_INVALID, "moe_ffn: T*S too large");
+  return cuda_result(kdnn::moe_ffn_launch(X, ldx, T, x_scalar, gate, up, down, idx, wts, S, Y, ldy,
+                                          y_scalar, expert_first, expert_count, workspace,
+                                          static_cast<cudaStream_t>(stream)),
+                     "moe_ffn");
+}
+
+}  // extern "C"

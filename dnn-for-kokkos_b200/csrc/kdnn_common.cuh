@@ -1,0 +1,200 @@
+// Shared device helpers for the sm_100a quantized-decode kernels: ggml block
+// geometry, the per-32 int8 activation quantizer, and the mbarrier / bulk-copy
+// (TMA 1-D) wrappers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/kdnn_b200.h"
+
+namespace kdnn {
+
+// ---- ggml block geometry --------------------------------------------------
+// "Item" = 64 consecutive-in-the-format weight elements, the work one lane does
+// per row: Q4_K one 32-byte nibble group (low nibbles = sub-block 2i, high
+// nibbles = sub-block 2i+1), Q6_K one (128-chunk, half) slice (two ql windows
+// sharing one qh window), Q8_0 two 34-byte blocks.
+template <uint32_t DT>
+struct Fmt;
+template <>
+struct Fmt<KDNN_GGML_Q4_K> {
+  static constexpr int kBlockElems = 256, kBlockBytes = 144;
+};
+template <>
+struct Fmt<KDNN_GGML_Q6_K> {
+  static constexpr int kBlockElems = 256, kBlockBytes = 210;
+};
+template <>
+struct Fmt<KDNN_GGML_Q8_0> {
+  static constexpr int kBlockElems = 32, kBlockBytes = 34;
+};
+
+__host__ __device__ inline size_t row_bytes_of(uint32_t dt, size_t cols) {
+  switch (dt) {
+    case KDNN_GGML_Q8_0: return cols / 32 * 34;
+    case KDNN_GGML_Q4_K: return cols / 256 * 144;
+    case KDNN_GGML_Q5_K: return cols / 256 * 176;
+    case KDNN_GGML_Q6_K: return cols / 256 * 210;
+  }
+  return 0;
+}
+__host__ __device__ inline bool block_aligned(uint32_t dt, size_t cols) {
+  if (cols == 0 || cols % 32 != 0) return false;
+  return dt == KDNN_GGML_Q8_0 ? true : cols % 256 == 0;
+}
+
+// Activation staging layout of the reference (int8 row, then 16-byte headers).
+struct ActHdr {
+  float d;
+  int32_t sum_lo, sum_hi, pad;
+};
+__host__ __device__ inline size_t act_hdr_offset(size_t K) { return (K + 15) & ~size_t(15); }
+__host__ __device__ inline size_t act_bytes(size_t K) {
+  return K % 32 ? 0 : act_hdr_offset(K) + 16 * (K / 32);
+}
+
+// ---- scalar helpers ---------------------------------------------------------
+__device__ __forceinline__ float h2f(uint32_t bits16) {
+  // cvt.f32.f16 is exact for every fp16 value (subnormals, inf, nan payloads).
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
+}
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void store_scalar(float* p, float v) { *p = v; }
+__device__ __forceinline__ void store_scalar(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// dp4a over one 16-byte window (four words each side).
+__device__ __forceinline__ int dot16(const uint32_t (&w)[4], const int4& x, int acc) {
+  acc = __dp4a(static_cast<int>(w[0]), x.x, acc);
+  acc = __dp4a(static_cast<int>(w[1]), x.y, acc);
+  acc = __dp4a(static_cast<int>(w[2]), x.z, acc);
+  acc = __dp4a(static_cast<int>(w[3]), x.w, acc);
+  return acc;
+}
+
+// ---- per-32 int8 activation quantizer ---------------------------------------
+// Eight lanes cooperate on one 32-element block (four elements each). Returns
+// this lane's four quantized values packed into one word; d / part sums come
+// back through references. All 32 lanes of the warp must call it together.
+//   d = amax / 127 and inv = 127 / amax are IEEE divisions, q = rint(v * inv)
+//   clamped to +-127: the same roundings as the reference's stage 1.
+__device__ __forceinline__ uint32_t quantize_block_lane(const float (&v)[4], float& d,
+                                                        int& part_sum, int& block_sum) {
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  d                = __fdiv_rn(amax, 127.0f);
+  const float inv  = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+  uint32_t packed  = 0;
+  int s            = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int q = __float2int_rn(__fmul_rn(v[i], inv));
+    q     = max(-127, min(127, q));
+    s += q;
+    packed |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * i);
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  part_sum  = s;  // lanes 0-3 of the group: elements 0..15, lanes 4-7: 16..31
+  block_sum = s + __shfl_xor_sync(0xffffffffu, s, 4);
+  return packed;
+}
+
+template <class XT>
+__device__ __forceinline__ void load4(const XT* x, size_t k, bool vec_ok, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* x, size_t k, bool vec_ok, float (&v)[4]) {
+  if (vec_ok) {
+    const float4 t = *reinterpret_cast<const float4*>(x + k);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = x[k + i];
+  }
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* x, size_t k, bool vec_ok,
+                                                     float (&v)[4]) {
+  if (vec_ok) {
+    const uint2 t = *reinterpret_cast<const uint2*>(x + k);
+    v[0] = __uint_as_float(t.x << 16);
+    v[1] = __uint_as_float(t.x & 0xFFFF0000u);
+    v[2] = __uint_as_float(t.y << 16);
+    v[3] = __uint_as_float(t.y & 0xFFFF0000u);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __bfloat162float(x[k + i]);
+  }
+}
+
+// ---- mbarrier + bulk copy (TMA 1-D, no multicast) ----------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after `limit` probes (each probe itself blocks for a
+// hardware-defined slice), so a copy that never lands cannot hang the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
+                                                  uint32_t limit = (1u << 22)) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// global -> shared bulk copy completing on an mbarrier. Both addresses 16-byte
+// aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// Programmatic dependent launch: let the next kernel in the stream start its
+// prologue / wait for the previous kernel's memory before touching its outputs.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+}  // namespace kdnn

@@ -1,0 +1,163 @@
+/* C ABI of the B200 (sm_100a) quantized-decode library: GGUF block-quantized
+ * GEMV / batched GEMM with per-32 int8 activations, MoE routing and the packed
+ * expert feed-forward.
+ *
+ * This is the boundary a binding of the reference library
+ * (cwpearson/dnn-for-kokkos) would call from inside its own operator templates;
+ * each entry point names the reference operator it stands in for (paths are
+ * relative to the reference project root). include/KokkosDNN_B200.hpp holds the
+ * C++ layer that keeps the reference's Kokkos::View signatures on top of it.
+ *
+ * Conventions
+ *   - every pointer is a device pointer valid on the current CUDA device unless
+ *     a parameter comment says "host";
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream, which is what Kokkos::Cuda().cuda_stream() callers pass);
+ *   - calls are asynchronous: they enqueue kernels on `stream` and return;
+ *   - nothing here allocates device memory; scratch and workspaces are
+ *     caller-owned, sized by the *_bytes queries;
+ *   - return value: KDNN_OK (0) launched; KDNN_DECLINED (1) the fast path does
+ *     not cover this call and NOTHING was launched (the reference convention of
+ *     src/KokkosDNN_GGUFGemvInt8.hpp:708-710: the caller runs its own portable
+ *     path); negative = error, nothing launched, kdnn_b200_last_error() has text.
+ *   - weight payloads are ggml blocks, unchanged: Q8_0 (34 B / 32), Q4_K
+ *     (144 B / 256), Q6_K (210 B / 256), rows contiguous with stride
+ *     row_bytes = cols / block_len * block_bytes.
+ */
+#ifndef KDNN_B200_H
+#define KDNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  KDNN_OK              = 0,
+  KDNN_DECLINED        = 1,
+  KDNN_ERR_INVALID     = -1, /* maps to std::invalid_argument in the C++ layer */
+  KDNN_ERR_UNSUPPORTED = -2,
+  KDNN_ERR_CUDA        = -3,
+  KDNN_ERR_DEVICE_WAIT = -4  /* a bounded device-side wait gave up */
+};
+
+/* ggml type ids (src/KokkosDNN_GGUF.hpp:68-87). */
+enum { KDNN_GGML_Q8_0 = 8, KDNN_GGML_Q4_K = 12, KDNN_GGML_Q5_K = 13, KDNN_GGML_Q6_K = 14 };
+
+/* Scalar of activations / outputs (src/KokkosDNN_Types.hpp:16-18). */
+enum { KDNN_F32 = 0, KDNN_BF16 = 1 };
+
+/* Text of the last error on this host thread ("" if none). */
+const char* kdnn_b200_last_error(void);
+
+/* Reads and clears the device-side status word (0 = no bounded wait gave up).
+ * Synchronizes the device. */
+int kdnn_b200_device_status(void);
+
+/* ---- GEMV -------------------------------------------------------------- */
+
+/* Bytes of activation staging for a K-element row; 0 when K % 32 != 0.
+ * Stands in for Gguf::quant_gemv_int8_scratch_bytes, src/KokkosDNN_GGUF.hpp:2496-2499.
+ * Layout written: int8 xq[K], then at align16(K) one {float d; int32 sum_lo;
+ * int32 sum_hi; int32 pad} per 32 elements (src/KokkosDNN_GGUFGemvInt8.hpp:108-129). */
+size_t kdnn_b200_gemv_scratch_bytes(size_t K);
+
+/* 1 when kdnn_b200_quant_gemv takes the int8 path for this weight type, K and
+ * Scalar. Stands in for Gguf::quant_gemv_int8_supported, src/KokkosDNN_GGUF.hpp:2522-2529. */
+int kdnn_b200_gemv_supported(uint32_t ggml_type, size_t K, int scalar);
+
+/* y[rows] = W[rows, cols] . x[cols], int8 path: x is quantized per 32 elements
+ * (d = amax/127, q = rint(x * (127/amax)) clamped to +-127, half sums) inside
+ * the kernel's prologue, the integer dots run on dp4a, rescale in fp32.
+ * Stands in for Gguf::quant_gemv(handle, x, w, y, act_scratch),
+ * src/KokkosDNN_GGUF.hpp:2531-2551 -> Impl::GgufMvq::launch_quant_gemv_int8,
+ * src/KokkosDNN_GGUFGemvInt8.hpp:711-777 (both of its launches in one kernel).
+ * The staging bytes are also written to act_scratch, as the reference leaves them.
+ *   x_scalar / y_scalar: KDNN_F32 or KDNN_BF16 (the reference uses one Scalar for
+ *     both; y_scalar = KDNN_F32 with bf16 x gives the row sums before the cast).
+ * Declines (returns KDNN_DECLINED) exactly where the reference's launcher does:
+ * null w or scratch, K not block aligned, rows == 0 or > INT_MAX, scratch too
+ * small or not 16-byte aligned, odd w, Q4_K w not 16-byte aligned. */
+int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                         const void* x, int x_scalar, void* y, int y_scalar,
+                         void* act_scratch, size_t act_scratch_bytes, void* stream);
+
+/* Stage 1 alone: quantize one activation row into `scratch` (layout above).
+ * Stands in for Impl::GgufMvq::QuantizeActQ8Functor, src/KokkosDNN_GGUFGemvInt8.hpp:198-239. */
+int kdnn_b200_quantize_act_q8(const void* x, int x_scalar, size_t K, void* scratch,
+                              size_t scratch_bytes, void* stream);
+
+/* Parity probe: the integer dots of every decode unit (32 weights of one row)
+ * against an already staged activation row, exactly the integers the reference
+ * multiplies by its fp32 scales in Impl::GgufMvq::gemv_int8_unit_dot_win,
+ * src/KokkosDNN_GGUFGemvInt8.hpp:359-466:
+ *   Q4_K: {dotA, dotB}   Q6_K: {dotA - 32*sum0, dotB - 32*sum1}   Q8_0: {dot, 0}
+ * out: int32[rows * (cols/32) * 2]. */
+int kdnn_b200_unit_dots(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                        const void* staged_scratch, int32_t* out, void* stream);
+
+/* ---- batched GEMV / skinny GEMM ------------------------------------------ */
+
+/* Workspace bytes for kdnn_b200_quant_gemm with M activation rows of K elements. */
+size_t kdnn_b200_gemm_workspace_bytes(size_t M, size_t K);
+
+/* Y[M, N] = X[M, K] . W[N, K]^T with packed W, every activation row quantized per
+ * 32 elements as in the GEMV, so row m of Y equals kdnn_b200_quant_gemv on row m.
+ * Stands in for Gguf::quant_gemm, src/KokkosDNN_GGUF.hpp:2564-2593 (which is the
+ * fp path; the int8 numerics follow src/KokkosDNN_GGUFGemvInt8.hpp per row).
+ *   ldx, ldy: row pitches in elements. */
+int kdnn_b200_quant_gemm(uint32_t ggml_type, const void* w, size_t N, size_t K,
+                         const void* X, size_t ldx, size_t M, int x_scalar,
+                         void* Y, size_t ldy, int y_scalar,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- MoE ------------------------------------------------------------------ */
+
+/* Per-token top-k expert selection and combination weights.
+ * Stands in for KokkosDNN::moe_route (sigmoid = 0), src/KokkosDNN_MoE.hpp:240-263,
+ * and KokkosDNN::moe_route_sigmoid (sigmoid = 1), :280-304. Greedy selection with
+ * strict '>' (ties keep the lower expert id); weights recomputed from the logits
+ * at the selected ids (:84-147).
+ *   logits [T, E] Scalar, row pitch ld (elements); bias [E] Scalar or NULL;
+ *   top_idx [T, top_k] int32; top_w [T, top_k] float. */
+int kdnn_b200_moe_route(const void* logits, size_t ld, size_t T, size_t E, int scalar,
+                        const void* bias, int top_k, int norm_topk, float routed_scale,
+                        int sigmoid, int32_t* top_idx, float* top_w, void* stream);
+
+/* One packed expert matrix kind (gate, up or down): device array of n_experts
+ * payload pointers plus the shape every entry shares.
+ * Mirrors Gguf::QuantWeightTable, src/KokkosDNN_GGUF.hpp:2020-2029. */
+typedef struct {
+  const uintptr_t* base; /* device array [n_experts] of payload addresses */
+  uint32_t ggml_type;
+  size_t rows, cols, row_bytes;
+  size_t n_experts;
+} kdnn_b200_weight_table;
+
+/* Workspace bytes for kdnn_b200_moe_ffn with T tokens, S slots per token. */
+size_t kdnn_b200_moe_workspace_bytes(size_t T, size_t S, size_t H, size_t F, size_t n_experts);
+
+/* Expert feed-forward for T tokens with int8 activations:
+ *   per (token t, slot s), e = idx[t,s] (slots with e outside [0, n_experts) or
+ *   w == 0 contribute nothing): act = Scalar(silu(gate_e x_t) * (up_e x_t)),
+ *   Y[t,:] = Scalar(sum_s w[t,s] * (down_e act)), slots ascending, fp32.
+ * T == 1 stands in for Gguf::quant_moe_decode, src/KokkosDNN_GGUF.hpp:2335-2391;
+ * T > 1 for the per-expert gather / dequant / gemm / swiglu / gemm / scatter loop
+ * of LFM2.5's moe_forward_sparse, models/lfm2_5/KokkosDNN_LFM25Model.hpp:441-547.
+ *   X [T, H] Scalar pitch ldx; idx [T, S] int32; wts [T, S] float;
+ *   Y [T, H] y_scalar pitch ldy (assigned, not accumulated);
+ *   expert_first / expert_count: only experts in [first, first+count) are
+ *   computed here (expert-parallel shard); pass 0, n_experts for all. */
+int kdnn_b200_moe_ffn(const void* X, size_t ldx, size_t T, int x_scalar,
+                      const kdnn_b200_weight_table* gate, const kdnn_b200_weight_table* up,
+                      const kdnn_b200_weight_table* down, const int32_t* idx, const float* wts,
+                      size_t S, void* Y, size_t ldy, int y_scalar,
+                      size_t expert_first, size_t expert_count,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KDNN_B200_H */

@@ -1,0 +1,183 @@
+"""Parity of the CUDA int8 GEMV (through the C ABI) against the CPU checker.
+
+Bars: activation staging bytes and per-unit integer dots bit-exact; fp32 row sums
+within 1e-3 of max|y| (the north-star tolerance; the reference's own int8 tests use
+1e-3 absolute on crafted data and 1e-4*sum|terms|+1e-3 on random payloads,
+tests/Test_GGUF.cpp:923, :1021 -- both are asserted where they apply); bf16
+outputs within one bf16 ulp of the rounded checker value.
+Shapes follow tests/Test_GGUF.cpp:1118-1201.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+DTYPES = [O.Q4_K, O.Q6_K, O.Q8_0]
+
+
+def _run(kd, dtype, packed, rows, K, x_t, y_dtype):
+    dev = torch.device("cuda:0")
+    w = kd.QuantWeight.from_numpy(packed, dtype, rows, K, dev)
+    y = torch.full((rows,), float("nan"), dtype=y_dtype, device=dev)
+    scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+    kd.quant_gemv(x_t.to(dev), w, y, scratch)
+    torch.cuda.synchronize()
+    assert kd.device_status() == 0
+    return w, y, scratch
+
+
+def _check(kd, port, dtype, rows, K, seed, payload, x_dtype=torch.float32, y_dtype=torch.float32,
+           probe=True):
+    if payload == "random":
+        packed = kd.ggml_pack.random_payload(dtype, rows, K, seed)
+    else:
+        packed = kd.ggml_pack.synth_weight(dtype, rows, K, seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    x_t = torch.randn(K, generator=g).to(x_dtype)
+    w, y, scratch = _run(kd, dtype, packed, rows, K, x_t, y_dtype)
+    host = O.aligned_copy(packed)
+    xf = x_t.float().numpy()
+    y_ref, staging = port.gemv_int8(dtype, host, rows, K, xf)
+    # 1. staging bytes (int8 row + {d, sum_lo, sum_hi, pad} headers): bit-exact
+    assert np.array_equal(scratch.cpu().numpy(), staging)
+    # 2. integer dots of every unit: bit-exact
+    if probe:
+        ints_ref, _ = port.unit_table(dtype, host, rows, K, staging)
+        ints = kd.unit_dots(w, scratch).cpu().numpy()
+        assert np.array_equal(ints, ints_ref)
+    # 3. row sums
+    got = y.float().cpu().numpy()
+    scale = max(np.abs(y_ref).max(), 1e-30)
+    if y_dtype == torch.float32:
+        assert np.abs(got - y_ref).max() <= 1e-3 * scale
+        # the reference's random-payload bound against double accumulation
+        acc, mag = port.gemv_dequant_f64(dtype, host, rows, K, port.dequant_act(staging, K))
+        assert np.all(np.abs(got - acc) <= 1e-4 * mag + 1e-3)
+    else:
+        want = O.bf16_round(y_ref)
+        ulp = np.maximum(np.abs(want), 1e-30) * 2.0 ** -7
+        assert np.all(np.abs(got - want) <= ulp)
+    return got, y_ref
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("K", [512, 1024, 2048, 4096, 6656])
+def test_random_payload_small_rows(kd, port, dtype, K):
+    _check(kd, port, dtype, 7, K, 0xC0FFEE, "random")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [1, 3, 5, 17, 256, 1023, 1024, 1025, 1102])
+def test_row_tails(kd, port, dtype, rows):
+    _check(kd, port, dtype, rows, 2048 if dtype != O.Q4_K else 512, 11 + rows, "random")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_bf16_activations_and_outputs(kd, port, dtype):
+    _check(kd, port, dtype, 256, 4096, 5, "synth", torch.bfloat16, torch.float32)
+    _check(kd, port, dtype, 256, 4096, 6, "synth", torch.bfloat16, torch.bfloat16, probe=False)
+    _check(kd, port, dtype, 33, 2048, 7, "random", torch.float32, torch.bfloat16, probe=False)
+
+
+def test_crafted_unit_scale_cases(kd, port):
+    """Exact-value packings of tests/Test_GGUF.cpp:616-682 with the 1e-3 absolute bound of :1138-1145."""
+    dev = torch.device("cuda:0")
+    for dtype, K in [(O.Q4_K, 512), (O.Q4_K, 4096), (O.Q6_K, 2048), (O.Q6_K, 4096), (O.Q8_0, 512)]:
+        N = 5
+        idx = (np.arange(N * K).reshape(N, K))
+        if dtype == O.Q4_K:
+            vals = (idx % 16).astype(np.uint8).reshape(N, K // 256, 4, 2, 32)
+            blocks = np.zeros((N, K // 256, 144), dtype=np.uint8)
+            blocks[..., 0:2] = np.frombuffer(np.uint16(0x3C00).tobytes(), dtype=np.uint8)
+            blocks[..., 4:16] = np.array([1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1], dtype=np.uint8)
+            blocks[..., 16:] = (vals[:, :, :, 0, :] | (vals[:, :, :, 1, :] << 4)).reshape(N, K // 256, 128)
+            dense = (idx % 16).astype(np.float32)
+        elif dtype == O.Q6_K:
+            v = (idx % 16).astype(np.uint8).reshape(N, K // 256, 2, 4, 32)   # stored nibble = value + 32 - 32
+            blocks = np.zeros((N, K // 256, 210), dtype=np.uint8)
+            ql = blocks[..., :128].reshape(N, K // 256, 2, 2, 32)
+            ql[:, :, :, 0, :] = v[:, :, :, 0, :] | (v[:, :, :, 2, :] << 4)
+            ql[:, :, :, 1, :] = v[:, :, :, 1, :] | (v[:, :, :, 3, :] << 4)
+            blocks[..., 192:208] = 1
+            blocks[..., 208:210] = np.frombuffer(np.uint16(0x3C00).tobytes(), dtype=np.uint8)
+            dense = -32.0 + (idx % 16).astype(np.float32)
+        else:
+            dense = (0.125 * (idx % 5) - 0.25).astype(np.float32)
+            blocks = kd.ggml_pack.quantize_q8_0(dense)
+        packed = blocks.reshape(N, -1)
+        host = O.aligned_copy(packed)
+        if dtype != O.Q8_0:
+            assert np.array_equal(port.dequant_rows(dtype, host, N, K), dense)
+        x = (0.125 * ((np.arange(K) % 7) - 3)).astype(np.float32)
+        w, y, scratch = _run(kd, dtype, packed, N, K, torch.from_numpy(x), torch.float32)
+        staging = port.quantize_act(x)
+        assert np.array_equal(scratch.cpu().numpy(), staging)
+        acc, _ = port.gemv_dequant_f64(dtype, host, N, K, port.dequant_act(staging, K))
+        assert np.abs(y.cpu().numpy() - acc).max() <= 1e-3
+
+
+def test_quantizer_edge_values(kd, port):
+    """All-zero blocks give d = 0, q = 0; +-amax hit +-127; ties round to even."""
+    dev = torch.device("cuda:0")
+    K = 256
+    x = np.zeros(K, dtype=np.float32)
+    x[32:64] = np.linspace(-1, 1, 32)
+    x[64:96] = 0.5 * 127.0 / 127.0 * np.where(np.arange(32) % 2, 1.0, -1.0)
+    x[96:128] = (np.arange(32) + 0.5) * (1.0 / 127.0) * 4          # .5 ties after scaling by 127/amax
+    x[128:160] = 1e-30
+    x[160:192] = np.float32(3.0e38)
+    for dt in (torch.float32, torch.bfloat16):
+        xt = torch.from_numpy(x).to(dt)
+        scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+        kd.quantize_act_q8(xt.to(dev), scratch)
+        torch.cuda.synchronize()
+        assert np.array_equal(scratch.cpu().numpy(), port.quantize_act(xt.float().numpy()))
+
+
+def test_generic_kernel_matches_for_misaligned_payload(kd, port):
+    """A payload base that is only 2-byte aligned (allowed for Q6_K / Q8_0 by the reference's contract,
+    src/KokkosDNN_GGUFGemvInt8.hpp:739-743) takes the plain-load kernels."""
+    dev = torch.device("cuda:0")
+    for dtype in (O.Q6_K, O.Q8_0):
+        rows, K = 19, 2048
+        packed = kd.ggml_pack.random_payload(dtype, rows, K, 3)
+        buf = torch.zeros(packed.size + 16, dtype=torch.uint8, device=dev)
+        buf[2:2 + packed.size] = torch.from_numpy(packed.reshape(-1)).to(dev)
+        w = kd.QuantWeight(buf[2:2 + packed.size], dtype, rows, K)
+        x = torch.randn(K, generator=torch.Generator().manual_seed(9))
+        y = torch.empty(rows, dtype=torch.float32, device=dev)
+        scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+        kd.quant_gemv(x.to(dev), w, y, scratch)
+        torch.cuda.synchronize()
+        y_ref, staging = port.gemv_int8(dtype, O.aligned_copy(packed), rows, K, x.numpy())
+        assert np.array_equal(scratch.cpu().numpy(), staging)
+        assert np.abs(y.cpu().numpy() - y_ref).max() <= 1e-3 * np.abs(y_ref).max()
+
+
+@pytest.mark.parametrize("dtype,rows,K", [(O.Q4_K, 4096, 4096), (O.Q8_0, 4096, 4096),
+                                           (O.Q4_K, 14336, 4096), (O.Q6_K, 4096, 14336)])
+def test_baseline_shapes_full_size(kd, port, dtype, rows, K):
+    """The benchmark configurations themselves, every row against the checker."""
+    _check(kd, port, dtype, rows, K, 1234, "synth", torch.bfloat16, torch.float32, probe=False)
+
+
+def test_golden_fixture(kd):
+    """Outputs of the reference's own int8 quant_gemv, generated by tests/golden/make_golden.py."""
+    import os
+    path = os.path.join(os.path.dirname(__file__), "golden", "gemv_int8.npz")
+    g = np.load(path)
+    dev = torch.device("cuda:0")
+    for tag in [t[:-2] for t in g.files if t.endswith("_w")]:
+        dtype, rows, K = [int(v) for v in g[tag + "_meta"]]
+        x = torch.from_numpy(g[tag + "_x"])
+        xt = x.to(torch.bfloat16) if "bf16" in tag else x
+        w, y, scratch = _run(kd, dtype, g[tag + "_w"], rows, K, xt, torch.float32)
+        assert np.array_equal(scratch.cpu().numpy(), g[tag + "_staging"])
+        yr = g[tag + "_y"]
+        if "bf16" in tag:   # the reference rounded y to bf16
+            got = O.bf16_round(y.cpu().numpy())
+            assert np.all(np.abs(got - yr) <= np.abs(yr) * 2.0 ** -7 + 1e-30)
+        else:
+            assert np.abs(y.cpu().numpy() - yr).max() <= 1e-3 * np.abs(yr).max()
