@@ -1,5 +1,51 @@
-#include "kdnn_common.cuh"
+// Batched GEMV / skinny GEMM Y[M,N] = X[M,K] W[N,K]^T with packed W and per-row
+// int8 activations: the grouped kernel of kdnn_grouped.cuh with one group that
+// holds all M activation rows. Row m of Y equals the decode GEMV applied to row m.
+#include "kdnn_grouped.cuh"
+
 namespace kdnn {
-size_t gemm_workspace_bytes(size_t M, size_t K) { return M * ((act_bytes(K) + 255) & ~size_t(255)); }
-cudaError_t gemm_launch(uint32_t, const void*, size_t, size_t, const void*, size_t, size_t, int, void*, size_t, int, void*, cudaStream_t) { return cudaErrorNotSupported; }
+
+// workspace: [offs: 2 ints | pad to 256][wptr: 1 address | pad to 256][list: M ints][items: M x K/64]
+static size_t gemm_items_offset(size_t M) { return 512 + ((M * sizeof(int) + 255) & ~size_t(255)); }
+size_t gemm_workspace_bytes(size_t M, size_t K) {
+  return gemm_items_offset(M) + M * (K / 64) * sizeof(ActItem);
 }
+
+__global__ void gemm_setup_kernel(int M, uintptr_t w, int* offs, uintptr_t* wptr, int* list) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0) {
+    offs[0] = 0;
+    offs[1] = M;
+    wptr[0] = w;
+  }
+  if (i < M) list[i] = i;
+}
+
+cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const void* X, size_t ldx,
+                        size_t M, int xs, void* Y, size_t ldy, int ys, void* ws, cudaStream_t st) {
+  uint8_t* b      = static_cast<uint8_t*>(ws);
+  int* offs       = reinterpret_cast<int*>(b);
+  uintptr_t* wptr = reinterpret_cast<uintptr_t*>(b + 256);
+  int* list       = reinterpret_cast<int*>(b + 512);
+  gemm_setup_kernel<<<(unsigned)((M + 255) / 256), 256, 0, st>>>((int)M, reinterpret_cast<uintptr_t>(w),
+                                                                 offs, wptr, list);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  ActItem* items = reinterpret_cast<ActItem*>(b + gemm_items_offset(M));
+  err = xs == KDNN_F32
+            ? launch_quantize_items<float>(dt, static_cast<const float*>(X), ldx, (int)M, (int)K, nullptr, items, st)
+            : launch_quantize_items<__nv_bfloat16>(dt, static_cast<const __nv_bfloat16*>(X), ldx, (int)M, (int)K, nullptr, items, st);
+  if (err != cudaSuccess) return err;
+  GroupedParams p{};
+  p.w0 = wptr;
+  p.row_bytes0 = (int)row_bytes_of(dt, K);
+  p.N = (int)N; p.K = (int)K;
+  p.offs = offs; p.list = list; p.S = 1; p.g_first = 0;
+  p.src = items; p.dst = Y; p.ld_dst = ldy;
+  if (xs == KDNN_F32 && ys == KDNN_F32) return launch_grouped_dt<2, float, float>(dt, p, 1, st);
+  if (xs == KDNN_BF16 && ys == KDNN_BF16) return launch_grouped_dt<2, __nv_bfloat16, __nv_bfloat16>(dt, p, 1, st);
+  if (xs == KDNN_BF16 && ys == KDNN_F32) return launch_grouped_dt<2, __nv_bfloat16, float>(dt, p, 1, st);
+  return launch_grouped_dt<2, float, __nv_bfloat16>(dt, p, 1, st);
+}
+
+}  // namespace kdnn

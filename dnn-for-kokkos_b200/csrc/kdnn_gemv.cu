@@ -21,6 +21,7 @@
 #include "kdnn_common.cuh"
 
 #include <limits.h>
+#include <stdlib.h>
 
 namespace kdnn {
 
@@ -67,32 +68,45 @@ __device__ __forceinline__ void stage_activations(const XT* __restrict__ x, int 
   const bool vec_ok  = (reinterpret_cast<uintptr_t>(x) & (sizeof(XT) * 4 - 1)) == 0;
   int8_t* gq         = reinterpret_cast<int8_t*>(gscratch);
   ActHdr* gh         = gscratch ? reinterpret_cast<ActHdr*>(gscratch + act_hdr_offset(K)) : nullptr;
-  for (int base = (threadIdx.x >> 5) * 4; base < nblk; base += warps * 4) {
-    const int b      = base + (lane >> 3);
-    const bool valid = b < nblk;
-    float v[4]       = {0.f, 0.f, 0.f, 0.f};
-    if (valid) load4<XT>(x, static_cast<size_t>(b) * 32 + l8 * 4, vec_ok, v);
-    float d;
-    int part, total;
-    const uint32_t packed = quantize_block_lane(v, d, part, total);
-    if (!valid) continue;
-    const int p = l8 >> 2;
-    int item, g;
-    granule_of<DT>(b, p, item, g);
-    reinterpret_cast<uint32_t*>(xg + static_cast<size_t>(g) * nitems + item)[l8 & 3] = packed;
-    if ((l8 & 3) == 0) {
-      if (DT == KDNN_GGML_Q6_K) {
-        reinterpret_cast<float*>(hd + item)[g] = d;
-        reinterpret_cast<int*>(hs + item)[g]   = part << 5;
-      } else if (p == 0) {
-        float* h = reinterpret_cast<float*>(hd + (b >> 1));
-        h[b & 1] = d;
-        if (DT == KDNN_GGML_Q4_K) h[2 + (b & 1)] = __fmul_rn(static_cast<float>(total), d);
-      }
+  // U independent loads in flight per thread before any of them is consumed: the
+  // prologue is one memory round trip, not one per block.
+  constexpr int U = 4;
+  const int step  = warps * 4;
+  for (int base0 = (threadIdx.x >> 5) * 4; base0 < nblk; base0 += step * U) {
+    float v[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int b = base0 + u * step + (lane >> 3);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[u][i] = 0.f;
+      if (b < nblk) load4<XT>(x, static_cast<size_t>(b) * 32 + l8 * 4, vec_ok, v[u]);
     }
-    if (gscratch) {
-      reinterpret_cast<uint32_t*>(gq + static_cast<size_t>(b) * 32)[l8] = packed;
-      if (l8 == 0) gh[b] = ActHdr{d, part, total - part, 0};
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (base0 + u * step >= nblk) break;  // uniform across the warp
+      const int b = base0 + u * step + (lane >> 3);
+      float d;
+      int part, total;
+      const uint32_t packed = quantize_block_lane(v[u], d, part, total);
+      if (b >= nblk) continue;
+      const int p = l8 >> 2;
+      int item, g;
+      granule_of<DT>(b, p, item, g);
+      reinterpret_cast<uint32_t*>(xg + static_cast<size_t>(g) * nitems + item)[l8 & 3] = packed;
+      if ((l8 & 3) == 0) {
+        if (DT == KDNN_GGML_Q6_K) {
+          reinterpret_cast<float*>(hd + item)[g] = d;
+          reinterpret_cast<int*>(hs + item)[g]   = part << 5;
+        } else if (p == 0) {
+          float* h = reinterpret_cast<float*>(hd + (b >> 1));
+          h[b & 1] = d;
+          if (DT == KDNN_GGML_Q4_K) h[2 + (b & 1)] = __fmul_rn(static_cast<float>(total), d);
+        }
+      }
+      if (gscratch) {
+        reinterpret_cast<uint32_t*>(gq + static_cast<size_t>(b) * 32)[l8] = packed;
+        if (l8 == 0) gh[b] = ActHdr{d, part, total - part, 0};
+      }
     }
   }
 }
@@ -244,13 +258,14 @@ struct GemvParams {
   int nchunks;        // ceil(nitems / 32)
   int ngroups;        // ceil(rows / RW)
   int stages;         // ring depth per warp
+  int stream_warps;   // warps that own a ring (the CTA may hold more, for the prologue)
   int stage_bytes;    // RW * chunk_bytes_full, rounded up to 128
 };
 
 template <uint32_t DT, int RW, class XT, class YT>
 __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = p.stream_warps;
   // shared layout: [xg 4*nitems*16][hd nitems*16][hs nitems*16 (Q6_K)] [barriers] [rings]
   int4* xg      = reinterpret_cast<int4*>(smem);
   float4* hd    = reinterpret_cast<float4*>(smem + static_cast<size_t>(p.nitems) * 64);
@@ -266,7 +281,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const GemvParams p)
   // this warp's work: row groups gw, gw+G, ...; each split into nchunks stages
   const int G  = gridDim.x * nwarps;
   const int gw = warp * gridDim.x + blockIdx.x;
-  const int my_groups = gw < p.ngroups ? (p.ngroups - gw + G - 1) / G : 0;
+  const int my_groups = (warp < nwarps && gw < p.ngroups) ? (p.ngroups - gw + G - 1) / G : 0;
   const int n_total   = my_groups * p.nchunks;
 
   auto issue = [&](int n) {  // lane 0 only
@@ -288,7 +303,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const GemvParams p)
         bulk_g2s(dst + r * chunk_bytes_full<DT>(), src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
   };
 
-  if (lane == 0) {
+  if (lane == 0 && warp < nwarps) {
     for (int s = 0; s < p.stages; ++s) mbar_init(bar_u32 + s * 8, 1);
     fence_barrier_init();
     fence_proxy_async();
@@ -495,6 +510,16 @@ static const DeviceInfo& device_info() {
   return d;
 }
 
+// KDNN_NO_PDL=1 launches without programmatic stream serialization (A/B aid).
+static bool use_pdl() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("KDNN_NO_PDL");
+    v             = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v != 0;
+}
+
 template <uint32_t DT, int RW, class XT, class YT>
 static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   const DeviceInfo& di = device_info();
@@ -516,6 +541,7 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   while (smem_need(nwarps, stages) > budget && nwarps > 1) --nwarps;
   if (smem_need(nwarps, stages) > budget) return cudaErrorInvalidConfiguration;
   p.stages       = stages;
+  p.stream_warps = nwarps;
   const int grid = min(di.sms, (p.ngroups + nwarps - 1) / nwarps);
   const size_t smem = smem_need(nwarps, stages);
   auto kern = gemv_stream_kernel<DT, RW, XT, YT>;
@@ -528,14 +554,14 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim            = dim3(grid);
-  cfg.blockDim           = dim3(nwarps * 32);
+  cfg.blockDim           = dim3((nwarps < 8 ? 8 : nwarps) * 32);
   cfg.dynamicSmemBytes   = smem;
   cfg.stream             = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs                                          = attr;
-  cfg.numAttrs                                       = 1;
+  cfg.numAttrs                                       = use_pdl() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 

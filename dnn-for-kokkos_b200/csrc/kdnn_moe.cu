@@ -1,7 +1,279 @@
-#include "kdnn_common.cuh"
+// MoE kernels for sm_100a: router (top-k + weights), slot sort by expert, the
+// packed expert feed-forward with per-32 int8 activations (gate/up + SwiGLU,
+// down), and the weighted combine.
+//
+// Launch sequence of kdnn_b200_moe_ffn (no host synchronisation anywhere; the
+// routing result is consumed on the device, as in the reference's fused decode
+// kernels, src/KokkosDNN_GGUF.hpp:2329-2332):
+//   1. moe_sort_kernel      slots (t,s) grouped by expert -> offsets, slot list
+//   2. quantize_items       x rows -> per-32 int8 items
+//   3. grouped_gemm<1>      act[pos, j] = Scalar(silu(gate_e x_t)_j * (up_e x_t)_j)
+//   4. quantize_items       act rows -> per-32 int8 items
+//   5. grouped_gemm<0>      out[pos, d] = down_e[d,:] . act[pos,:]
+//   6. moe_combine_kernel   Y[t, d] = Scalar(sum_s w[t,s] * out[pos(t,s), d])
+// Workspace (caller-owned): offsets, slot list, slot positions, int8 items, act, out.
+#include "kdnn_grouped.cuh"
+
 namespace kdnn {
-cudaError_t moe_route_launch(const void*, size_t, size_t, size_t, int, const void*, int, int, float, int, int32_t*, float*, cudaStream_t) { return cudaErrorNotSupported; }
-size_t moe_workspace_bytes(size_t, size_t, size_t, size_t, size_t) { return 256; }
-cudaError_t moe_ffn_launch(const void*, size_t, size_t, int, const kdnn_b200_weight_table*, const kdnn_b200_weight_table*, const kdnn_b200_weight_table*, const int32_t*, const float*, size_t, void*, size_t, int, size_t, size_t, void*, cudaStream_t) { return cudaErrorNotSupported; }
-int moe_take_status() { return 0; }
+
+__device__ int g_moe_status = 0;
+
+// ---- router ----------------------------------------------------------------------
+// One warp per token; the E scores live in shared memory (src/KokkosDNN_MoE.hpp:
+// 161-200 stages them the same way), selection is a warp arg-max repeated top_k
+// times with the reference's tie rule (strict '>' scanning ids upward = lowest id
+// among equals), weights are recomputed from the logits by lane 0 in the
+// reference's order (:114-146).
+template <class ST>
+__global__ void moe_route_kernel(const ST* __restrict__ logits, size_t ld, int T, int E,
+                                 const ST* __restrict__ bias, int top_k, int norm_topk,
+                                 float routed_scale, int sigmoid, int32_t* __restrict__ top_idx,
+                                 float* __restrict__ top_w) {
+  extern __shared__ float route_smem[];
+  constexpr float NEG = -3.4028235e38f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const int t = blockIdx.x * wpb + warp;
+  if (t >= T) return;
+  float* score = route_smem + static_cast<size_t>(warp) * E;
+  const ST* lg = logits + static_cast<size_t>(t) * ld;
+  for (int e = lane; e < E; e += 32) {
+    const float raw = to_f32(lg[e]);
+    const float b   = bias ? to_f32(bias[e]) : 0.0f;
+    score[e]        = sigmoid ? (1.0f / (1.0f + expf(-raw))) + b : raw + b;
+  }
+  __syncwarp();
+  float gmx = NEG, gsum = 0.0f;
+  if (!sigmoid && !norm_topk) {  // global softmax denominator, sequential like the reference
+    if (lane == 0) {
+      for (int e = 0; e < E; ++e)
+        if (score[e] > gmx) gmx = score[e];
+      for (int e = 0; e < E; ++e) gsum += expf(score[e] - gmx);
+    }
+  }
+  int32_t* idx = top_idx + static_cast<size_t>(t) * top_k;
+  float* w     = top_w + static_cast<size_t>(t) * top_k;
+  for (int k = 0; k < top_k; ++k) {
+    float best = NEG;
+    int be     = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float s = score[e];
+      if (s > best) {
+        best = s;
+        be   = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe   = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ob > best || (ob == best && oe < be)) {
+        best = ob;
+        be   = oe;
+      }
+    }
+    if (be == 0x7fffffff) be = -1;  // nothing above the sentinel
+    if (lane == 0) {
+      idx[k] = be;
+      if (be >= 0) score[be] = NEG;
+    }
+    __syncwarp();
+  }
+  if (lane != 0) return;
+  auto logit = [&](int k) {
+    const int i     = idx[k];
+    const float raw = to_f32(lg[i < 0 ? 0 : i]);
+    return sigmoid ? 1.0f / (1.0f + expf(-raw)) : raw + (bias ? to_f32(bias[i < 0 ? 0 : i]) : 0.0f);
+  };
+  if (sigmoid) {
+    if (norm_topk) {
+      float sum = 0.0f;
+      for (int k = 0; k < top_k; ++k) sum += logit(k);
+      const float denom = sum + 1e-6f;
+      for (int k = 0; k < top_k; ++k) w[k] = logit(k) / denom * routed_scale;
+    } else {
+      for (int k = 0; k < top_k; ++k) w[k] = logit(k) * routed_scale;
+    }
+  } else if (norm_topk) {
+    float mx = NEG, sum = 0.0f;
+    for (int k = 0; k < top_k; ++k) mx = logit(k) > mx ? logit(k) : mx;
+    for (int k = 0; k < top_k; ++k) sum += expf(logit(k) - mx);
+    for (int k = 0; k < top_k; ++k) w[k] = expf(logit(k) - mx) / sum * routed_scale;
+  } else {
+    for (int k = 0; k < top_k; ++k) w[k] = expf(logit(k) - gmx) / gsum * routed_scale;
+  }
 }
+
+cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, int scalar,
+                             const void* bias, int top_k, int norm_topk, float routed_scale,
+                             int sigmoid, int32_t* top_idx, float* top_w, cudaStream_t st) {
+  int wpb = 4;
+  while (wpb > 1 && static_cast<size_t>(wpb) * E * sizeof(float) > 48 * 1024) wpb >>= 1;
+  const size_t smem = static_cast<size_t>(wpb) * E * sizeof(float);
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  const int blocks = static_cast<int>((T + wpb - 1) / wpb);
+  if (scalar == KDNN_F32)
+    moe_route_kernel<float><<<blocks, wpb * 32, smem, st>>>(
+        static_cast<const float*>(logits), ld, (int)T, (int)E, static_cast<const float*>(bias), top_k,
+        norm_topk, routed_scale, sigmoid, top_idx, top_w);
+  else
+    moe_route_kernel<__nv_bfloat16><<<blocks, wpb * 32, smem, st>>>(
+        static_cast<const __nv_bfloat16*>(logits), ld, (int)T, (int)E,
+        static_cast<const __nv_bfloat16*>(bias), top_k, norm_topk, routed_scale, sigmoid, top_idx, top_w);
+  return cudaGetLastError();
+}
+
+// ---- slot sort ---------------------------------------------------------------------
+// Groups the T*S routed slots by expert for experts in [e_first, e_first+e_count).
+//   offs[e_count + 1]  start of each local expert's run in `list`
+//   list[n]            slot id (t*S + s) of the n-th position
+//   pos[t*S + s]       position of the slot in `list`, or -1 when the slot's expert
+//                      is out of range / not local (it then contributes nothing,
+//                      src/KokkosDNN_GGUF.hpp:2106-2110)
+// One CTA. Order inside an expert's run is by slot id (token-major), as the
+// reference's host-side counting sort produces
+// (models/lfm2_5/KokkosDNN_LFM25Model.hpp:455-486); results do not depend on it.
+__global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_slots, int e_first,
+                                int e_count, int* __restrict__ offs, int* __restrict__ list,
+                                int* __restrict__ pos) {
+  extern __shared__ int sort_smem[];  // counts[e_count], cursor[e_count]
+  int* counts = sort_smem;
+  int* cursor = sort_smem + e_count;
+  for (int e = threadIdx.x; e < e_count; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
+    const int e = idx[i] - e_first;
+    if (e >= 0 && e < e_count) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < e_count; ++e) {
+      offs[e]   = run;
+      cursor[e] = run;
+      run += counts[e];
+    }
+    offs[e_count] = run;
+  }
+  __syncthreads();
+  // stable placement: expert e's run is filled by one thread scanning slot ids upward
+  for (int e = threadIdx.x; e < e_count; e += blockDim.x) {
+    if (counts[e] == 0) continue;
+    int c = cursor[e];
+    for (int i = 0; i < n_slots; ++i)
+      if (idx[i] - e_first == e) {
+        list[c] = i;
+        pos[i]  = c++;
+      }
+  }
+  for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
+    const int e = idx[i] - e_first;
+    if (e < 0 || e >= e_count) pos[i] = -1;
+  }
+}
+
+// Y[t, d] = Scalar(sum_s w[t,s] * out[pos(t,s), d]), slots ascending, fp32
+// (src/KokkosDNN_MoE.hpp:326-331; zero-weight and unrouted slots skipped,
+// src/KokkosDNN_GGUF.hpp:2205-2207).
+template <class YT>
+__global__ void moe_combine_kernel(const float* __restrict__ out, const int* __restrict__ pos,
+                                   const float* __restrict__ wts, int T, int S, int H, YT* Y,
+                                   size_t ldy) {
+  const int t = blockIdx.y;
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= H) return;
+  float acc = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const int ps  = pos[t * S + s];
+    const float w = wts[t * S + s];
+    if (ps < 0 || w == 0.0f) continue;
+    acc += w * out[static_cast<size_t>(ps) * H + d];
+  }
+  store_scalar(Y + static_cast<size_t>(t) * ldy + d, acc);
+}
+
+// ---- workspace layout -------------------------------------------------------------------
+struct MoeWs {
+  size_t offs, list, pos, xq, act, actq, out, total;
+};
+static MoeWs moe_ws_layout(size_t T, size_t S, size_t H, size_t F, size_t n_experts) {
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  MoeWs w{};
+  size_t o = 0;
+  w.offs = o; o += up((n_experts + 1) * sizeof(int));
+  w.list = o; o += up(T * S * sizeof(int));
+  w.pos  = o; o += up(T * S * sizeof(int));
+  w.xq   = o; o += up(T * (H / 64) * sizeof(ActItem));
+  w.act  = o; o += up(T * S * F * sizeof(float));
+  w.actq = o; o += up(T * S * (F / 64) * sizeof(ActItem));
+  w.out  = o; o += up(T * S * H * sizeof(float));
+  w.total = o;
+  return w;
+}
+size_t moe_workspace_bytes(size_t T, size_t S, size_t H, size_t F, size_t n_experts) {
+  return moe_ws_layout(T, S, H, F, n_experts).total;
+}
+
+cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
+                           const kdnn_b200_weight_table* gate, const kdnn_b200_weight_table* up,
+                           const kdnn_b200_weight_table* down, const int32_t* idx, const float* wts,
+                           size_t S, void* Y, size_t ldy, int ys, size_t e_first, size_t e_count,
+                           void* ws, cudaStream_t st) {
+  const size_t H = gate->cols, F = gate->rows;
+  if (gate->ggml_type != up->ggml_type) return cudaErrorNotSupported;  // mixed gate/up recipe
+  const MoeWs L = moe_ws_layout(T, S, H, F, gate->n_experts);
+  uint8_t* b    = static_cast<uint8_t*>(ws);
+  int* offs = reinterpret_cast<int*>(b + L.offs);
+  int* list = reinterpret_cast<int*>(b + L.list);
+  int* pos  = reinterpret_cast<int*>(b + L.pos);
+  float* act = reinterpret_cast<float*>(b + L.act);
+  ActItem* xq   = reinterpret_cast<ActItem*>(b + L.xq);
+  ActItem* actq = reinterpret_cast<ActItem*>(b + L.actq);
+  float* out = reinterpret_cast<float*>(b + L.out);
+  const int n_slots = static_cast<int>(T * S);
+  moe_sort_kernel<<<1, 1024, 2 * (e_count + 1) * sizeof(int), st>>>(idx, n_slots, (int)e_first,
+                                                                     (int)e_count, offs, list, pos);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  if (e_count > 0) {
+    err = xs == KDNN_F32
+              ? launch_quantize_items<float>(gate->ggml_type, static_cast<const float*>(X), ldx, (int)T, (int)H, nullptr, xq, st)
+              : launch_quantize_items<__nv_bfloat16>(gate->ggml_type, static_cast<const __nv_bfloat16*>(X), ldx, (int)T, (int)H, nullptr, xq, st);
+    if (err != cudaSuccess) return err;
+    GroupedParams g{};
+    g.w0 = gate->base; g.w1 = up->base;
+    g.row_bytes0 = (int)gate->row_bytes; g.row_bytes1 = (int)up->row_bytes;
+    g.N = (int)F; g.K = (int)H;
+    g.offs = offs; g.list = list; g.S = (int)S; g.g_first = (int)e_first;
+    g.src = xq; g.dst = act; g.ld_dst = F; g.round_bf16 = xs == KDNN_BF16;
+    err = xs == KDNN_F32 ? launch_grouped_dt<1, float, float>(gate->ggml_type, g, (int)e_count, st)
+                         : launch_grouped_dt<1, __nv_bfloat16, float>(gate->ggml_type, g, (int)e_count, st);
+    if (err != cudaSuccess) return err;
+    err = launch_quantize_items<float>(down->ggml_type, act, F, n_slots, (int)F, offs + e_count, actq, st);
+    if (err != cudaSuccess) return err;
+    GroupedParams d{};
+    d.w0 = down->base; d.w1 = nullptr;
+    d.row_bytes0 = (int)down->row_bytes;
+    d.N = (int)H; d.K = (int)F;
+    d.offs = offs; d.list = list; d.S = (int)S; d.g_first = (int)e_first;
+    d.src = actq; d.dst = out; d.ld_dst = H;
+    err = launch_grouped_dt<0, float, float>(down->ggml_type, d, (int)e_count, st);
+    if (err != cudaSuccess) return err;
+  }
+  dim3 cgrid((unsigned)((H + 255) / 256), (unsigned)T);
+  if (ys == KDNN_F32)
+    moe_combine_kernel<float><<<cgrid, 256, 0, st>>>(out, pos, wts, (int)T, (int)S, (int)H,
+                                                     static_cast<float*>(Y), ldy);
+  else
+    moe_combine_kernel<__nv_bfloat16><<<cgrid, 256, 0, st>>>(out, pos, wts, (int)T, (int)S, (int)H,
+                                                             static_cast<__nv_bfloat16*>(Y), ldy);
+  return cudaGetLastError();
+}
+
+int moe_take_status() {
+  int v = 0, zero = 0;
+  cudaMemcpyFromSymbol(&v, g_moe_status, sizeof(int));
+  if (v != 0) cudaMemcpyToSymbol(g_moe_status, &zero, sizeof(int));
+  return v;
+}
+
+}  // namespace kdnn
