@@ -1,0 +1,409 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-moe]
+
+Workload (``config.workload``): the mixed-format decode GEMVs at Llama-3-8B shapes,
+batch 1, bf16 activations ~ N(0,1), weights quantized from seeded N(0, 0.02) fp32:
+Q8_0 4096x4096, Q4_K 14336x4096, Q6_K 4096x14336. One STEP is one pass over
+``rotate`` distinct copies of the three matrices (more bytes than two L2s, so every
+weight byte comes from HBM), i.e. 3*rotate GEMV launches replayed from one CUDA graph.
+
+Metric: GB/s of algorithmic bytes (packed weight bytes + x + y per GEMV, the
+reference's own convention of counting the packed payload). ``roofline`` is the Q4_K
+14336x4096 GEMV alone, timed with CUDA events on the launch stream, against the
+measured HBM copy bandwidth in MEASURED_PEAKS.json. ``e2e`` is the same pass driven
+from pinned host buffers: per GEMV the activation row is copied host->device and the
+result row device->host inside the timed region. ``moe_decode`` carries the second
+headline number (tokens/s of the 48-layer, 128-expert, top-8 MoE stack at 256 tokens).
+
+With --gpus N > 1 (launched under torchrun) every rank runs the same GEMV pass on its
+own GPU (the GEMV does not shard at these sizes: replicas only) and the MoE stack is
+expert-parallel over the ranks.
+
+``--impl reference`` times the reference's own CPU int8 GEMV (oracle/_ref, compiled
+from the reference's headers; the C port when that library is absent) on the host
+cores, on the same matrices.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+Q8_0, Q4_K, Q6_K = 8, 12, 14
+GEMV_SHAPES = [("Q8_0", Q8_0, 4096, 4096), ("Q4_K", Q4_K, 14336, 4096), ("Q6_K", Q6_K, 4096, 14336)]
+SEED = 20261125
+
+
+def algorithmic_bytes(dtype, rows, K, xbytes=2, ybytes=4):
+    blk, bsz = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}[dtype]
+    return rows * (K // blk) * bsz + K * xbytes + rows * ybytes
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.rows = []
+        self._stop = threading.Event()
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.idx)], capture_output=True, text=True, timeout=5).stdout
+                for line in out.strip().splitlines():
+                    self.rows.append([c.strip() for c in line.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except Exception:
+                continue
+            for n, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def build_weights(pack):
+    """Seeded N(0, 0.02) fp32 -> packed bytes, one matrix per shape (host numpy)."""
+    out = []
+    for i, (name, dt, rows, K) in enumerate(GEMV_SHAPES):
+        out.append(pack.synth_weight(dt, rows, K, SEED + i, std=0.02))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+def cpu_leg(host_weights, target_seconds, use_ref=True, threads=None):
+    """Times the reference's CPU int8 quant_gemv on the three matrices. Returns
+    (GB/s, cores, kind, sample description, seconds per pass)."""
+    from oracle import oracle as O
+    O.build()
+    if use_ref and O.Ref.available():
+        eng, kind = O.Ref(), "reference"
+    else:
+        eng, kind = O.Port(), "port"
+    cores = os.cpu_count() or 1
+    if threads:
+        cores = threads
+    eng.set_threads(cores)
+    rng = np.random.default_rng(SEED)
+    xs = [O.bf16_round(rng.standard_normal(K).astype(np.float32)) for (_, _, _, K) in GEMV_SHAPES]
+    ws = [O.aligned_copy(w) for w in host_weights]
+    nbytes = sum(algorithmic_bytes(dt, rows, K) for (_, dt, rows, K) in GEMV_SHAPES)
+
+    def one_pass():
+        for (name, dt, rows, K), w, x in zip(GEMV_SHAPES, ws, xs):
+            if kind == "reference":
+                eng.quant_gemv(dt, w, rows, K, x, bf16=True, int8=True)
+            else:
+                eng.gemv_int8(dt, w, rows, K, x)
+
+    one_pass()
+    one_pass()
+    t0 = time.perf_counter()
+    one_pass()
+    t1 = time.perf_counter() - t0
+    n = max(3, min(200, int(target_seconds / max(t1, 1e-6))))
+    times = []
+    for _ in range(n):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    sample = (f"{n} passes over the three GEMVs ({nbytes / 1e6:.1f} MB per pass), best pass; "
+              f"{'reference functor bodies under a stand-in OpenMP scheduler' if kind == 'reference' else 'C restatement with OpenMP'}")
+    return nbytes / best / 1e9, cores, kind, sample, best
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import __graft_entry__ as ge
+    pack = ge._load_module("_kd_pack", os.path.join(ge.PKG_DIR, "ggml_pack.py"))
+    host_weights = build_weights(pack)
+    from oracle import oracle as O
+    O.build()
+    eng = O.Ref() if O.Ref.available() else O.Port()
+    kind = eng.kind
+    cores = os.cpu_count() or 1
+    eng.set_threads(cores)
+    rng = np.random.default_rng(SEED)
+    xs = [O.bf16_round(rng.standard_normal(K).astype(np.float32)) for (_, _, _, K) in GEMV_SHAPES]
+    ws = [O.aligned_copy(w) for w in host_weights]
+    nbytes = sum(algorithmic_bytes(dt, rows, K) for (_, dt, rows, K) in GEMV_SHAPES)
+
+    def step():
+        for (name, dt, rows, K), w, x in zip(GEMV_SHAPES, ws, xs):
+            if kind == "reference":
+                eng.quant_gemv(dt, w, rows, K, x, bf16=True, int8=True)
+            else:
+                eng.gemv_int8(dt, w, rows, K, x)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt_s = time.perf_counter() - t0
+    val = nbytes * args.steps / dt_s / 1e9
+    sample = f"each step = one pass over the three GEMVs ({nbytes / 1e6:.1f} MB), host resident"
+    line = {
+        "impl": "reference", "metric": "gguf_int8_gemv_algorithmic_GBps", "value": val, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 dots, fp32 rescale", "data": "synthetic",
+        "config": {"workload": "mixed-format decode GEMVs, Llama-3-8B shapes: Q8_0 4096x4096, Q4_K 14336x4096, "
+                               "Q6_K 4096x14336, batch 1, bf16 activations", "rotate": 1, "seed": SEED},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import __graft_entry__ as ge
+    kd = ge.load_package()
+    host_weights = build_weights(kd.ggml_pack)
+    per_set = sum(algorithmic_bytes(dt, rows, K) for (_, dt, rows, K) in GEMV_SHAPES)
+    rotate = max(4, int(2 * 126e6 * 1.5 // per_set) + 1)            # > 2 x L2 of distinct bytes per step
+
+    # device state: `rotate` copies of each matrix, inputs, outputs, staging
+    sets = []
+    for r in range(rotate):
+        ws = []
+        for (name, dt, rows, K), hw in zip(GEMV_SHAPES, host_weights):
+            ws.append(kd.QuantWeight.from_numpy(hw, dt, rows, K, dev))
+        sets.append(ws)
+    g = torch.Generator().manual_seed(SEED)
+    xs_host = [torch.randn(K, generator=g).to(torch.bfloat16).pin_memory() for (_, _, _, K) in GEMV_SHAPES]
+    xs = [x.to(dev) for x in xs_host]
+    ys = [torch.empty(rows, dtype=torch.float32, device=dev) for (_, _, rows, _) in GEMV_SHAPES]
+    ys_host = [torch.empty(rows, dtype=torch.float32).pin_memory() for (_, _, rows, _) in GEMV_SHAPES]
+    scr = [torch.empty(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+           for (_, _, _, K) in GEMV_SHAPES]
+
+    def one_pass():
+        for ws in sets:
+            for i, w in enumerate(ws):
+                kd.quant_gemv(xs[i], w, ys[i], scr[i])
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        one_pass()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: K steps, CUDA events on the launch stream ----------
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record(stream)
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+        # keep the GPU busy long enough for a few clock samples
+        if ms_total < 1500:
+            with torch.cuda.stream(stream):
+                for _ in range(int(1500 / max(ms_total / args.steps, 1e-3))):
+                    graph.replay()
+            torch.cuda.synchronize()
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    bytes_step = per_set * rotate
+    value = world * bytes_step * args.steps / (ms_total * 1e-3) / 1e9
+    launches = 3 * rotate * args.steps
+
+    # ---- per-kernel roofline: each shape alone, rotating copies, CUDA events -----------
+    peak, peak_kind = measured_peaks()
+    per_kernel = {}
+    for i, (name, dt, rows, K) in enumerate(GEMV_SHAPES + [("Q4_K_4096", Q4_K, 4096, 4096)]):
+        if i < 3:
+            copies = [s[i] for s in sets]
+            x, y, sc = xs[i], ys[i], scr[i]
+        else:
+            hw = kd.ggml_pack.synth_weight(dt, rows, K, SEED + 9, std=0.02)
+            ncp = int(2 * 126e6 * 1.5 // algorithmic_bytes(dt, rows, K)) + 1
+            copies = [kd.QuantWeight.from_numpy(hw, dt, rows, K, dev) for _ in range(ncp)]
+            x, y, sc = xs[0], torch.empty(rows, dtype=torch.float32, device=dev), scr[0]
+        reps = max(1, int(600e6 // (algorithmic_bytes(dt, rows, K) * len(copies))))
+        gk = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            for w in copies:
+                kd.quant_gemv(x, w, y, sc)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(gk, stream=stream):
+                for _ in range(reps):
+                    for w in copies:
+                        kd.quant_gemv(x, w, y, sc)
+            for _ in range(3):
+                gk.replay()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(5):
+                gk.replay()
+            b.record(stream)
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (5 * reps * len(copies))
+        ab = algorithmic_bytes(dt, rows, K)
+        per_kernel[f"{name}_{rows}x{K}"] = {"us_per_launch": us, "algorithmic_bytes": ab,
+                                            "achieved_GBps": ab / us / 1e3, "frac": ab / us / 1e3 / peak}
+    dom = per_kernel["Q4_K_14336x4096"]
+    roofline = {"kernel": "gemv_stream_kernel<Q4_K> 14336x4096", "bound": "hbm", "achieved": dom["achieved_GBps"],
+                "peak": peak, "peak_source": f"{peak_kind} HBM copy bandwidth (MEASURED_PEAKS.json)",
+                "unit": "GB/s", "frac": dom["frac"], "frac_of_nominal_8TBps": dom["achieved_GBps"] / 8000.0,
+                "traffic": None, "by_shape": per_kernel}
+
+    # ---- end to end through the public call with host buffers --------------------------
+    def e2e_pass():
+        for ws in sets:
+            for i, w in enumerate(ws):
+                xs[i].copy_(xs_host[i], non_blocking=True)
+                kd.quant_gemv(xs[i], w, ys[i], scr[i])
+                ys_host[i].copy_(ys[i], non_blocking=True)
+
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            e2e_pass()
+    barrier()
+    steps_e2e = max(2, min(args.steps, 20))
+    t0 = time.perf_counter()
+    with torch.cuda.stream(stream):
+        for _ in range(steps_e2e):
+            e2e_pass()
+        stream.synchronize()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_val = world * bytes_step * steps_e2e / float(t.item()) / 1e9
+    h2d = rotate * sum(K * 2 for (_, _, _, K) in GEMV_SHAPES)
+    d2h = rotate * sum(rows * 4 for (_, _, rows, _) in GEMV_SHAPES)
+    assert kd.device_status() == 0, "a bounded device-side wait gave up"
+
+    moe = None
+    if not args.no_moe:
+        try:
+            moe_bench = ge._load_module("_kd_moe_bench", os.path.join(ge.PKG_DIR, "moe_stack.py"))
+            moe = moe_bench.bench_moe_stack(kd, dev, rank, world, steps=max(2, min(args.steps, 10)),
+                                            warmup=3, peak=peak)
+        except Exception as ex:  # the GEMV line must still be printed
+            moe = {"error": f"{type(ex).__name__}: {ex}"}
+
+    cpu = None
+    if rank == 0 and world == 1:
+        v, cores, kind, sample, _ = cpu_leg(host_weights, target_seconds=10.0)
+        cpu = {"value": v, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample}
+
+    if rank == 0:
+        line = {
+            "metric": "gguf_int8_gemv_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 dots, fp32 rescale", "data": "synthetic",
+            "config": {"workload": "mixed-format decode GEMVs, Llama-3-8B shapes: Q8_0 4096x4096, Q4_K 14336x4096, "
+                                   "Q6_K 4096x14336, batch 1, bf16 activations, fp32 outputs",
+                       "rotate": rotate, "bytes_per_step": bytes_step, "l2": "inputs larger than L2 "
+                       f"({bytes_step / 1e6:.0f} MB of distinct weights per step)", "seed": SEED,
+                       "multi_gpu": "replicas only (GEMV); MoE stack expert-parallel"},
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches, "clocks": clocks.summary(), "moe_decode": moe,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-moe", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -33,7 +33,7 @@ F32, BF16 = 0, 1
 
 # every symbol include/kdnn_b200.h declares (checked by the CPU test-suite)
 EXPORTS = [
-    "kdnn_b200_last_error", "kdnn_b200_device_status", "kdnn_b200_gemv_scratch_bytes",
+    "kdnn_b200_last_error", "kdnn_b200_device_status", "kdnn_b200_debug_set_trace", "kdnn_b200_gemv_scratch_bytes",
     "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quantize_act_q8",
     "kdnn_b200_unit_dots", "kdnn_b200_gemm_workspace_bytes", "kdnn_b200_quant_gemm",
     "kdnn_b200_moe_route", "kdnn_b200_moe_workspace_bytes", "kdnn_b200_moe_ffn",
@@ -57,6 +57,8 @@ def _load() -> C.CDLL:
             "(there is no CPU or PyTorch fallback)")
     lib = C.CDLL(LIB_PATH)
     lib.kdnn_b200_last_error.restype = C.c_char_p
+    lib.kdnn_b200_debug_set_trace.argtypes = [C.c_void_p]
+    lib.kdnn_b200_debug_set_trace.restype = None
     lib.kdnn_b200_gemv_scratch_bytes.restype = C.c_size_t
     lib.kdnn_b200_gemv_scratch_bytes.argtypes = [C.c_size_t]
     lib.kdnn_b200_gemv_supported.argtypes = [C.c_uint32, C.c_size_t, C.c_int]

@@ -14,6 +14,7 @@ cudaError_t quantize_act_launch(const void* x, int xs, size_t K, void* scratch, 
 cudaError_t unit_dots_launch(uint32_t dt, const void* w, size_t rows, size_t cols,
                              const void* scratch, int32_t* out, cudaStream_t st);
 int gemv_take_status();
+void gemv_set_trace(void* buf);
 
 size_t gemm_workspace_bytes(size_t M, size_t K);
 cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const void* X, size_t ldx,
@@ -66,6 +67,8 @@ int kdnn_b200_device_status(void) {
   const int b = kdnn::moe_take_status();
   return a != 0 ? a : b;
 }
+
+void kdnn_b200_debug_set_trace(void* device_buffer) { kdnn::gemv_set_trace(device_buffer); }
 
 size_t kdnn_b200_gemv_scratch_bytes(size_t K) { return kdnn::act_bytes(K); }
 

@@ -113,6 +113,64 @@ __device__ __forceinline__ uint32_t quantize_block_lane(const float (&v)[4], flo
   return packed;
 }
 
+// Four lanes cooperate on one 32-element block (eight elements each): half the
+// per-block fixed cost (divisions, shuffles, addressing) of the eight-lane form.
+// Returns the lane's eight quantized values as two words (elements 0-3, 4-7).
+__device__ __forceinline__ uint2 quantize_block_lane8(const float (&v)[8], float& d, int& part_sum,
+                                                      int& block_sum) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  d               = __fdiv_rn(amax, 127.0f);
+  const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+  uint32_t w[2]   = {0u, 0u};
+  int s           = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    int q = __float2int_rn(__fmul_rn(v[i], inv));
+    q     = max(-127, min(127, q));
+    s += q;
+    w[i >> 2] |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * (i & 3));
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  part_sum  = s;  // lanes 0-1 of the group: elements 0..15, lanes 2-3: 16..31
+  block_sum = s + __shfl_xor_sync(0xffffffffu, s, 2);
+  return make_uint2(w[0], w[1]);
+}
+
+template <class XT>
+__device__ __forceinline__ void load8(const XT* x, size_t k, bool vec_ok, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* x, size_t k, bool vec_ok, float (&v)[8]) {
+  if (vec_ok) {
+    const float4 a = *reinterpret_cast<const float4*>(x + k);
+    const float4 b = *reinterpret_cast<const float4*>(x + k + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = x[k + i];
+  }
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* x, size_t k, bool vec_ok,
+                                                     float (&v)[8]) {
+  if (vec_ok) {
+    const uint4 t = *reinterpret_cast<const uint4*>(x + k);
+    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i]     = __uint_as_float(u[i] << 16);
+      v[2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(x[k + i]);
+  }
+}
+
 template <class XT>
 __device__ __forceinline__ void load4(const XT* x, size_t k, bool vec_ok, float (&v)[4]);
 template <>

@@ -63,37 +63,37 @@ __device__ __forceinline__ void stage_activations(const XT* __restrict__ x, int 
                                                   uint8_t* gscratch) {
   const int nblk     = K / 32;
   const int lane     = threadIdx.x & 31;
-  const int l8       = lane & 7;
+  const int l4       = lane & 3;          // four lanes per 32-element block, eight elements each
   const int warps    = blockDim.x >> 5;
-  const bool vec_ok  = (reinterpret_cast<uintptr_t>(x) & (sizeof(XT) * 4 - 1)) == 0;
+  const bool vec_ok  = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
   int8_t* gq         = reinterpret_cast<int8_t*>(gscratch);
   ActHdr* gh         = gscratch ? reinterpret_cast<ActHdr*>(gscratch + act_hdr_offset(K)) : nullptr;
   // U independent loads in flight per thread before any of them is consumed: the
   // prologue is one memory round trip, not one per block.
   constexpr int U = 4;
-  const int step  = warps * 4;
-  for (int base0 = (threadIdx.x >> 5) * 4; base0 < nblk; base0 += step * U) {
-    float v[U][4];
+  const int step  = warps * 8;
+  for (int base0 = (threadIdx.x >> 5) * 8; base0 < nblk; base0 += step * U) {
+    float v[U][8];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int b = base0 + u * step + (lane >> 3);
+      const int b = base0 + u * step + (lane >> 2);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[u][i] = 0.f;
-      if (b < nblk) load4<XT>(x, static_cast<size_t>(b) * 32 + l8 * 4, vec_ok, v[u]);
+      for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
+      if (b < nblk) load8<XT>(x, static_cast<size_t>(b) * 32 + l4 * 8, vec_ok, v[u]);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (base0 + u * step >= nblk) break;  // uniform across the warp
-      const int b = base0 + u * step + (lane >> 3);
+      const int b = base0 + u * step + (lane >> 2);
       float d;
       int part, total;
-      const uint32_t packed = quantize_block_lane(v[u], d, part, total);
+      const uint2 packed = quantize_block_lane8(v[u], d, part, total);
       if (b >= nblk) continue;
-      const int p = l8 >> 2;
+      const int p = l4 >> 1;
       int item, g;
       granule_of<DT>(b, p, item, g);
-      reinterpret_cast<uint32_t*>(xg + static_cast<size_t>(g) * nitems + item)[l8 & 3] = packed;
-      if ((l8 & 3) == 0) {
+      reinterpret_cast<uint2*>(xg + static_cast<size_t>(g) * nitems + item)[l4 & 1] = packed;
+      if ((l4 & 1) == 0) {
         if (DT == KDNN_GGML_Q6_K) {
           reinterpret_cast<float*>(hd + item)[g] = d;
           reinterpret_cast<int*>(hs + item)[g]   = part << 5;
@@ -104,8 +104,8 @@ __device__ __forceinline__ void stage_activations(const XT* __restrict__ x, int 
         }
       }
       if (gscratch) {
-        reinterpret_cast<uint32_t*>(gq + static_cast<size_t>(b) * 32)[l8] = packed;
-        if (l8 == 0) gh[b] = ActHdr{d, part, total - part, 0};
+        reinterpret_cast<uint2*>(gq + static_cast<size_t>(b) * 32)[l4] = packed;
+        if (l4 == 0) gh[b] = ActHdr{d, part, total - part, 0};
       }
     }
   }
@@ -247,6 +247,13 @@ __device__ __forceinline__ float item_dot<KDNN_GGML_Q8_0>(uint32_t rowp, int il,
 }
 
 // ---- the streaming kernel --------------------------------------------------------
+// Each CTA owns a contiguous slab of rows. Its work units are (row group, chunk)
+// pairs -- RW consecutive rows x one 2048-element chunk -- dealt round-robin to the
+// CTA's warps, so a slab of R rows x C chunks keeps all warps busy even when R is
+// small. Every warp streams its units through a private ring of shared-memory
+// stages (bulk copies, mbarrier completion), reduces a unit over its lanes and
+// parks the partial row sums in shared memory; at the end the CTA adds each row's
+// chunk partials in chunk order (a fixed order: results do not depend on timing).
 struct GemvParams {
   const uint8_t* w;
   const void* x;
@@ -256,42 +263,60 @@ struct GemvParams {
   int row_bytes;
   int nitems;         // K / 64
   int nchunks;        // ceil(nitems / 32)
-  int ngroups;        // ceil(rows / RW)
+  int rows_per_cta;   // slab height, a multiple of RW
+  int tile_rows;      // rows whose partials fit the shared-memory table, a multiple of RW
   int stages;         // ring depth per warp
-  int stream_warps;   // warps that own a ring (the CTA may hold more, for the prologue)
   int stage_bytes;    // RW * chunk_bytes_full, rounded up to 128
+  unsigned long long* trace;  // optional timeline buffer (debug aid), else null
 };
 
+constexpr int kGemvWarps  = 16;
+constexpr int kTraceSlots = 8;   // timestamps per warp when tracing
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define KDNN_TRACE(slot)                                                                   \
+  do {                                                                                     \
+    if (p.trace && lane == 0)                                                              \
+      p.trace[(static_cast<size_t>(blockIdx.x) * kGemvWarps + warp) * kTraceSlots + (slot)] = globaltimer_ns(); \
+  } while (0)
+
 template <uint32_t DT, int RW, class XT, class YT>
-__global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = p.stream_warps;
-  // shared layout: [xg 4*nitems*16][hd nitems*16][hs nitems*16 (Q6_K)] [barriers] [rings]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // shared layout: [xg 4*nitems*16][hd nitems*16][hs nitems*16 (Q6_K)] [barriers] [partials] [rings]
   int4* xg      = reinterpret_cast<int4*>(smem);
   float4* hd    = reinterpret_cast<float4*>(smem + static_cast<size_t>(p.nitems) * 64);
   int4* hs      = reinterpret_cast<int4*>(smem + static_cast<size_t>(p.nitems) * 80);
   size_t off    = static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80);
   off           = (off + 127) & ~size_t(127);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off) + warp * 8;  // <= 8 stages
-  off += static_cast<size_t>(nwarps) * 64;
-  off = (off + 127) & ~size_t(127);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off) + warp * 8;   // <= 8 stages per warp
+  off += kGemvWarps * 64;
+  float* partial = reinterpret_cast<float*>(smem + off);                 // [tile_rows][nchunks]
+  off += (static_cast<size_t>(p.tile_rows) * p.nchunks * sizeof(float) + 127) & ~size_t(127);
   uint8_t* ring = smem + off + static_cast<size_t>(warp) * p.stages * p.stage_bytes;
   const uint32_t ring_u32 = smem_u32(ring), bar_u32 = smem_u32(bars);
+  KDNN_TRACE(0);
 
-  // this warp's work: row groups gw, gw+G, ...; each split into nchunks stages
-  const int G  = gridDim.x * nwarps;
-  const int gw = warp * gridDim.x + blockIdx.x;
-  const int my_groups = (warp < nwarps && gw < p.ngroups) ? (p.ngroups - gw + G - 1) / G : 0;
-  const int n_total   = my_groups * p.nchunks;
+  const int slab0 = blockIdx.x * p.rows_per_cta;
+  const int slab1 = min(p.rows, slab0 + p.rows_per_cta);
+  YT* y = static_cast<YT*>(p.y);
 
-  auto issue = [&](int n) {  // lane 0 only
-    const int s    = n % p.stages;
-    const int grp  = gw + (n / p.nchunks) * G;
-    const int ch   = n % p.nchunks;
-    const int items = min(kChunkItems, p.nitems - ch * kChunkItems);
+  // Units of the tile that starts at row t0: u -> (group u / nchunks, chunk u % nchunks);
+  // warp w takes u = w, w + 16, ... Consecutive warps read consecutive chunks of a row.
+  int issued = 0;  // lane 0: stages issued so far in the whole kernel (ring position)
+  auto issue_unit = [&](int t0, int t1, int u) {  // lane 0 only
+    const int grp  = u / p.nchunks, ch = u - grp * p.nchunks;
+    const int row0 = t0 + grp * RW;
+    const int nrow = min(RW, t1 - row0);
+    const int items   = min(kChunkItems, p.nitems - ch * kChunkItems);
     const uint32_t cb = chunk_bytes<DT>(items);
-    const int row0 = grp * RW;
-    const int nrow = min(RW, p.rows - row0);
+    const int s = issued % p.stages;
+    ++issued;
     const uint32_t bar = bar_u32 + s * 8;
     mbar_expect_tx(bar, cb * nrow);
     const uint8_t* src = p.w + static_cast<size_t>(row0) * p.row_bytes +
@@ -303,58 +328,82 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const GemvParams p)
         bulk_g2s(dst + r * chunk_bytes_full<DT>(), src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
   };
 
-  if (lane == 0 && warp < nwarps) {
+  if (lane == 0) {
     for (int s = 0; s < p.stages; ++s) mbar_init(bar_u32 + s * 8, 1);
     fence_barrier_init();
     fence_proxy_async();
-    // weights do not depend on the previous kernel in the stream: start streaming now
-    const int pre = min(p.stages, n_total);
-    for (int n = 0; n < pre; ++n) issue(n);
   }
-  pdl_launch_dependents();
-  pdl_wait();  // x may be the previous kernel's output
-  stage_activations<DT, XT>(static_cast<const XT*>(p.x), p.K, p.nitems, xg, hd, hs,
-                            blockIdx.x == 0 ? p.scratch : nullptr);
-  __syncthreads();
+  __syncwarp();
 
-  float acc[RW];
-#pragma unroll
-  for (int r = 0; r < RW; ++r) acc[r] = 0.f;
-  YT* y = static_cast<YT*>(p.y);
-
-  for (int n = 0; n < n_total; ++n) {
-    const int s  = n % p.stages;
-    const int ch = n % p.nchunks;
-    if (!mbar_wait_bounded(bar_u32 + s * 8, (n / p.stages) & 1)) {
-      if (lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
-      return;
+  bool staged = false;
+  int consumed = 0;  // stages consumed so far by this warp (ring position / parity)
+  for (int t0 = slab0; t0 < slab1; t0 += p.tile_rows) {
+    const int t1      = min(slab1, t0 + p.tile_rows);
+    const int ngroups = (t1 - t0 + RW - 1) / RW;
+    const int nunits  = ngroups * p.nchunks;
+    // Weights do not depend on the previous kernel in the stream: the first
+    // `stages` units are requested before the dependency is resolved.
+    int next_u = warp;
+    if (lane == 0)
+      for (int i = 0; i < p.stages && next_u < nunits; ++i, next_u += kGemvWarps) issue_unit(t0, t1, next_u);
+    if (!staged) {
+      KDNN_TRACE(1);
+      pdl_launch_dependents();
+      pdl_wait();  // x may be the previous kernel's output
+      KDNN_TRACE(2);
+      stage_activations<DT, XT>(static_cast<const XT*>(p.x), p.K, p.nitems, xg, hd, hs,
+                                blockIdx.x == 0 ? p.scratch : nullptr);
+      __syncthreads();
+      KDNN_TRACE(3);
+      staged = true;
     }
-    const int item = ch * kChunkItems + lane;
-    if (item < p.nitems) {
-      ItemX x;
+    for (int u = warp; u < nunits; u += kGemvWarps) {
+      const int s = consumed % p.stages;
+      if (!mbar_wait_bounded(bar_u32 + s * 8, (consumed / p.stages) & 1)) {
+        if (lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
+        return;
+      }
+      if (consumed == 0) KDNN_TRACE(4);
+      ++consumed;
+      const int grp = u / p.nchunks, ch = u - grp * p.nchunks;
+      const int item = ch * kChunkItems + lane;
+      float acc[RW];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) x.g[g] = xg[static_cast<size_t>(g) * p.nitems + item];
-      x.hd = hd[item];
-      if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
-      const uint32_t st = ring_u32 + s * p.stage_bytes;
+      for (int r = 0; r < RW; ++r) acc[r] = 0.f;
+      if (item < p.nitems) {
+        ItemX x;
 #pragma unroll
-      for (int r = 0; r < RW; ++r) acc[r] += item_dot<DT>(st + r * chunk_bytes_full<DT>(), lane, x);
-    }
-    if (ch == p.nchunks - 1) {
-      const int row0 = (gw + (n / p.nchunks) * G) * RW;
+        for (int g = 0; g < 4; ++g) x.g[g] = xg[static_cast<size_t>(g) * p.nitems + item];
+        x.hd = hd[item];
+        if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
+        const uint32_t st = ring_u32 + s * p.stage_bytes;
+#pragma unroll
+        for (int r = 0; r < RW; ++r) acc[r] = item_dot<DT>(st + r * chunk_bytes_full<DT>(), lane, x);
+      }
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
         const float v = warp_sum(acc[r]);
-        if (lane == 0 && row0 + r < p.rows) store_scalar(y + row0 + r, v);
-        acc[r] = 0.f;
+        if (lane == 0) partial[(grp * RW + r) * p.nchunks + ch] = v;
+      }
+      __syncwarp();  // every lane has read this stage: it can be refilled
+      if (lane == 0) {
+        next_u = u + p.stages * kGemvWarps;
+        if (next_u < nunits) issue_unit(t0, t1, next_u);
       }
     }
-    __syncwarp();
-    if (lane == 0 && n + p.stages < n_total) {
-      fence_proxy_async();  // order this warp's generic reads before the async refill
-      issue(n + p.stages);
+    __syncthreads();
+    for (int r = threadIdx.x; r < t1 - t0; r += blockDim.x) {
+      float sum = 0.f;
+      for (int c = 0; c < p.nchunks; ++c) sum += partial[r * p.nchunks + c];
+      store_scalar(y + t0 + r, sum);
     }
+    if (t1 < slab1) __syncthreads();  // the table is reused by the next tile
   }
+  if (!staged) {  // a CTA with an empty slab still takes part in the dependency chain
+    pdl_launch_dependents();
+    pdl_wait();
+  }
+  KDNN_TRACE(6);
 }
 
 // ---- generic kernels (any alignment; also the parity probe) ------------------------
@@ -496,7 +545,7 @@ __global__ void unit_dots_kernel(const uint8_t* __restrict__ w, size_t row_bytes
 
 // ---- host side ------------------------------------------------------------------
 struct DeviceInfo {
-  int sms = 0, max_smem = 0;
+  int sms = 0, max_smem = 0, smem_per_sm = 0;
 };
 static const DeviceInfo& device_info() {
   static thread_local DeviceInfo cache[64];
@@ -506,6 +555,7 @@ static const DeviceInfo& device_info() {
   if (d.sms == 0) {
     cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
     cudaDeviceGetAttribute(&d.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    cudaDeviceGetAttribute(&d.smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
   }
   return d;
 }
@@ -520,30 +570,46 @@ static bool use_pdl() {
   return v != 0;
 }
 
+static int env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return (e && *e) ? atoi(e) : dflt;
+}
+
+// Debug aid: when set (kdnn_b200_debug_set_trace), every warp of the streaming kernel
+// writes kTraceSlots globaltimer stamps per launch into this device buffer.
+static unsigned long long* g_trace_buffer = nullptr;
+void gemv_set_trace(void* buf) { g_trace_buffer = static_cast<unsigned long long*>(buf); }
+
 template <uint32_t DT, int RW, class XT, class YT>
 static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   const DeviceInfo& di = device_info();
   GemvParams p         = base;
-  p.ngroups            = (p.rows + RW - 1) / RW;
   p.stage_bytes        = (RW * chunk_bytes_full<DT>() + 127) & ~127;
+  // slab height: rows spread evenly over the SMs, rounded up to whole groups
+  int rpc = (p.rows + di.sms - 1) / di.sms;
+  rpc     = (rpc + RW - 1) / RW * RW;
+  p.rows_per_cta = rpc;
+  const int grid = (p.rows + rpc - 1) / rpc;
+  // partial-sum table: at most 16 KB of shared memory
+  int tile = rpc;
+  const int tile_cap = max(RW, (4096 / p.nchunks) / RW * RW);
+  if (tile > tile_cap) tile = tile_cap;
+  p.tile_rows = tile;
   const size_t act     = ((static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80)) + 127) & ~size_t(127);
-  // warps per CTA: enough that every SM gets work, capped by shared memory
-  int nwarps = (p.ngroups + di.sms - 1) / di.sms;
-  nwarps     = nwarps < 1 ? 1 : (nwarps > 16 ? 16 : nwarps);
-  const int work_per_warp = ((p.ngroups + di.sms * nwarps - 1) / (di.sms * nwarps)) * p.nchunks;
-  int stages = work_per_warp < 4 ? (work_per_warp < 2 ? 2 : work_per_warp) : 4;
-  auto smem_need = [&](int nw, int st) {
-    return act + ((static_cast<size_t>(nw) * 64 + 127) & ~size_t(127)) +
-           static_cast<size_t>(nw) * st * p.stage_bytes + 128;
+  const size_t table   = (static_cast<size_t>(tile) * p.nchunks * sizeof(float) + 127) & ~size_t(127);
+  auto smem_need = [&](int st) {
+    return act + kGemvWarps * 64 + table + static_cast<size_t>(kGemvWarps) * st * p.stage_bytes + 128;
   };
-  const size_t budget = static_cast<size_t>(di.max_smem) - 1024;
-  while (smem_need(nwarps, stages) > budget && stages > 2) --stages;
-  while (smem_need(nwarps, stages) > budget && nwarps > 1) --nwarps;
-  if (smem_need(nwarps, stages) > budget) return cudaErrorInvalidConfiguration;
-  p.stages       = stages;
-  p.stream_warps = nwarps;
-  const int grid = min(di.sms, (p.ngroups + nwarps - 1) / nwarps);
-  const size_t smem = smem_need(nwarps, stages);
+  // Two stages per warp keep about one bandwidth-delay product in flight per SM;
+  // deeper rings measured slower (they queue ahead of the activation loads).
+  int stages = env_int("KDNN_GEMV_STAGES", 2);
+  stages     = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
+  const size_t budget = static_cast<size_t>(di.max_smem);
+  while (stages > 2 && smem_need(stages) > budget) --stages;
+  if (smem_need(stages) > budget) return cudaErrorInvalidConfiguration;
+  p.stages = stages;
+  p.trace  = g_trace_buffer;
+  const size_t smem = smem_need(stages);
   auto kern = gemv_stream_kernel<DT, RW, XT, YT>;
   static thread_local size_t configured = 0;
   if (smem > configured) {
@@ -554,7 +620,7 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim            = dim3(grid);
-  cfg.blockDim           = dim3((nwarps < 8 ? 8 : nwarps) * 32);
+  cfg.blockDim           = dim3(kGemvWarps * 32);
   cfg.dynamicSmemBytes   = smem;
   cfg.stream             = stream;
   cudaLaunchAttribute attr[1];
@@ -567,11 +633,10 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
 
 template <uint32_t DT, class XT, class YT>
 static cudaError_t launch_stream_rw(const GemvParams& p, cudaStream_t stream) {
-  const DeviceInfo& di = device_info();
-  // RW = 4 halves the activation-side shared-memory traffic again, but needs
-  // enough row groups to occupy every SM with several warps.
-  if (p.rows >= di.sms * 4 * 4) return launch_stream<DT, 4, XT, YT>(p, stream);
-  if (p.rows >= di.sms * 2) return launch_stream<DT, 2, XT, YT>(p, stream);
+  // Rows per unit: 2 halves the activation-side shared-memory reads per weight byte
+  // but makes units coarser; 1 measured fastest at every benchmark shape.
+  const int rw = env_int("KDNN_GEMV_RW", 1);
+  if (rw >= 2) return launch_stream<DT, 2, XT, YT>(p, stream);
   return launch_stream<DT, 1, XT, YT>(p, stream);
 }
 

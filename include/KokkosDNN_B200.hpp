@@ -1,0 +1,215 @@
+// C++ layer that keeps the reference library's operator signatures
+// (Kokkos::View in and out, QuantWeight / QuantWeightTable, DNNHandle, exceptions
+// for bad arguments, `false` for a declined fast path) on top of the C ABI in
+// kdnn_b200.h.
+//
+// Every template below is duck-typed on the view / weight classes: it needs only
+// `data()`, `extent(i)`, `stride(i)` from views and the public fields of
+// Gguf::QuantWeight (`data`, `dtype`, `rows`, `cols`) and Gguf::QuantWeightTable
+// (`base`, `dtype`, `rows`, `cols`, `row_bytes`, `size()`), so the same header
+// compiles inside the reference library (real Kokkos, ExecSpace = Kokkos::Cuda)
+// and against a test stand-in. Paths in comments are relative to the reference
+// project root.
+//
+// Stream: the reference launches on the default instance of ExecSpace. Pass that
+// instance's stream (Kokkos::Cuda().cuda_stream()) through `StreamOf`, or rely on
+// the default (the legacy default stream, which is what a default-constructed
+// Kokkos::Cuda uses unless Kokkos was initialised with its own stream).
+#ifndef KOKKOSDNN_B200_HPP
+#define KOKKOSDNN_B200_HPP
+
+#include <climits>
+#include <cstddef>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <type_traits>
+
+#include "kdnn_b200.h"
+
+namespace KokkosDNN {
+namespace B200 {
+
+// Scalar -> C ABI tag. float and any 2-byte type (Kokkos::Experimental::bhalf_t on
+// a CUDA build is __nv_bfloat16) are accepted; everything else declines.
+template <class Scalar>
+constexpr int scalar_tag() {
+  return std::is_same<Scalar, float>::value ? KDNN_F32 : (sizeof(Scalar) == 2 ? KDNN_BF16 : -1);
+}
+
+// Where the launches go. Specialise / overload for your execution space; the
+// default is the legacy default stream.
+template <class ExecSpace>
+struct StreamOf {
+  static void* get(const ExecSpace&) { return nullptr; }
+};
+#if defined(KOKKOS_ENABLE_CUDA)
+template <>
+struct StreamOf<Kokkos::Cuda> {
+  static void* get(const Kokkos::Cuda& e) { return static_cast<void*>(e.cuda_stream()); }
+};
+#endif
+
+inline void throw_on_error(int rc, const char* what) {
+  if (rc == KDNN_ERR_INVALID) throw std::invalid_argument(kdnn_b200_last_error());
+  if (rc < 0) throw std::runtime_error(std::string(what) + ": " + kdnn_b200_last_error());
+}
+
+// Gguf::quant_gemv_int8_scratch_bytes, src/KokkosDNN_GGUF.hpp:2496-2499
+inline std::size_t quant_gemv_int8_scratch_bytes(std::size_t K) {
+  return kdnn_b200_gemv_scratch_bytes(K);
+}
+
+// Gguf::quant_gemv_int8_supported, src/KokkosDNN_GGUF.hpp:2522-2529
+template <class ExecSpace, class Scalar, class GgmlType>
+inline bool quant_gemv_int8_supported(GgmlType dtype, std::size_t K) {
+  return scalar_tag<Scalar>() >= 0 &&
+         kdnn_b200_gemv_supported(static_cast<uint32_t>(dtype), K, scalar_tag<Scalar>()) != 0;
+}
+
+// Impl::GgufMvq::launch_quant_gemv_int8, src/KokkosDNN_GGUFGemvInt8.hpp:711-777.
+// Same contract: returns false (nothing launched) when the fast path does not cover
+// the call, so the caller keeps its portable kernel; never throws for a decline.
+template <class ExecSpace, class XView, class YView>
+bool launch_quant_gemv_int8(const ExecSpace& space, const XView& x, const std::uint8_t* wdata,
+                            std::uint32_t ggml_type, std::size_t rows, std::size_t cols,
+                            const YView& y, std::uint8_t* scratch, std::size_t scratch_bytes) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(x.data())>::type>::type;
+  if (scalar_tag<Scalar>() < 0) return false;
+  if (x.stride(0) != 1 || y.stride(0) != 1) return false;  // :730
+  const int rc = kdnn_b200_quant_gemv(ggml_type, wdata, rows, cols, x.data(), scalar_tag<Scalar>(),
+                                      y.data(), scalar_tag<Scalar>(), scratch, scratch_bytes,
+                                      StreamOf<ExecSpace>::get(space));
+  throw_on_error(rc, "quant_gemv");
+  return rc == KDNN_OK;
+}
+
+// Gguf::quant_gemv(handle, x, w, y, act_scratch, label), src/KokkosDNN_GGUF.hpp:2531-2551.
+// `fallback` is what the reference runs when the int8 path declines (its
+// quant_gemv(handle, x, w, y, label)); it is called with no arguments.
+template <class ExecSpace, class XView, class QuantWeight, class YView, class SView, class Fallback>
+void quant_gemv(const ExecSpace& space, const XView& x, const QuantWeight& w, const YView& y,
+                const SView& act_scratch, Fallback&& fallback) {
+  if (x.extent(0) != w.cols || y.extent(0) != w.rows)
+    throw std::invalid_argument("quant_gemv: dimension mismatch");  // :2538-2539
+  if (w.rows == 0 || w.cols == 0) return;                          // :2541
+  const std::size_t need = quant_gemv_int8_scratch_bytes(w.cols);
+  if (need > 0 && act_scratch.extent(0) >= need &&
+      launch_quant_gemv_int8(space, x, w.data.data(), static_cast<std::uint32_t>(w.dtype), w.rows,
+                             w.cols, y, act_scratch.data(), act_scratch.extent(0)))
+    return;
+  fallback();
+}
+
+// Gguf::quant_gemm, src/KokkosDNN_GGUF.hpp:2564-2593 (int8 activations per row).
+// `workspace` is a caller-owned byte view of at least kdnn_b200_gemm_workspace_bytes(M, K).
+template <class ExecSpace, class XView, class QuantWeight, class YView, class WsView, class Fallback>
+void quant_gemm(const ExecSpace& space, const XView& X, const QuantWeight& w, const YView& Y,
+                const WsView& workspace, Fallback&& fallback) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(X.data())>::type>::type;
+  const std::size_t M = X.extent(0), K = X.extent(1), N = w.rows;
+  if (w.cols != K || Y.extent(0) != M || Y.extent(1) != N)
+    throw std::invalid_argument("quant_gemm: dimension mismatch");
+  if (M == 0 || N == 0 || K == 0) return;
+  if (M * N > static_cast<std::size_t>(INT_MAX)) throw std::invalid_argument("quant_gemm: M*N too large");
+  int rc = KDNN_DECLINED;
+  if (scalar_tag<Scalar>() >= 0 && X.stride(1) == 1 && Y.stride(1) == 1)
+    rc = kdnn_b200_quant_gemm(static_cast<std::uint32_t>(w.dtype), w.data.data(), N, K, X.data(),
+                              X.stride(0), M, scalar_tag<Scalar>(), Y.data(), Y.stride(0),
+                              scalar_tag<Scalar>(), workspace.data(), workspace.extent(0),
+                              StreamOf<ExecSpace>::get(space));
+  throw_on_error(rc, "quant_gemm");
+  if (rc == KDNN_DECLINED) fallback();
+}
+
+// KokkosDNN::moe_route / moe_route_sigmoid, src/KokkosDNN_MoE.hpp:240-304.
+template <class ExecSpace, class LView, class BView, class IView, class WView>
+void moe_route(const ExecSpace& space, const LView& logits, const BView& expert_bias, int top_k,
+               bool norm_topk, float routed_scale, const IView& top_idx, const WView& top_w,
+               bool sigmoid = false) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(logits.data())>::type>::type;
+  const char* name    = sigmoid ? "moe_route_sigmoid" : "moe_route";
+  const std::size_t T = logits.extent(0), E = logits.extent(1);
+  const std::size_t K = top_k < 0 ? 0 : static_cast<std::size_t>(top_k);
+  const bool have_bias = expert_bias.extent(0) != 0;
+  if (have_bias && expert_bias.extent(0) != E)
+    throw std::invalid_argument(std::string(name) + ": expert_bias extent must be E");
+  if (top_idx.extent(0) != T || top_idx.extent(1) != K || top_w.extent(0) != T || top_w.extent(1) != K)
+    throw std::invalid_argument(std::string(name) + ": output dimension mismatch");
+  if (T == 0) return;
+  if (top_k <= 0 || K > E) throw std::invalid_argument(std::string(name) + ": need 1 <= top_k <= E");
+  static_assert(sizeof(Scalar) == 4 || sizeof(Scalar) == 2, "Scalar must be float or a 2-byte bfloat16");
+  throw_on_error(kdnn_b200_moe_route(logits.data(), logits.stride(0), T, E, scalar_tag<Scalar>(),
+                                     have_bias ? expert_bias.data() : nullptr, top_k, norm_topk ? 1 : 0,
+                                     routed_scale, sigmoid ? 1 : 0, top_idx.data(), top_w.data(),
+                                     StreamOf<ExecSpace>::get(space)),
+                 name);
+}
+
+// Gguf::QuantWeightTable -> C struct (src/KokkosDNN_GGUF.hpp:2020-2029).
+template <class Table>
+kdnn_b200_weight_table table_of(const Table& t) {
+  kdnn_b200_weight_table c;
+  c.base      = reinterpret_cast<const uintptr_t*>(t.base.data());
+  c.ggml_type = static_cast<std::uint32_t>(t.dtype);
+  c.rows      = t.rows;
+  c.cols      = t.cols;
+  c.row_bytes = t.row_bytes;
+  c.n_experts = t.size();
+  return c;
+}
+
+// Gguf::quant_moe_decode, src/KokkosDNN_GGUF.hpp:2335-2391, with the int8 activation
+// numerics of the GEMV. Same argument checks and messages. `workspace`: caller-owned
+// bytes, at least kdnn_b200_moe_workspace_bytes(1, S, K, MI, n_experts), 256-byte aligned.
+template <class ExecSpace, class XView, class Table, class IView, class WView, class AView, class YView,
+          class WsView>
+void quant_moe_decode(const ExecSpace& space, const XView& X, const Table& gate, const Table& up,
+                      const Table& down, const IView& idx, const WView& wts, const AView& act,
+                      const YView& Y, const WsView& workspace) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(X.data())>::type>::type;
+  if (X.extent(0) != 1 || Y.extent(0) != 1) throw std::invalid_argument("quant_moe_decode: expected one row");
+  const std::size_t K = X.extent(1), MI = gate.rows;
+  const std::size_t S = idx.extent(0) == 0 ? 0 : idx.extent(1);
+  if (gate.cols != K || up.cols != K || up.rows != MI || down.rows != K || down.cols != MI ||
+      Y.extent(1) != K)
+    throw std::invalid_argument("quant_moe_decode: dimension mismatch");
+  if (gate.size() == 0 || gate.size() != up.size() || gate.size() != down.size())
+    throw std::invalid_argument("quant_moe_decode: expert table mismatch");
+  if (idx.extent(0) != 1 || wts.extent(0) != 1 || wts.extent(1) != S)
+    throw std::invalid_argument("quant_moe_decode: routing dimension mismatch");
+  if (act.extent(0) < S || (S > 0 && act.extent(1) != MI))
+    throw std::invalid_argument("quant_moe_decode: act scratch too small");
+  if (S == 0 || K == 0 || MI == 0) return;
+  const kdnn_b200_weight_table g = table_of(gate), u = table_of(up), d = table_of(down);
+  throw_on_error(kdnn_b200_moe_ffn(X.data(), X.stride(0), 1, scalar_tag<Scalar>(), &g, &u, &d, idx.data(),
+                                   wts.data(), S, Y.data(), Y.stride(0), scalar_tag<Scalar>(), 0,
+                                   gate.size(), workspace.data(), workspace.extent(0),
+                                   StreamOf<ExecSpace>::get(space)),
+                 "quant_moe_decode");
+}
+
+// Batched form (T tokens): the device-side replacement of LFM2.5's
+// moe_forward_sparse loop, models/lfm2_5/KokkosDNN_LFM25Model.hpp:441-547.
+template <class ExecSpace, class XView, class Table, class IView, class WView, class YView, class WsView>
+void moe_ffn(const ExecSpace& space, const XView& X, const Table& gate, const Table& up, const Table& down,
+             const IView& idx, const WView& wts, const YView& Y, const WsView& workspace,
+             std::size_t expert_first = 0, std::size_t expert_count = static_cast<std::size_t>(-1)) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(X.data())>::type>::type;
+  const std::size_t T = X.extent(0), S = idx.extent(0) == 0 ? 0 : idx.extent(1);
+  if (Y.extent(0) != T || Y.extent(1) != X.extent(1)) throw std::invalid_argument("moe_ffn: dimension mismatch");
+  if (idx.extent(0) != T || wts.extent(0) != T || wts.extent(1) != S)
+    throw std::invalid_argument("moe_ffn: routing dimension mismatch");
+  const kdnn_b200_weight_table g = table_of(gate), u = table_of(up), d = table_of(down);
+  if (expert_count == static_cast<std::size_t>(-1)) expert_count = gate.size() - expert_first;
+  throw_on_error(kdnn_b200_moe_ffn(X.data(), X.stride(0), T, scalar_tag<Scalar>(), &g, &u, &d, idx.data(),
+                                   wts.data(), S, Y.data(), Y.stride(0), scalar_tag<Scalar>(), expert_first,
+                                   expert_count, workspace.data(), workspace.extent(0),
+                                   StreamOf<ExecSpace>::get(space)),
+                 "moe_ffn");
+}
+
+}  // namespace B200
+}  // namespace KokkosDNN
+
+#endif  // KOKKOSDNN_B200_HPP

@@ -56,6 +56,12 @@ const char* kdnn_b200_last_error(void);
  * Synchronizes the device. */
 int kdnn_b200_device_status(void);
 
+/* Debug aid: with a device buffer of 2 * SMs * 8 warps * 8 uint64 set, every warp of the
+ * streaming GEMV kernel records eight globaltimer stamps (entry, prefetch issued,
+ * dependency resolved, activations staged, first stage landed, first refill, -, exit)
+ * of the most recent launch. NULL switches it off. No counterpart in the reference. */
+void kdnn_b200_debug_set_trace(void* device_buffer);
+
 /* ---- GEMV -------------------------------------------------------------- */
 
 /* Bytes of activation staging for a K-element row; 0 when K % 32 != 0.
