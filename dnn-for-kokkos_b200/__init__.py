@@ -37,6 +37,7 @@ EXPORTS = [
     "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quantize_act_q8",
     "kdnn_b200_unit_dots", "kdnn_b200_gemm_workspace_bytes", "kdnn_b200_quant_gemm",
     "kdnn_b200_moe_route", "kdnn_b200_moe_workspace_bytes", "kdnn_b200_moe_ffn",
+    "kdnn_b200_residual_rmsnorm",
 ]
 
 
@@ -83,6 +84,8 @@ def _load() -> C.CDLL:
                                       C.POINTER(WeightTableC), C.c_void_p, C.c_void_p, C.c_size_t,
                                       C.c_void_p, C.c_size_t, C.c_int, C.c_size_t, C.c_size_t,
                                       C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_residual_rmsnorm.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p,
+                                               C.c_size_t, C.c_size_t, C.c_size_t, C.c_float, C.c_int, C.c_void_p]
     return lib
 
 
@@ -323,3 +326,13 @@ def quant_moe_decode(X: torch.Tensor, gate: QuantWeightTable, up: QuantWeightTab
     if S == 0 or K == 0 or MI == 0:
         return
     moe_ffn(X, gate, up, down, idx, wts, Y, workspace)
+
+
+def residual_rmsnorm(h: torch.Tensor, y: torch.Tensor, out: torch.Tensor, eps: float = 1e-6) -> None:
+    """out = Scalar(rmsnorm_noscale(Scalar(h + y))) (see kdnn_b200_residual_rmsnorm)."""
+    T, H = h.shape
+    if tuple(y.shape) != (T, H) or tuple(out.shape) != (T, H) or y.dtype != torch.float32 or out.dtype != h.dtype:
+        raise ValueError("residual_rmsnorm: dimension or dtype mismatch")
+    rc = lib.kdnn_b200_residual_rmsnorm(h.data_ptr(), h.stride(0), y.data_ptr(), y.stride(0), out.data_ptr(),
+                                        out.stride(0), T, H, float(eps), _scalar(h), _stream())
+    _check(rc, "residual_rmsnorm")

@@ -30,6 +30,8 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
                            size_t S, void* Y, size_t ldy, int ys, size_t e_first, size_t e_count,
                            void* ws, cudaStream_t st);
 int moe_take_status();
+cudaError_t residual_rmsnorm_launch(const void* h, size_t ldh, const float* y, size_t ldy, void* out,
+                                    size_t ldo, size_t T, size_t H, float eps, int scalar, cudaStream_t st);
 }  // namespace kdnn
 
 namespace {
@@ -203,6 +205,17 @@ int kdnn_b200_moe_ffn(const void* X, size_t ldx, size_t T, int x_scalar,
                                           y_scalar, expert_first, expert_count, workspace,
                                           static_cast<cudaStream_t>(stream)),
                      "moe_ffn");
+}
+
+int kdnn_b200_residual_rmsnorm(const void* h, size_t ldh, const float* y, size_t ldy, void* out, size_t ldo,
+                               size_t T, size_t H, float eps, int scalar, void* stream) {
+  if (!scalar_ok(scalar)) return fail(KDNN_ERR_INVALID, "residual_rmsnorm: bad scalar");
+  if (T == 0 || H == 0) return KDNN_OK;
+  if (!h || !y || !out || ldh < H || ldy < H || ldo < H || T > INT_MAX || H > INT_MAX)
+    return fail(KDNN_ERR_INVALID, "residual_rmsnorm: bad argument");
+  return cuda_result(kdnn::residual_rmsnorm_launch(h, ldh, y, ldy, out, ldo, T, H, eps, scalar,
+                                                   static_cast<cudaStream_t>(stream)),
+                     "residual_rmsnorm");
 }
 
 }  // extern "C"

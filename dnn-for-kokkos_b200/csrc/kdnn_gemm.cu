@@ -2,13 +2,18 @@
 // int8 activations: the grouped kernel of kdnn_grouped.cuh with one group that
 // holds all M activation rows. Row m of Y equals the decode GEMV applied to row m.
 #include "kdnn_grouped.cuh"
+#include "kdnn_mma.cuh"
 
 namespace kdnn {
+
+bool tile_mma_enabled();
+int* moe_status_ptr();
 
 // workspace: [offs: 2 ints | pad to 256][wptr: 1 address | pad to 256][list: M ints][items: M x K/64]
 static size_t gemm_items_offset(size_t M) { return 512 + ((M * sizeof(int) + 255) & ~size_t(255)); }
 size_t gemm_workspace_bytes(size_t M, size_t K) {
-  return gemm_items_offset(M) + M * (K / 64) * sizeof(ActItem);
+  const size_t a = M * (K / 64) * sizeof(ActItem), b = M * act_row_pitch(K);
+  return gemm_items_offset(M) + (a > b ? a : b);
 }
 
 __global__ void gemm_setup_kernel(int M, uintptr_t w, int* offs, uintptr_t* wptr, int* list) {
@@ -31,6 +36,18 @@ cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const vo
                                                                  offs, wptr, list);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
+  if (dt == KDNN_GGML_Q4_K && tile_mma_enabled() && (reinterpret_cast<uintptr_t>(w) & 15u) == 0) {
+    uint8_t* xrows = b + gemm_items_offset(M);
+    err = xs == KDNN_F32
+              ? launch_quantize_rows<float>(static_cast<const float*>(X), ldx, (int)M, (int)K, nullptr, xrows, act_row_pitch(K), st)
+              : launch_quantize_rows<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(X), ldx, (int)M, (int)K, nullptr, xrows, act_row_pitch(K), st);
+    if (err != cudaSuccess) return err;
+    MmaParams q{};
+    q.w0 = wptr; q.row_bytes = (int)row_bytes_of(dt, K);
+    q.N = (int)N; q.K = (int)K; q.offs = offs; q.list = list; q.S = 1; q.g_first = 0;
+    q.xrows = xrows; q.x_pitch = act_row_pitch(K); q.dst = Y; q.ld_dst = ldy; q.status = moe_status_ptr();
+    return ys == KDNN_F32 ? launch_grouped_mma<2, float>(q, 1, st) : launch_grouped_mma<2, __nv_bfloat16>(q, 1, st);
+  }
   ActItem* items = reinterpret_cast<ActItem*>(b + gemm_items_offset(M));
   err = xs == KDNN_F32
             ? launch_quantize_items<float>(dt, static_cast<const float*>(X), ldx, (int)M, (int)K, nullptr, items, st)

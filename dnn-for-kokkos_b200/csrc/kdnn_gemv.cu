@@ -247,10 +247,12 @@ __device__ __forceinline__ float item_dot<KDNN_GGML_Q8_0>(uint32_t rowp, int il,
 }
 
 // ---- the streaming kernel --------------------------------------------------------
-// Each CTA owns a contiguous slab of rows. Its work units are (row group, chunk)
-// pairs -- RW consecutive rows x one 2048-element chunk -- dealt round-robin to the
-// CTA's warps, so a slab of R rows x C chunks keeps all warps busy even when R is
-// small. Every warp streams its units through a private ring of shared-memory
+// CTA b owns row groups b, b + gridDim, b + 2*gridDim, ... (RW consecutive rows per
+// group), so at any moment the CTAs work on neighbouring rows and the whole GPU
+// sweeps the matrix in address order (148 separate row slabs measured 4x slower:
+// every DRAM page was opened by one stream only). A CTA's work units are (group,
+// chunk) pairs dealt round-robin to its warps, so even a few groups x a few chunks
+// keep all warps busy. Every warp streams its units through a private ring of shared-memory
 // stages (bulk copies, mbarrier completion), reduces a unit over its lanes and
 // parks the partial row sums in shared memory; at the end the CTA adds each row's
 // chunk partials in chunk order (a fixed order: results do not depend on timing).
@@ -263,8 +265,8 @@ struct GemvParams {
   int row_bytes;
   int nitems;         // K / 64
   int nchunks;        // ceil(nitems / 32)
-  int rows_per_cta;   // slab height, a multiple of RW
-  int tile_rows;      // rows whose partials fit the shared-memory table, a multiple of RW
+  int ngroups;        // ceil(rows / RW)
+  int tile_groups;    // groups whose partials fit the shared-memory table
   int stages;         // ring depth per warp
   int stage_bytes;    // RW * chunk_bytes_full, rounded up to 128
   unsigned long long* trace;  // optional timeline buffer (debug aid), else null
@@ -296,23 +298,25 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const G
   off           = (off + 127) & ~size_t(127);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off) + warp * 8;   // <= 8 stages per warp
   off += kGemvWarps * 64;
-  float* partial = reinterpret_cast<float*>(smem + off);                 // [tile_rows][nchunks]
-  off += (static_cast<size_t>(p.tile_rows) * p.nchunks * sizeof(float) + 127) & ~size_t(127);
+  float* partial = reinterpret_cast<float*>(smem + off);                 // [tile units][RW][32 lanes]
+  off += static_cast<size_t>(p.tile_groups) * p.nchunks * RW * 32 * sizeof(float);
   uint8_t* ring = smem + off + static_cast<size_t>(warp) * p.stages * p.stage_bytes;
   const uint32_t ring_u32 = smem_u32(ring), bar_u32 = smem_u32(bars);
   KDNN_TRACE(0);
 
-  const int slab0 = blockIdx.x * p.rows_per_cta;
-  const int slab1 = min(p.rows, slab0 + p.rows_per_cta);
+  // local group i of this CTA is global group blockIdx.x + i * gridDim.x
+  const int my_groups = (p.ngroups - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                        static_cast<int>(gridDim.x);
   YT* y = static_cast<YT*>(p.y);
 
-  // Units of the tile that starts at row t0: u -> (group u / nchunks, chunk u % nchunks);
-  // warp w takes u = w, w + 16, ... Consecutive warps read consecutive chunks of a row.
+  // Units of the tile that starts at local group t0: u -> (group t0 + u / nchunks,
+  // chunk u % nchunks); warp w takes u = w, w + 16, ... so consecutive warps read
+  // consecutive chunks of a row.
   int issued = 0;  // lane 0: stages issued so far in the whole kernel (ring position)
-  auto issue_unit = [&](int t0, int t1, int u) {  // lane 0 only
+  auto issue_unit = [&](int t0, int u) {  // lane 0 only
     const int grp  = u / p.nchunks, ch = u - grp * p.nchunks;
-    const int row0 = t0 + grp * RW;
-    const int nrow = min(RW, t1 - row0);
+    const int row0 = (static_cast<int>(blockIdx.x) + (t0 + grp) * static_cast<int>(gridDim.x)) * RW;
+    const int nrow = min(RW, p.rows - row0);
     const int items   = min(kChunkItems, p.nitems - ch * kChunkItems);
     const uint32_t cb = chunk_bytes<DT>(items);
     const int s = issued % p.stages;
@@ -337,15 +341,14 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const G
 
   bool staged = false;
   int consumed = 0;  // stages consumed so far by this warp (ring position / parity)
-  for (int t0 = slab0; t0 < slab1; t0 += p.tile_rows) {
-    const int t1      = min(slab1, t0 + p.tile_rows);
-    const int ngroups = (t1 - t0 + RW - 1) / RW;
-    const int nunits  = ngroups * p.nchunks;
+  for (int t0 = 0; t0 < my_groups; t0 += p.tile_groups) {
+    const int tg     = min(p.tile_groups, my_groups - t0);
+    const int nunits = tg * p.nchunks;
     // Weights do not depend on the previous kernel in the stream: the first
     // `stages` units are requested before the dependency is resolved.
     int next_u = warp;
     if (lane == 0)
-      for (int i = 0; i < p.stages && next_u < nunits; ++i, next_u += kGemvWarps) issue_unit(t0, t1, next_u);
+      for (int i = 0; i < p.stages && next_u < nunits; ++i, next_u += kGemvWarps) issue_unit(t0, next_u);
     if (!staged) {
       KDNN_TRACE(1);
       pdl_launch_dependents();
@@ -359,45 +362,47 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const G
     }
     for (int u = warp; u < nunits; u += kGemvWarps) {
       const int s = consumed % p.stages;
+      // everything that does not depend on the weight bytes goes before the wait
+      const int grp = u / p.nchunks, ch = u - grp * p.nchunks;
+      const int item = ch * kChunkItems + lane;
+      const bool live = item < p.nitems;
+      ItemX x;
+      if (live) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) x.g[g] = xg[static_cast<size_t>(g) * p.nitems + item];
+        x.hd = hd[item];
+        if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
+      }
       if (!mbar_wait_bounded(bar_u32 + s * 8, (consumed / p.stages) & 1)) {
         if (lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
         return;
       }
       if (consumed == 0) KDNN_TRACE(4);
       ++consumed;
-      const int grp = u / p.nchunks, ch = u - grp * p.nchunks;
-      const int item = ch * kChunkItems + lane;
-      float acc[RW];
-#pragma unroll
-      for (int r = 0; r < RW; ++r) acc[r] = 0.f;
-      if (item < p.nitems) {
-        ItemX x;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) x.g[g] = xg[static_cast<size_t>(g) * p.nitems + item];
-        x.hd = hd[item];
-        if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
-        const uint32_t st = ring_u32 + s * p.stage_bytes;
-#pragma unroll
-        for (int r = 0; r < RW; ++r) acc[r] = item_dot<DT>(st + r * chunk_bytes_full<DT>(), lane, x);
-      }
+      const uint32_t st = ring_u32 + s * p.stage_bytes;
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
-        const float v = warp_sum(acc[r]);
-        if (lane == 0) partial[(grp * RW + r) * p.nchunks + ch] = v;
+        const float v = live ? item_dot<DT>(st + r * chunk_bytes_full<DT>(), lane, x) : 0.f;
+        partial[(u * RW + r) * 32 + lane] = v;   // per-lane partials: no shuffles in the streaming loop
       }
       __syncwarp();  // every lane has read this stage: it can be refilled
       if (lane == 0) {
         next_u = u + p.stages * kGemvWarps;
-        if (next_u < nunits) issue_unit(t0, t1, next_u);
+        if (next_u < nunits) issue_unit(t0, next_u);
       }
     }
     __syncthreads();
-    for (int r = threadIdx.x; r < t1 - t0; r += blockDim.x) {
+    // one warp per row: lane l adds its column of the row's chunk partials in chunk
+    // order, then a single shuffle reduction; a fixed order, independent of timing
+    for (int i = warp; i < tg * RW; i += kGemvWarps) {
+      const int gl = i / RW, r = i - gl * RW;
       float sum = 0.f;
-      for (int c = 0; c < p.nchunks; ++c) sum += partial[r * p.nchunks + c];
-      store_scalar(y + t0 + r, sum);
+      for (int c = 0; c < p.nchunks; ++c) sum += partial[((gl * p.nchunks + c) * RW + r) * 32 + lane];
+      sum = warp_sum(sum);
+      const int row = (static_cast<int>(blockIdx.x) + (t0 + gl) * static_cast<int>(gridDim.x)) * RW + r;
+      if (lane == 0 && row < p.rows) store_scalar(y + row, sum);
     }
-    if (t1 < slab1) __syncthreads();  // the table is reused by the next tile
+    if (t0 + tg < my_groups) __syncthreads();  // the table is reused by the next tile
   }
   if (!staged) {  // a CTA with an empty slab still takes part in the dependency chain
     pdl_launch_dependents();
@@ -585,18 +590,15 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   const DeviceInfo& di = device_info();
   GemvParams p         = base;
   p.stage_bytes        = (RW * chunk_bytes_full<DT>() + 127) & ~127;
-  // slab height: rows spread evenly over the SMs, rounded up to whole groups
-  int rpc = (p.rows + di.sms - 1) / di.sms;
-  rpc     = (rpc + RW - 1) / RW * RW;
-  p.rows_per_cta = rpc;
-  const int grid = (p.rows + rpc - 1) / rpc;
-  // partial-sum table: at most 16 KB of shared memory
-  int tile = rpc;
-  const int tile_cap = max(RW, (4096 / p.nchunks) / RW * RW);
+  p.ngroups      = (p.rows + RW - 1) / RW;
+  const int grid = min(di.sms, p.ngroups);
+  // per-lane partial table (128 B per unit and row): at most 48 KB of shared memory
+  int tile = (p.ngroups + grid - 1) / grid;
+  const int tile_cap = max(1, 384 / (p.nchunks * RW));
   if (tile > tile_cap) tile = tile_cap;
-  p.tile_rows = tile;
+  p.tile_groups = tile;
   const size_t act     = ((static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80)) + 127) & ~size_t(127);
-  const size_t table   = (static_cast<size_t>(tile) * p.nchunks * sizeof(float) + 127) & ~size_t(127);
+  const size_t table   = static_cast<size_t>(tile) * p.nchunks * RW * 32 * sizeof(float);
   auto smem_need = [&](int st) {
     return act + kGemvWarps * 64 + table + static_cast<size_t>(kGemvWarps) * st * p.stage_bytes + 128;
   };

@@ -13,10 +13,18 @@
 //   6. moe_combine_kernel   Y[t, d] = Scalar(sum_s w[t,s] * out[pos(t,s), d])
 // Workspace (caller-owned): offsets, slot list, slot positions, int8 items, act, out.
 #include "kdnn_grouped.cuh"
+#include "kdnn_mma.cuh"
+
+#include <stdlib.h>
 
 namespace kdnn {
 
 __device__ int g_moe_status = 0;
+int* moe_status_ptr() {
+  int* p = nullptr;
+  cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_moe_status);
+  return p;
+}
 
 // ---- router ----------------------------------------------------------------------
 // One warp per token; the E scores live in shared memory (src/KokkosDNN_MoE.hpp:
@@ -195,6 +203,16 @@ __global__ void moe_combine_kernel(const float* __restrict__ out, const int* __r
 struct MoeWs {
   size_t offs, list, pos, xq, act, actq, out, total;
 };
+static size_t max_sz(size_t a, size_t b) { return a > b ? a : b; }
+// KDNN_TILE=dp4a keeps the CUDA-core grouped kernel for every format (A/B aid).
+bool tile_mma_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("KDNN_TILE");
+    v             = (e && e[0] == 'd') ? 0 : 1;
+  }
+  return v != 0;
+}
 static MoeWs moe_ws_layout(size_t T, size_t S, size_t H, size_t F, size_t n_experts) {
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
   MoeWs w{};
@@ -202,9 +220,9 @@ static MoeWs moe_ws_layout(size_t T, size_t S, size_t H, size_t F, size_t n_expe
   w.offs = o; o += up((n_experts + 1) * sizeof(int));
   w.list = o; o += up(T * S * sizeof(int));
   w.pos  = o; o += up(T * S * sizeof(int));
-  w.xq   = o; o += up(T * (H / 64) * sizeof(ActItem));
+  w.xq   = o; o += up(T * max_sz((H / 64) * sizeof(ActItem), act_row_pitch(H)));
   w.act  = o; o += up(T * S * F * sizeof(float));
-  w.actq = o; o += up(T * S * (F / 64) * sizeof(ActItem));
+  w.actq = o; o += up(T * S * max_sz((F / 64) * sizeof(ActItem), act_row_pitch(F)));
   w.out  = o; o += up(T * S * H * sizeof(float));
   w.total = o;
   return w;
@@ -234,7 +252,32 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
                                                                      (int)e_count, offs, list, pos);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  if (e_count > 0) {
+  const bool all_q4k = gate->ggml_type == KDNN_GGML_Q4_K && down->ggml_type == KDNN_GGML_Q4_K &&
+                       (reinterpret_cast<uintptr_t>(ws) & 15u) == 0;
+  if (e_count > 0 && all_q4k && tile_mma_enabled()) {
+    // tensor-core tile path: quantized rows in the reference staging layout
+    uint8_t* xrows = b + L.xq;
+    uint8_t* arows = b + L.actq;
+    err = xs == KDNN_F32
+              ? launch_quantize_rows<float>(static_cast<const float*>(X), ldx, (int)T, (int)H, nullptr, xrows, act_row_pitch(H), st)
+              : launch_quantize_rows<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(X), ldx, (int)T, (int)H, nullptr, xrows, act_row_pitch(H), st);
+    if (err != cudaSuccess) return err;
+    MmaParams g{};
+    g.w0 = gate->base; g.w1 = up->base; g.row_bytes = (int)gate->row_bytes;
+    g.N = (int)F; g.K = (int)H; g.offs = offs; g.list = list; g.S = (int)S; g.g_first = (int)e_first;
+    g.xrows = xrows; g.x_pitch = act_row_pitch(H); g.dst = act; g.ld_dst = F;
+    g.round_bf16 = xs == KDNN_BF16; g.status = moe_status_ptr();
+    err = launch_grouped_mma<1, float>(g, (int)e_count, st);
+    if (err != cudaSuccess) return err;
+    err = launch_quantize_rows<float>(act, F, n_slots, (int)F, offs + e_count, arows, act_row_pitch(F), st);
+    if (err != cudaSuccess) return err;
+    MmaParams d{};
+    d.w0 = down->base; d.w1 = nullptr; d.row_bytes = (int)down->row_bytes;
+    d.N = (int)H; d.K = (int)F; d.offs = offs; d.list = list; d.S = (int)S; d.g_first = (int)e_first;
+    d.xrows = arows; d.x_pitch = act_row_pitch(F); d.dst = out; d.ld_dst = H; d.status = moe_status_ptr();
+    err = launch_grouped_mma<0, float>(d, (int)e_count, st);
+    if (err != cudaSuccess) return err;
+  } else if (e_count > 0) {
     err = xs == KDNN_F32
               ? launch_quantize_items<float>(gate->ggml_type, static_cast<const float*>(X), ldx, (int)T, (int)H, nullptr, xq, st)
               : launch_quantize_items<__nv_bfloat16>(gate->ggml_type, static_cast<const __nv_bfloat16*>(X), ldx, (int)T, (int)H, nullptr, xq, st);
@@ -266,6 +309,49 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
   else
     moe_combine_kernel<__nv_bfloat16><<<cgrid, 256, 0, st>>>(out, pos, wts, (int)T, (int)S, (int)H,
                                                              static_cast<__nv_bfloat16*>(Y), ldy);
+  return cudaGetLastError();
+}
+
+// out[t,:] = Scalar(r / sqrt(mean(r^2) + eps)) with r = Scalar(float(h[t,:]) + y[t,:]): the residual
+// add after the MoE block (models/lfm2_5/KokkosDNN_LFM25Model.hpp:812-816) fused with the next block's
+// un-scaled RMS norm (src/KokkosDNN_RMSNorm.hpp:347-361). One CTA per row, fp32 statistics.
+template <class ST>
+__global__ void residual_rmsnorm_kernel(const ST* __restrict__ h, size_t ldh, const float* __restrict__ y,
+                                        size_t ldy, ST* __restrict__ out, size_t ldo, int H, float eps) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < H; d += blockDim.x) {
+    ST r;
+    store_scalar(&r, to_f32(h[static_cast<size_t>(t) * ldh + d]) + y[static_cast<size_t>(t) * ldy + d]);
+    const float v = to_f32(r);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) red[0] = 1.0f / sqrtf(v / static_cast<float>(H) + eps);
+  }
+  __syncthreads();
+  const float inv = red[0];
+  for (int d = threadIdx.x; d < H; d += blockDim.x) {
+    ST r;
+    store_scalar(&r, to_f32(h[static_cast<size_t>(t) * ldh + d]) + y[static_cast<size_t>(t) * ldy + d]);
+    store_scalar(out + static_cast<size_t>(t) * ldo + d, to_f32(r) * inv);
+  }
+}
+
+cudaError_t residual_rmsnorm_launch(const void* h, size_t ldh, const float* y, size_t ldy, void* out,
+                                    size_t ldo, size_t T, size_t H, float eps, int scalar, cudaStream_t st) {
+  if (scalar == KDNN_F32)
+    residual_rmsnorm_kernel<float><<<(unsigned)T, 256, 0, st>>>(static_cast<const float*>(h), ldh, y, ldy,
+                                                                static_cast<float*>(out), ldo, (int)H, eps);
+  else
+    residual_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)T, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(h), ldh, y, ldy, static_cast<__nv_bfloat16*>(out), ldo, (int)H, eps);
   return cudaGetLastError();
 }
 

@@ -163,6 +163,14 @@ int kdnn_b200_moe_ffn(const void* X, size_t ldx, size_t T, int x_scalar,
                       size_t expert_first, size_t expert_count,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/* out[t,:] = Scalar(r / sqrt(mean(r^2) + eps)), r = Scalar(float(h[t,:]) + y[t,:]): the residual add that
+ * follows the MoE block (models/lfm2_5/KokkosDNN_LFM25Model.hpp:812-816) fused with the next block's
+ * un-scaled RMS norm, KokkosDNN::rmsnorm_noscale, src/KokkosDNN_RMSNorm.hpp:347-361.
+ *   h, out [T, H] Scalar (pitches ldh, ldo); y [T, H] float (pitch ldy), e.g. the fp32 output of
+ *   kdnn_b200_moe_ffn. */
+int kdnn_b200_residual_rmsnorm(const void* h, size_t ldh, const float* y, size_t ldy, void* out, size_t ldo,
+                               size_t T, size_t H, float eps, int scalar, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
