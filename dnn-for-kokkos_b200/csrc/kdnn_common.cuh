@@ -83,6 +83,22 @@ __device__ __forceinline__ int dot16(const uint32_t (&w)[4], const int4& x, int 
   return acc;
 }
 
+// dp4a with unsigned bytes on the weight side: lets the high nibbles of a packed Q4_K
+// word be used in place (w & 0xF0F0F0F0 = 16 * nibble, bytes up to 240), the exact
+// factor 16 is removed from the int32 sum afterwards.
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dot16_us(const uint32_t (&w)[4], const int4& x, int acc) {
+  acc = dp4a_us(w[0], x.x, acc);
+  acc = dp4a_us(w[1], x.y, acc);
+  acc = dp4a_us(w[2], x.z, acc);
+  acc = dp4a_us(w[3], x.w, acc);
+  return acc;
+}
+
 // ---- per-32 int8 activation quantizer ---------------------------------------
 // Eight lanes cooperate on one 32-element block (four elements each). Returns
 // this lane's four quantized values packed into one word; d / part sums come

@@ -3,10 +3,12 @@
 // holds all M activation rows. Row m of Y equals the decode GEMV applied to row m.
 #include "kdnn_grouped.cuh"
 #include "kdnn_mma.cuh"
+#include "kdnn_umma.cuh"
 
 namespace kdnn {
 
 bool tile_mma_enabled();
+int tile_kind();
 int* moe_status_ptr();
 
 // workspace: [offs: 2 ints | pad to 256][wptr: 1 address | pad to 256][list: M ints][items: M x K/64]
@@ -46,6 +48,8 @@ cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const vo
     q.w0 = wptr; q.row_bytes = (int)row_bytes_of(dt, K);
     q.N = (int)N; q.K = (int)K; q.offs = offs; q.list = list; q.S = 1; q.g_first = 0;
     q.xrows = xrows; q.x_pitch = act_row_pitch(K); q.dst = Y; q.ld_dst = ldy; q.status = moe_status_ptr();
+    if (tile_kind() == 2)
+      return ys == KDNN_F32 ? launch_grouped_umma<2, float>(q, 1, st) : launch_grouped_umma<2, __nv_bfloat16>(q, 1, st);
     return ys == KDNN_F32 ? launch_grouped_mma<2, float>(q, 1, st) : launch_grouped_mma<2, __nv_bfloat16>(q, 1, st);
   }
   ActItem* items = reinterpret_cast<ActItem*>(b + gemm_items_offset(M));

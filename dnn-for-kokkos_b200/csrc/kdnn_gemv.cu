@@ -177,13 +177,13 @@ __device__ __forceinline__ float item_dot<KDNN_GGML_Q4_K>(uint32_t rowp, int il,
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     lo0[i] = q[i] & 0x0F0F0F0Fu;
-    hi0[i] = (q[i] >> 4) & 0x0F0F0F0Fu;
+    hi0[i] = q[i] & 0xF0F0F0F0u;      // 16 * high nibble, used as unsigned bytes
     lo1[i] = q[4 + i] & 0x0F0F0F0Fu;
-    hi1[i] = (q[4 + i] >> 4) & 0x0F0F0F0Fu;
+    hi1[i] = q[4 + i] & 0xF0F0F0F0u;
   }
   // low nibbles <-> elements 0..31 of the item (granules 0,1), high <-> 32..63 (2,3)
   const int dotA = dot16(lo1, x.g[1], dot16(lo0, x.g[0], 0));
-  const int dotB = dot16(hi1, x.g[3], dot16(hi0, x.g[2], 0));
+  const int dotB = dot16_us(hi1, x.g[3], dot16_us(hi0, x.g[2], 0)) >> 4;  // exact: the sum is a multiple of 16
   const int sc0 = scp & 0xFF, sc1 = scp >> 8, mn0 = mnp & 0xFF, mn1 = mnp >> 8;
   const float p = static_cast<float>(sc0 * dotA) * x.hd.x + static_cast<float>(sc1 * dotB) * x.hd.y;
   const float m = static_cast<float>(mn0) * x.hd.z + static_cast<float>(mn1) * x.hd.w;
@@ -267,6 +267,7 @@ struct GemvParams {
   int nchunks;        // ceil(nitems / 32)
   int ngroups;        // ceil(rows / RW)
   int tile_groups;    // groups whose partials fit the shared-memory table
+  int stage_shift;    // log2(stages)
   int stages;         // ring depth per warp
   int stage_bytes;    // RW * chunk_bytes_full, rounded up to 128
   unsigned long long* trace;  // optional timeline buffer (debug aid), else null
@@ -309,28 +310,16 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const G
                         static_cast<int>(gridDim.x);
   YT* y = static_cast<YT*>(p.y);
 
-  // Units of the tile that starts at local group t0: u -> (group t0 + u / nchunks,
-  // chunk u % nchunks); warp w takes u = w, w + 16, ... so consecutive warps read
-  // consecutive chunks of a row.
-  int issued = 0;  // lane 0: stages issued so far in the whole kernel (ring position)
-  auto issue_unit = [&](int t0, int u) {  // lane 0 only
-    const int grp  = u / p.nchunks, ch = u - grp * p.nchunks;
-    const int row0 = (static_cast<int>(blockIdx.x) + (t0 + grp) * static_cast<int>(gridDim.x)) * RW;
-    const int nrow = min(RW, p.rows - row0);
-    const int items   = min(kChunkItems, p.nitems - ch * kChunkItems);
-    const uint32_t cb = chunk_bytes<DT>(items);
-    const int s = issued % p.stages;
-    ++issued;
-    const uint32_t bar = bar_u32 + s * 8;
-    mbar_expect_tx(bar, cb * nrow);
-    const uint8_t* src = p.w + static_cast<size_t>(row0) * p.row_bytes +
-                         static_cast<size_t>(ch) * chunk_bytes_full<DT>();
-    const uint32_t dst = ring_u32 + s * p.stage_bytes;
-#pragma unroll
-    for (int r = 0; r < RW; ++r)
-      if (r < nrow)
-        bulk_g2s(dst + r * chunk_bytes_full<DT>(), src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
-  };
+  // Units of a tile: u -> (local group u / nchunks, chunk u % nchunks); warp w takes
+  // u = w, w + 16, ... (consecutive warps read consecutive chunks of a row). Both the
+  // consuming side and the issuing side (lane 0, `stages` units ahead) walk that
+  // sequence with incremental cursors: no division in the streaming loop.
+  const int dq = kGemvWarps / p.nchunks, dr = kGemvWarps % p.nchunks;   // one step of 16 units
+  const size_t group_pitch = static_cast<size_t>(gridDim.x) * RW * p.row_bytes;  // bytes between my groups
+  const uint32_t cb_full = chunk_bytes_full<DT>();
+  const uint32_t cb_last = chunk_bytes<DT>(p.nitems - (p.nchunks - 1) * kChunkItems);
+  const uint32_t smask = static_cast<uint32_t>(p.stages - 1);            // stages is a power of two
+  const int sshift = p.stage_shift;
 
   if (lane == 0) {
     for (int s = 0; s < p.stages; ++s) mbar_init(bar_u32 + s * 8, 1);
@@ -340,15 +329,42 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const G
   __syncwarp();
 
   bool staged = false;
-  int consumed = 0;  // stages consumed so far by this warp (ring position / parity)
+  uint32_t consumed = 0, issued = 0;  // ring positions (issued: lane 0 only)
   for (int t0 = 0; t0 < my_groups; t0 += p.tile_groups) {
     const int tg     = min(p.tile_groups, my_groups - t0);
     const int nunits = tg * p.nchunks;
+    // issue cursor (lane 0): unit iu = (ig, ic), source pointer of group ig
+    int iu = warp, ig = warp / p.nchunks, ic = warp - ig * p.nchunks;
+    const uint8_t* isrc = p.w + (static_cast<size_t>(blockIdx.x) * RW * p.row_bytes) +
+                          static_cast<size_t>(t0 + ig) * group_pitch;
+    auto issue_next = [&]() {  // lane 0 only; issues unit iu (if any) and advances the cursor
+      if (iu >= nunits) return;
+      const int row0 = (static_cast<int>(blockIdx.x) + (t0 + ig) * static_cast<int>(gridDim.x)) * RW;
+      const int nrow = min(RW, p.rows - row0);
+      const uint32_t cb  = ic == p.nchunks - 1 ? cb_last : cb_full;
+      const uint32_t s   = issued & smask;
+      ++issued;
+      const uint32_t bar = bar_u32 + s * 8;
+      mbar_expect_tx(bar, cb * nrow);
+      const uint8_t* src = isrc + static_cast<size_t>(ic) * cb_full;
+      const uint32_t dst = ring_u32 + s * p.stage_bytes;
+#pragma unroll
+      for (int r = 0; r < RW; ++r)
+        if (r < nrow) bulk_g2s(dst + r * cb_full, src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
+      iu += kGemvWarps;
+      ic += dr;
+      int adv = dq;
+      if (ic >= p.nchunks) {
+        ic -= p.nchunks;
+        ++adv;
+      }
+      ig += adv;
+      isrc += static_cast<size_t>(adv) * group_pitch;
+    };
     // Weights do not depend on the previous kernel in the stream: the first
     // `stages` units are requested before the dependency is resolved.
-    int next_u = warp;
     if (lane == 0)
-      for (int i = 0; i < p.stages && next_u < nunits; ++i, next_u += kGemvWarps) issue_unit(t0, next_u);
+      for (int i = 0; i < p.stages; ++i) issue_next();
     if (!staged) {
       KDNN_TRACE(1);
       pdl_launch_dependents();
@@ -360,11 +376,11 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const G
       KDNN_TRACE(3);
       staged = true;
     }
+    int cg = warp / p.nchunks, cc = warp - cg * p.nchunks;  // consume cursor
     for (int u = warp; u < nunits; u += kGemvWarps) {
-      const int s = consumed % p.stages;
+      const uint32_t s = consumed & smask;
       // everything that does not depend on the weight bytes goes before the wait
-      const int grp = u / p.nchunks, ch = u - grp * p.nchunks;
-      const int item = ch * kChunkItems + lane;
+      const int item  = cc * kChunkItems + lane;
       const bool live = item < p.nitems;
       ItemX x;
       if (live) {
@@ -373,7 +389,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const G
         x.hd = hd[item];
         if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
       }
-      if (!mbar_wait_bounded(bar_u32 + s * 8, (consumed / p.stages) & 1)) {
+      if (!mbar_wait_bounded(bar_u32 + s * 8, (consumed >> sshift) & 1u)) {
         if (lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
         return;
       }
@@ -382,13 +398,16 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const G
       const uint32_t st = ring_u32 + s * p.stage_bytes;
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
-        const float v = live ? item_dot<DT>(st + r * chunk_bytes_full<DT>(), lane, x) : 0.f;
-        partial[(u * RW + r) * 32 + lane] = v;   // per-lane partials: no shuffles in the streaming loop
+        const float v = live ? item_dot<DT>(st + r * cb_full, lane, x) : 0.f;
+        partial[((cg * p.nchunks + cc) * RW + r) * 32 + lane] = v;   // per-lane partials, reduced at the end
       }
       __syncwarp();  // every lane has read this stage: it can be refilled
-      if (lane == 0) {
-        next_u = u + p.stages * kGemvWarps;
-        if (next_u < nunits) issue_unit(t0, next_u);
+      if (lane == 0) issue_next();
+      cc += dr;
+      cg += dq;
+      if (cc >= p.nchunks) {
+        cc -= p.nchunks;
+        ++cg;
       }
     }
     __syncthreads();
@@ -605,12 +624,13 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   // Two stages per warp keep about one bandwidth-delay product in flight per SM;
   // deeper rings measured slower (they queue ahead of the activation loads).
   int stages = env_int("KDNN_GEMV_STAGES", 2);
-  stages     = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
+  stages     = stages >= 8 ? 8 : (stages >= 4 ? 4 : 2);   // a power of two (ring positions by mask)
   const size_t budget = static_cast<size_t>(di.max_smem);
-  while (stages > 2 && smem_need(stages) > budget) --stages;
+  while (stages > 2 && smem_need(stages) > budget) stages >>= 1;
   if (smem_need(stages) > budget) return cudaErrorInvalidConfiguration;
-  p.stages = stages;
-  p.trace  = g_trace_buffer;
+  p.stages      = stages;
+  p.stage_shift = stages == 2 ? 1 : (stages == 4 ? 2 : 3);
+  p.trace       = g_trace_buffer;
   const size_t smem = smem_need(stages);
   auto kern = gemv_stream_kernel<DT, RW, XT, YT>;
   static thread_local size_t configured = 0;

@@ -14,6 +14,7 @@
 // Workspace (caller-owned): offsets, slot list, slot positions, int8 items, act, out.
 #include "kdnn_grouped.cuh"
 #include "kdnn_mma.cuh"
+#include "kdnn_umma.cuh"
 
 #include <stdlib.h>
 
@@ -204,15 +205,17 @@ struct MoeWs {
   size_t offs, list, pos, xq, act, actq, out, total;
 };
 static size_t max_sz(size_t a, size_t b) { return a > b ? a : b; }
-// KDNN_TILE=dp4a keeps the CUDA-core grouped kernel for every format (A/B aid).
-bool tile_mma_enabled() {
+// KDNN_TILE selects the Q4_K tile kernel: "mma" (mma.sync, default), "umma" (tcgen05 + TMEM),
+// "dp4a" (CUDA-core grouped kernel, which also serves every other format).
+int tile_kind() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("KDNN_TILE");
-    v             = (e && e[0] == 'd') ? 0 : 1;
+    v             = !e ? 1 : (e[0] == 'd' ? 0 : (e[0] == 'u' ? 2 : 1));
   }
-  return v != 0;
+  return v;
 }
+bool tile_mma_enabled() { return tile_kind() != 0; }
 static MoeWs moe_ws_layout(size_t T, size_t S, size_t H, size_t F, size_t n_experts) {
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
   MoeWs w{};
@@ -267,7 +270,8 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
     g.N = (int)F; g.K = (int)H; g.offs = offs; g.list = list; g.S = (int)S; g.g_first = (int)e_first;
     g.xrows = xrows; g.x_pitch = act_row_pitch(H); g.dst = act; g.ld_dst = F;
     g.round_bf16 = xs == KDNN_BF16; g.status = moe_status_ptr();
-    err = launch_grouped_mma<1, float>(g, (int)e_count, st);
+    err = tile_kind() == 2 ? launch_grouped_umma<1, float>(g, (int)e_count, st)
+                           : launch_grouped_mma<1, float>(g, (int)e_count, st);
     if (err != cudaSuccess) return err;
     err = launch_quantize_rows<float>(act, F, n_slots, (int)F, offs + e_count, arows, act_row_pitch(F), st);
     if (err != cudaSuccess) return err;
@@ -275,7 +279,8 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
     d.w0 = down->base; d.w1 = nullptr; d.row_bytes = (int)down->row_bytes;
     d.N = (int)H; d.K = (int)F; d.offs = offs; d.list = list; d.S = (int)S; d.g_first = (int)e_first;
     d.xrows = arows; d.x_pitch = act_row_pitch(F); d.dst = out; d.ld_dst = H; d.status = moe_status_ptr();
-    err = launch_grouped_mma<0, float>(d, (int)e_count, st);
+    err = tile_kind() == 2 ? launch_grouped_umma<0, float>(d, (int)e_count, st)
+                           : launch_grouped_mma<0, float>(d, (int)e_count, st);
     if (err != cudaSuccess) return err;
   } else if (e_count > 0) {
     err = xs == KDNN_F32
