@@ -8,13 +8,10 @@
 // folded into the prologue; CTA 0 also writes the reference's staging layout to
 // the caller's scratch), then consumes the weight stages with dp4a.
 //
-// Each warp is an independent streaming engine with its own ring of stages: it
-// owns row groups of RW consecutive rows, a stage holds RW row segments of one
-// 2048-element chunk, lane 0 refills a stage as soon as the warp has consumed
-// it. No cross-warp synchronisation after the prologue. Each lane handles one
-// 64-element item of the chunk for all RW rows, so the activation window and its
-// block scales are loaded from shared memory once per RW weight rows (the
-// cross-row reuse of the reference's row-blocked kernel, :525-599).
+// Each lane handles one 64-element item of a 2048-element chunk per row, so the
+// activation window and its block scales are loaded from shared memory once per
+// RW weight rows (the cross-row reuse of the reference's row-blocked kernel,
+// :525-599).
 //
 // HBM traffic per call: rows*row_bytes (each weight byte exactly once) +
 // K*sizeof(x) per CTA from L2 + rows*sizeof(y).
@@ -23,12 +20,13 @@
 #include <limits.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 namespace kdnn {
 
 __device__ int g_gemv_status = 0;
 
 constexpr int kChunkItems = 32;    // one item per lane
-constexpr int kChunkElems = 2048;  // 32 items x 64 elements
 
 template <uint32_t DT>
 __host__ __device__ constexpr int chunk_bytes_full() {
@@ -247,32 +245,6 @@ __device__ __forceinline__ float item_dot<KDNN_GGML_Q8_0>(uint32_t rowp, int il,
 }
 
 // ---- the streaming kernel --------------------------------------------------------
-// CTA b owns row groups b, b + gridDim, b + 2*gridDim, ... (RW consecutive rows per
-// group), so at any moment the CTAs work on neighbouring rows and the whole GPU
-// sweeps the matrix in address order (148 separate row slabs measured 4x slower:
-// every DRAM page was opened by one stream only). A CTA's work units are (group,
-// chunk) pairs dealt round-robin to its warps, so even a few groups x a few chunks
-// keep all warps busy. Every warp streams its units through a private ring of shared-memory
-// stages (bulk copies, mbarrier completion), reduces a unit over its lanes and
-// parks the partial row sums in shared memory; at the end the CTA adds each row's
-// chunk partials in chunk order (a fixed order: results do not depend on timing).
-struct GemvParams {
-  const uint8_t* w;
-  const void* x;
-  void* y;
-  uint8_t* scratch;   // reference-layout staging (written by CTA 0)
-  int rows, K;
-  int row_bytes;
-  int nitems;         // K / 64
-  int nchunks;        // ceil(nitems / 32)
-  int ngroups;        // ceil(rows / RW)
-  int tile_groups;    // groups whose partials fit the shared-memory table
-  int stage_shift;    // log2(stages)
-  int stages;         // ring depth per warp
-  int stage_bytes;    // RW * chunk_bytes_full, rounded up to 128
-  unsigned long long* trace;  // optional timeline buffer (debug aid), else null
-};
-
 constexpr int kGemvWarps  = 16;
 constexpr int kTraceSlots = 8;   // timestamps per warp when tracing
 
@@ -287,145 +259,134 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
       p.trace[(static_cast<size_t>(blockIdx.x) * kGemvWarps + warp) * kTraceSlots + (slot)] = globaltimer_ns(); \
   } while (0)
 
+// One 16-warp CTA per SM. Every warp is an independent streaming engine with a private
+// ring of shared-memory stages (bulk copies, mbarrier completion, bounded waits): it takes
+// whole row groups (RW rows, their 2048-element chunks in sequence), keeps the row sums in
+// registers and does one shuffle reduction per group. The first group of every warp is
+// fixed (gw = warp * gridDim + blockIdx, so the GPU sweeps the matrix in address order and
+// the weights can be requested before the previous kernel in the stream has finished);
+// the rest are handed out by a ticket counter, requested one group ahead so the atomic's
+// round trip is off the critical path and all warps finish within one group of each other.
+// The warp reconverges (__syncwarp) after lane 0 has refilled a stage and before anybody
+// waits on the next one.
+constexpr int kTicketSlots = 64;
+__device__ unsigned int g_gemv_tickets[kTicketSlots];
+
+struct GemvParams {
+  const uint8_t* w;
+  const void* x;
+  void* y;
+  uint8_t* scratch;
+  int rows, K, row_bytes, nitems, nchunks;
+  int ngroups, stages, stage_bytes, ticket_slot;
+  unsigned long long* trace;
+};
+
 template <uint32_t DT, int RW, class XT, class YT>
 __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // shared layout: [xg 4*nitems*16][hd nitems*16][hs nitems*16 (Q6_K)] [barriers] [partials] [rings]
   int4* xg      = reinterpret_cast<int4*>(smem);
   float4* hd    = reinterpret_cast<float4*>(smem + static_cast<size_t>(p.nitems) * 64);
   int4* hs      = reinterpret_cast<int4*>(smem + static_cast<size_t>(p.nitems) * 80);
   size_t off    = static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80);
   off           = (off + 127) & ~size_t(127);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off) + warp * 8;   // <= 8 stages per warp
-  off += kGemvWarps * 64;
-  float* partial = reinterpret_cast<float*>(smem + off);                 // [tile units][RW][32 lanes]
-  off += static_cast<size_t>(p.tile_groups) * p.nchunks * RW * 32 * sizeof(float);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off) + warp * 8;
+  int2* meta     = reinterpret_cast<int2*>(smem + off + kGemvWarps * 64) + warp * 8;   // {group, chunk} per stage
+  off += kGemvWarps * 128;
   uint8_t* ring = smem + off + static_cast<size_t>(warp) * p.stages * p.stage_bytes;
   const uint32_t ring_u32 = smem_u32(ring), bar_u32 = smem_u32(bars);
   KDNN_TRACE(0);
 
-  // local group i of this CTA is global group blockIdx.x + i * gridDim.x
-  const int my_groups = (p.ngroups - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                        static_cast<int>(gridDim.x);
-  YT* y = static_cast<YT*>(p.y);
-
-  // Units of a tile: u -> (local group u / nchunks, chunk u % nchunks); warp w takes
-  // u = w, w + 16, ... (consecutive warps read consecutive chunks of a row). Both the
-  // consuming side and the issuing side (lane 0, `stages` units ahead) walk that
-  // sequence with incremental cursors: no division in the streaming loop.
-  const int dq = kGemvWarps / p.nchunks, dr = kGemvWarps % p.nchunks;   // one step of 16 units
-  const size_t group_pitch = static_cast<size_t>(gridDim.x) * RW * p.row_bytes;  // bytes between my groups
-  const uint32_t cb_full = chunk_bytes_full<DT>();
-  const uint32_t cb_last = chunk_bytes<DT>(p.nitems - (p.nchunks - 1) * kChunkItems);
-  const uint32_t smask = static_cast<uint32_t>(p.stages - 1);            // stages is a power of two
-  const int sshift = p.stage_shift;
-
+  const int G  = gridDim.x * kGemvWarps;
+  const int gw = warp * gridDim.x + blockIdx.x;
+  int is_group = gw, is_chunk = 0, is_n = 0;
+  bool is_done = gw >= p.ngroups;
+  int is_next  = 0x7fffffff;
+  auto fetch_next = [&]() {
+    is_next = G + static_cast<int>(atomicAdd(&g_gemv_tickets[p.ticket_slot], 1u));
+  };
+  auto issue = [&]() {  // lane 0 only
+    const int s = is_n % p.stages;
+    ++is_n;
+    if (is_done) {
+      meta[s] = make_int2(-1, 0);
+      return;
+    }
+    meta[s] = make_int2(is_group, is_chunk);
+    const int items   = min(kChunkItems, p.nitems - is_chunk * kChunkItems);
+    const uint32_t cb = chunk_bytes<DT>(items);
+    const int row0 = is_group * RW;
+    const int nrow = min(RW, p.rows - row0);
+    const uint32_t bar = bar_u32 + s * 8;
+    mbar_expect_tx(bar, cb * nrow);
+    const uint8_t* src = p.w + static_cast<size_t>(row0) * p.row_bytes +
+                         static_cast<size_t>(is_chunk) * chunk_bytes_full<DT>();
+    const uint32_t dst = ring_u32 + s * p.stage_bytes;
+#pragma unroll
+    for (int r = 0; r < RW; ++r)
+      if (r < nrow)
+        bulk_g2s(dst + r * chunk_bytes_full<DT>(), src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
+    if (++is_chunk == p.nchunks) {
+      is_chunk = 0;
+      is_group = is_next;
+      if (is_group >= p.ngroups) is_done = true; else fetch_next();
+    }
+  };
   if (lane == 0) {
     for (int s = 0; s < p.stages; ++s) mbar_init(bar_u32 + s * 8, 1);
     fence_barrier_init();
     fence_proxy_async();
+    if (!is_done) fetch_next();
+    for (int s = 0; s < p.stages; ++s) issue();
   }
-  __syncwarp();
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    g_gemv_tickets[(p.ticket_slot + kTicketSlots / 2) % kTicketSlots] = 0;  // a slot not in use
+  KDNN_TRACE(1);
+  pdl_launch_dependents();
+  pdl_wait();
+  KDNN_TRACE(2);
+  stage_activations<DT, XT>(static_cast<const XT*>(p.x), p.K, p.nitems, xg, hd, hs,
+                            blockIdx.x == 0 ? p.scratch : nullptr);
+  __syncthreads();
+  KDNN_TRACE(3);
 
-  bool staged = false;
-  uint32_t consumed = 0, issued = 0;  // ring positions (issued: lane 0 only)
-  for (int t0 = 0; t0 < my_groups; t0 += p.tile_groups) {
-    const int tg     = min(p.tile_groups, my_groups - t0);
-    const int nunits = tg * p.nchunks;
-    // issue cursor (lane 0): unit iu = (ig, ic), source pointer of group ig
-    int iu = warp, ig = warp / p.nchunks, ic = warp - ig * p.nchunks;
-    const uint8_t* isrc = p.w + (static_cast<size_t>(blockIdx.x) * RW * p.row_bytes) +
-                          static_cast<size_t>(t0 + ig) * group_pitch;
-    auto issue_next = [&]() {  // lane 0 only; issues unit iu (if any) and advances the cursor
-      if (iu >= nunits) return;
-      const int row0 = (static_cast<int>(blockIdx.x) + (t0 + ig) * static_cast<int>(gridDim.x)) * RW;
-      const int nrow = min(RW, p.rows - row0);
-      const uint32_t cb  = ic == p.nchunks - 1 ? cb_last : cb_full;
-      const uint32_t s   = issued & smask;
-      ++issued;
-      const uint32_t bar = bar_u32 + s * 8;
-      mbar_expect_tx(bar, cb * nrow);
-      const uint8_t* src = isrc + static_cast<size_t>(ic) * cb_full;
-      const uint32_t dst = ring_u32 + s * p.stage_bytes;
+  float acc[RW];
 #pragma unroll
-      for (int r = 0; r < RW; ++r)
-        if (r < nrow) bulk_g2s(dst + r * cb_full, src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
-      iu += kGemvWarps;
-      ic += dr;
-      int adv = dq;
-      if (ic >= p.nchunks) {
-        ic -= p.nchunks;
-        ++adv;
-      }
-      ig += adv;
-      isrc += static_cast<size_t>(adv) * group_pitch;
-    };
-    // Weights do not depend on the previous kernel in the stream: the first
-    // `stages` units are requested before the dependency is resolved.
-    if (lane == 0)
-      for (int i = 0; i < p.stages; ++i) issue_next();
-    if (!staged) {
-      KDNN_TRACE(1);
-      pdl_launch_dependents();
-      pdl_wait();  // x may be the previous kernel's output
-      KDNN_TRACE(2);
-      stage_activations<DT, XT>(static_cast<const XT*>(p.x), p.K, p.nitems, xg, hd, hs,
-                                blockIdx.x == 0 ? p.scratch : nullptr);
-      __syncthreads();
-      KDNN_TRACE(3);
-      staged = true;
+  for (int r = 0; r < RW; ++r) acc[r] = 0.f;
+  YT* y = static_cast<YT*>(p.y);
+  for (int n = 0;; ++n) {
+    const int s  = n % p.stages;
+    const int2 m = meta[s];
+    if (m.x < 0) break;
+    if (!mbar_wait_bounded(bar_u32 + s * 8, (n / p.stages) & 1)) {
+      if (lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
+      return;
     }
-    int cg = warp / p.nchunks, cc = warp - cg * p.nchunks;  // consume cursor
-    for (int u = warp; u < nunits; u += kGemvWarps) {
-      const uint32_t s = consumed & smask;
-      // everything that does not depend on the weight bytes goes before the wait
-      const int item  = cc * kChunkItems + lane;
-      const bool live = item < p.nitems;
+    if (n == 0) KDNN_TRACE(4);
+    const int item = m.y * kChunkItems + lane;
+    if (item < p.nitems) {
       ItemX x;
-      if (live) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) x.g[g] = xg[static_cast<size_t>(g) * p.nitems + item];
-        x.hd = hd[item];
-        if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
-      }
-      if (!mbar_wait_bounded(bar_u32 + s * 8, (consumed >> sshift) & 1u)) {
-        if (lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
-        return;
-      }
-      if (consumed == 0) KDNN_TRACE(4);
-      ++consumed;
+      for (int g = 0; g < 4; ++g) x.g[g] = xg[static_cast<size_t>(g) * p.nitems + item];
+      x.hd = hd[item];
+      if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
       const uint32_t st = ring_u32 + s * p.stage_bytes;
 #pragma unroll
+      for (int r = 0; r < RW; ++r) acc[r] += item_dot<DT>(st + r * chunk_bytes_full<DT>(), lane, x);
+    }
+    if (m.y == p.nchunks - 1) {
+      const int row0 = m.x * RW;
+#pragma unroll
       for (int r = 0; r < RW; ++r) {
-        const float v = live ? item_dot<DT>(st + r * cb_full, lane, x) : 0.f;
-        partial[((cg * p.nchunks + cc) * RW + r) * 32 + lane] = v;   // per-lane partials, reduced at the end
-      }
-      __syncwarp();  // every lane has read this stage: it can be refilled
-      if (lane == 0) issue_next();
-      cc += dr;
-      cg += dq;
-      if (cc >= p.nchunks) {
-        cc -= p.nchunks;
-        ++cg;
+        const float v = warp_sum(acc[r]);
+        if (lane == 0 && row0 + r < p.rows) store_scalar(y + row0 + r, v);
+        acc[r] = 0.f;
       }
     }
-    __syncthreads();
-    // one warp per row: lane l adds its column of the row's chunk partials in chunk
-    // order, then a single shuffle reduction; a fixed order, independent of timing
-    for (int i = warp; i < tg * RW; i += kGemvWarps) {
-      const int gl = i / RW, r = i - gl * RW;
-      float sum = 0.f;
-      for (int c = 0; c < p.nchunks; ++c) sum += partial[((gl * p.nchunks + c) * RW + r) * 32 + lane];
-      sum = warp_sum(sum);
-      const int row = (static_cast<int>(blockIdx.x) + (t0 + gl) * static_cast<int>(gridDim.x)) * RW + r;
-      if (lane == 0 && row < p.rows) store_scalar(y + row, sum);
-    }
-    if (t0 + tg < my_groups) __syncthreads();  // the table is reused by the next tile
-  }
-  if (!staged) {  // a CTA with an empty slab still takes part in the dependency chain
-    pdl_launch_dependents();
-    pdl_wait();
+    __syncwarp();
+    if (lane == 0) issue();
+    __syncwarp();
   }
   KDNN_TRACE(6);
 }
@@ -604,60 +565,56 @@ static int env_int(const char* name, int dflt) {
 static unsigned long long* g_trace_buffer = nullptr;
 void gemv_set_trace(void* buf) { g_trace_buffer = static_cast<unsigned long long*>(buf); }
 
+static std::atomic<unsigned> g_launch_counter{0};
+
 template <uint32_t DT, int RW, class XT, class YT>
 static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   const DeviceInfo& di = device_info();
-  GemvParams p         = base;
-  p.stage_bytes        = (RW * chunk_bytes_full<DT>() + 127) & ~127;
-  p.ngroups      = (p.rows + RW - 1) / RW;
-  const int grid = min(di.sms, p.ngroups);
-  // per-lane partial table (128 B per unit and row): at most 48 KB of shared memory
-  int tile = (p.ngroups + grid - 1) / grid;
-  const int tile_cap = max(1, 384 / (p.nchunks * RW));
-  if (tile > tile_cap) tile = tile_cap;
-  p.tile_groups = tile;
-  const size_t act     = ((static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80)) + 127) & ~size_t(127);
-  const size_t table   = static_cast<size_t>(tile) * p.nchunks * RW * 32 * sizeof(float);
+  GemvParams p = base;
+  p.ngroups     = (p.rows + RW - 1) / RW;
+  p.stage_bytes = (RW * chunk_bytes_full<DT>() + 127) & ~127;
+  const size_t act = ((static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80)) + 127) & ~size_t(127);
   auto smem_need = [&](int st) {
-    return act + kGemvWarps * 64 + table + static_cast<size_t>(kGemvWarps) * st * p.stage_bytes + 128;
+    return act + kGemvWarps * 128 + static_cast<size_t>(kGemvWarps) * st * p.stage_bytes + 128;
   };
-  // Two stages per warp keep about one bandwidth-delay product in flight per SM;
-  // deeper rings measured slower (they queue ahead of the activation loads).
+  // Two stages per warp keep about one bandwidth-delay product in flight per SM; deeper
+  // rings measured slower (their requests queue ahead of the activation loads).
   int stages = env_int("KDNN_GEMV_STAGES", 2);
-  stages     = stages >= 8 ? 8 : (stages >= 4 ? 4 : 2);   // a power of two (ring positions by mask)
-  const size_t budget = static_cast<size_t>(di.max_smem);
-  while (stages > 2 && smem_need(stages) > budget) stages >>= 1;
-  if (smem_need(stages) > budget) return cudaErrorInvalidConfiguration;
+  stages     = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
+  while (stages > 2 && smem_need(stages) > static_cast<size_t>(di.max_smem)) --stages;
+  if (smem_need(stages) > static_cast<size_t>(di.max_smem)) return cudaErrorInvalidConfiguration;
   p.stages      = stages;
-  p.stage_shift = stages == 2 ? 1 : (stages == 4 ? 2 : 3);
+  p.ticket_slot = static_cast<int>(g_launch_counter.fetch_add(1) % kTicketSlots);
   p.trace       = g_trace_buffer;
+  const int grid = min(di.sms, (p.ngroups + kGemvWarps - 1) / kGemvWarps);
   const size_t smem = smem_need(stages);
   auto kern = gemv_stream_kernel<DT, RW, XT, YT>;
   static thread_local size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         di.max_smem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem);
     if (e != cudaSuccess) return e;
     configured = di.max_smem;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim            = dim3(grid);
-  cfg.blockDim           = dim3(kGemvWarps * 32);
-  cfg.dynamicSmemBytes   = smem;
-  cfg.stream             = stream;
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kGemvWarps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs                                          = attr;
-  cfg.numAttrs                                       = use_pdl() ? 1 : 0;
+  cfg.attrs = attr; cfg.numAttrs = use_pdl() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 template <uint32_t DT, class XT, class YT>
 static cudaError_t launch_stream_rw(const GemvParams& p, cudaStream_t stream) {
-  // Rows per unit: 2 halves the activation-side shared-memory reads per weight byte
-  // but makes units coarser; 1 measured fastest at every benchmark shape.
-  const int rw = env_int("KDNN_GEMV_RW", 1);
+  const DeviceInfo& di = device_info();
+  // Rows per group. One row per group gives the finest work units and measured fastest
+  // for tall matrices; when there are at most two rows per warp, two-row groups (one
+  // group per warp, shared activation window) win for the 144- and 34-byte formats.
+  int rw = env_int("KDNN_GEMV_RW", 0);
+  if (rw == 0) {
+    const int warps = di.sms * kGemvWarps;
+    rw = (DT != KDNN_GGML_Q6_K && p.rows > warps && p.rows <= 2 * warps) ? 2 : 1;
+  }
   if (rw >= 2) return launch_stream<DT, 2, XT, YT>(p, stream);
   return launch_stream<DT, 1, XT, YT>(p, stream);
 }
