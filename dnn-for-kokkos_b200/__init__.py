@@ -34,7 +34,8 @@ F32, BF16 = 0, 1
 # every symbol include/kdnn_b200.h declares (checked by the CPU test-suite)
 EXPORTS = [
     "kdnn_b200_last_error", "kdnn_b200_device_status", "kdnn_b200_debug_set_trace", "kdnn_b200_gemv_scratch_bytes",
-    "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quantize_act_q8",
+    "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quant_gemv_noalloc",
+    "kdnn_b200_quantize_act_q8",
     "kdnn_b200_unit_dots", "kdnn_b200_gemm_workspace_bytes", "kdnn_b200_quant_gemm",
     "kdnn_b200_moe_route", "kdnn_b200_moe_workspace_bytes", "kdnn_b200_moe_ffn",
     "kdnn_b200_residual_rmsnorm",
@@ -65,6 +66,8 @@ def _load() -> C.CDLL:
     lib.kdnn_b200_gemv_supported.argtypes = [C.c_uint32, C.c_size_t, C.c_int]
     lib.kdnn_b200_quant_gemv.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                          C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_quant_gemv_noalloc.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
+                                                 C.c_int, C.c_void_p, C.c_int, C.c_void_p]
     lib.kdnn_b200_quantize_act_q8.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t,
                                               C.c_void_p]
     lib.kdnn_b200_unit_dots.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
@@ -185,6 +188,25 @@ def quant_gemv(x: torch.Tensor, w: QuantWeight, y: torch.Tensor, act_scratch: to
                                   y.data_ptr(), _scalar(y), act_scratch.data_ptr(), act_scratch.numel(),
                                   _stream())
     _check(rc, "quant_gemv")
+
+
+NOALLOC_MAX_COLS = 32768
+
+
+def quant_gemv_noalloc(x: torch.Tensor, w: QuantWeight, y: torch.Tensor) -> None:
+    """quant_gemv without a caller-owned staging buffer: for hosts that may not allocate device memory
+    (see kdnn_b200_quant_gemv_noalloc). K is limited to NOALLOC_MAX_COLS; calls that overlap on the GPU
+    race on the shared built-in staging."""
+    if x.numel() != w.cols or y.numel() != w.rows:
+        raise ValueError("quant_gemv: dimension mismatch")
+    _quant_check(w, "quant_gemv")
+    if w.rows == 0 or w.cols == 0:
+        return
+    for t, n in ((x, "x"), (y, "y"), (w.data, "w")):
+        _cuda(t, n)
+    rc = lib.kdnn_b200_quant_gemv_noalloc(w.dtype, w.data.data_ptr(), w.rows, w.cols, x.data_ptr(), _scalar(x),
+                                          y.data_ptr(), _scalar(y), _stream())
+    _check(rc, "quant_gemv_noalloc")
 
 
 def quantize_act_q8(x: torch.Tensor, scratch: torch.Tensor) -> None:

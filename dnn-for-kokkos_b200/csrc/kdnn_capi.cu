@@ -36,6 +36,11 @@ cudaError_t residual_rmsnorm_launch(const void* h, size_t ldh, const float* y, s
 
 namespace {
 thread_local std::string g_last_error;
+}  // namespace
+namespace kdnn {
+void set_last_error(const char* msg) { g_last_error = msg; }
+}  // namespace kdnn
+namespace {
 
 int fail(int code, const std::string& msg) {
   g_last_error = msg;

@@ -21,6 +21,7 @@
 #include <stdlib.h>
 
 #include <atomic>
+#include <string>
 
 namespace kdnn {
 
@@ -716,4 +717,68 @@ int gemv_take_status() {
   return v;
 }
 
+// ---- allocation-free entry point --------------------------------------------------
+// Activation staging for callers that cannot hand us a scratch buffer: a fixed array in
+// device memory that every GPU loading this library carries until the process exits.
+// Host code must not pass the array's name to a kernel (on the host the name is only a
+// stand-in for the symbol); the device address is looked up once per device with
+// cudaGetSymbolAddress and cached.
+constexpr size_t kNoAllocMaxCols = 32768;                                  // largest K served
+constexpr size_t kNoAllocBytes   = kNoAllocMaxCols + kNoAllocMaxCols / 2;  // = act_bytes(32768) = 49152
+static __device__ __align__(256) uint8_t g_noalloc_staging[kNoAllocBytes];
+
+void set_last_error(const char* msg);  // kdnn_capi.cu
+
+static cudaError_t noalloc_staging_address(uint8_t** out) {
+  constexpr int kMaxDevices = 64;
+  static uint8_t* cache[kMaxDevices] = {};
+  static std::atomic<bool> ready[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_staging);  // resolved for the current device
+    if (e != cudaSuccess) return e;
+    cache[dev] = static_cast<uint8_t*>(p);
+    ready[dev].store(true, std::memory_order_release);
+  }
+  *out = cache[dev];
+  return cudaSuccess;
+}
+
 }  // namespace kdnn
+
+extern "C" int kdnn_b200_quant_gemv_noalloc(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                                            const void* x, int x_scalar, void* y, int y_scalar,
+                                            void* stream) {
+  using namespace kdnn;
+  if ((x_scalar != KDNN_F32 && x_scalar != KDNN_BF16) || (y_scalar != KDNN_F32 && y_scalar != KDNN_BF16)) {
+    set_last_error("quant_gemv_noalloc: scalar must be KDNN_F32 or KDNN_BF16");
+    return KDNN_ERR_INVALID;
+  }
+  if (cols > kNoAllocMaxCols) {
+    set_last_error("quant_gemv_noalloc: cols exceeds the built-in staging (32768 columns); "
+                   "use kdnn_b200_quant_gemv with a caller-owned scratch buffer");
+    return KDNN_ERR_INVALID;
+  }
+  // the same decline list as kdnn_b200_quant_gemv, minus the scratch checks
+  if (ggml_type != KDNN_GGML_Q4_K && ggml_type != KDNN_GGML_Q6_K && ggml_type != KDNN_GGML_Q8_0)
+    return KDNN_DECLINED;
+  if (w == nullptr || x == nullptr || y == nullptr) return KDNN_DECLINED;
+  if (!block_aligned(ggml_type, cols)) return KDNN_DECLINED;
+  if (rows == 0 || rows > static_cast<size_t>(INT_MAX)) return KDNN_DECLINED;
+  if ((reinterpret_cast<uintptr_t>(w) & 1u) != 0u) return KDNN_DECLINED;
+  if (ggml_type == KDNN_GGML_Q4_K && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u) return KDNN_DECLINED;
+  uint8_t* staging = nullptr;
+  cudaError_t e = noalloc_staging_address(&staging);
+  if (e == cudaSuccess)
+    e = gemv_launch(ggml_type, w, rows, cols, x, x_scalar, y, y_scalar, staging, 0,
+                    static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    set_last_error((std::string("quant_gemv_noalloc: ") + cudaGetErrorString(e)).c_str());
+    return KDNN_ERR_CUDA;
+  }
+  return KDNN_OK;
+}

@@ -90,6 +90,25 @@ int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t 
                          const void* x, int x_scalar, void* y, int y_scalar,
                          void* act_scratch, size_t act_scratch_bytes, void* stream);
 
+/* The same GEMV for callers that have no scratch buffer to give and may not create one: a
+ * host runtime that reserved the whole device up front and forbids cudaMalloc in its
+ * plug-ins, or a decode loop that is not allowed to touch the allocator because an
+ * allocation can stall every stream of the device. The activation staging lives in a
+ * fixed 48 KB array inside the library's device image instead (every GPU that loads the
+ * library holds it until the process exits), so the limit is cols <= 32768; larger K is
+ * rejected with KDNN_ERR_INVALID and a message that names the limit. The call allocates
+ * nothing (no cudaMalloc / cudaFree, no allocating library routine). Its first call on a
+ * device looks up the array's device address (with that device current) and caches it;
+ * make that first call outside any stream capture. All calls on a device share the one
+ * array: it keeps the previous call's staging (every byte the kernels read is rewritten
+ * first, nothing has to start at zero), and two calls that overlap on the GPU -- different
+ * streams, or concurrent host threads -- race on it; serialise them or use
+ * kdnn_b200_quant_gemv. Results are identical to kdnn_b200_quant_gemv.
+ * This entry point has no counterpart in the reference, whose operator always takes the
+ * caller's act_scratch view. */
+int kdnn_b200_quant_gemv_noalloc(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                                 const void* x, int x_scalar, void* y, int y_scalar, void* stream);
+
 /* Stage 1 alone: quantize one activation row into `scratch` (layout above).
  * Stands in for Impl::GgufMvq::QuantizeActQ8Functor, src/KokkosDNN_GGUFGemvInt8.hpp:198-239. */
 int kdnn_b200_quantize_act_q8(const void* x, int x_scalar, size_t K, void* scratch,
