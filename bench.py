@@ -327,7 +327,9 @@ def run_ours(args):
     roofline = {"kernel": "gemv_stream_kernel<Q4_K> 14336x4096", "bound": "hbm", "achieved": dom["achieved_GBps"],
                 "peak": peak, "peak_source": f"{peak_kind} HBM copy bandwidth (MEASURED_PEAKS.json)",
                 "unit": "GB/s", "frac": dom["frac"], "frac_of_nominal_8TBps": dom["achieved_GBps"] / 8000.0,
-                "traffic": None, "by_shape": per_kernel}
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+                # profiles/gemv_stream_q4k_14336x4096_ncu_full.md (algorithmic bytes: 33,095,680)
+                "traffic": 33074944, "by_shape": per_kernel}
 
     # ---- end to end through the public call with host buffers --------------------------
     def e2e_pass():
