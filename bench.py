@@ -251,10 +251,20 @@ def run_ours(args):
     with torch.cuda.stream(stream):
         one_pass()
         torch.cuda.synchronize()
+        ys_first = [y.clone() for y in ys]          # results of the plain launches (the GPU tests' path)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             one_pass()
     torch.cuda.synchronize()
+
+    def replay_is_complete(g, outs, firsts):
+        """Poison the outputs, replay once more, and require every row to be recomputed bit-for-bit."""
+        with torch.cuda.stream(stream):
+            for y in outs:
+                y.fill_(float("nan"))
+            g.replay()
+        torch.cuda.synchronize()
+        return all(torch.equal(y, f) for y, f in zip(outs, firsts))
 
     def barrier():
         if world > 1:
@@ -281,6 +291,8 @@ def run_ours(args):
                 for _ in range(int(1500 / max(ms_total / args.steps, 1e-3))):
                     graph.replay()
             torch.cuda.synchronize()
+    if not replay_is_complete(graph, ys, ys_first):
+        raise RuntimeError("a replayed step did not reproduce the results of the plain launches")
     t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -307,6 +319,7 @@ def run_ours(args):
             for w in copies:
                 kd.quant_gemv(x, w, y, sc)
             torch.cuda.synchronize()
+            y_first = y.clone()
             with torch.cuda.graph(gk, stream=stream):
                 for _ in range(reps):
                     for w in copies:
@@ -319,6 +332,8 @@ def run_ours(args):
                 gk.replay()
             b.record(stream)
         torch.cuda.synchronize()
+        if not replay_is_complete(gk, [y], [y_first]):
+            raise RuntimeError(f"replayed {name} GEMVs did not reproduce the results of the plain launches")
         us = a.elapsed_time(b) * 1e3 / (5 * reps * len(copies))
         ab = algorithmic_bytes(dt, rows, K)
         per_kernel[f"{name}_{rows}x{K}"] = {"us_per_launch": us, "algorithmic_bytes": ab,

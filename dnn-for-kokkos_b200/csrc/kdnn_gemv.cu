@@ -246,8 +246,9 @@ __device__ __forceinline__ float item_dot<KDNN_GGML_Q8_0>(uint32_t rowp, int il,
 }
 
 // ---- the streaming kernel --------------------------------------------------------
-constexpr int kGemvWarps  = 16;
-constexpr int kTraceSlots = 8;   // timestamps per warp when tracing
+constexpr int kGemvMaxWarps = 16;
+constexpr int kGemvStages   = 2;   // ring depth per warp: about one bandwidth-delay product per SM in flight
+constexpr int kTraceSlots   = 8;   // timestamps per warp when tracing
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
@@ -257,92 +258,164 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 #define KDNN_TRACE(slot)                                                                   \
   do {                                                                                     \
     if (p.trace && lane == 0)                                                              \
-      p.trace[(static_cast<size_t>(blockIdx.x) * kGemvWarps + warp) * kTraceSlots + (slot)] = globaltimer_ns(); \
+      p.trace[(static_cast<size_t>(blockIdx.x) * kGemvMaxWarps + warp) * kTraceSlots + (slot)] = globaltimer_ns(); \
   } while (0)
 
-// One 16-warp CTA per SM. Every warp is an independent streaming engine with a private
-// ring of shared-memory stages (bulk copies, mbarrier completion, bounded waits): it takes
-// whole row groups (RW rows, their 2048-element chunks in sequence), keeps the row sums in
-// registers and does one shuffle reduction per group. The first group of every warp is
-// fixed (gw = warp * gridDim + blockIdx, so the GPU sweeps the matrix in address order and
-// the weights can be requested before the previous kernel in the stream has finished);
-// the rest are handed out by a ticket counter, requested one group ahead so the atomic's
-// round trip is off the critical path and all warps finish within one group of each other.
-// The warp reconverges (__syncwarp) after lane 0 has refilled a stage and before anybody
-// waits on the next one.
-constexpr int kTicketSlots = 64;
-__device__ unsigned int g_gemv_tickets[kTicketSlots];
-
+// One CTA per SM, up to 16 warps. Every warp is an independent streaming engine with a
+// private two-stage ring in shared memory (bulk copies, mbarrier completion, bounded
+// waits); a stage holds one 2048-element chunk of RW consecutive weight rows.
+//
+// Work split. The row groups (RW rows) are divided evenly and contiguously over the CTAs,
+// so nothing is carried between launches and each CTA sweeps its slice in address order.
+// Inside a CTA the unit of work is (row group, range of `cpu` chunks): a warp accumulates
+// its unit in registers, reduces it across lanes once, and writes either y (the unit
+// covers the whole row) or a partial sum in shared memory that the CTA adds up, in chunk
+// order, at the end. The host picks `cpu` and the warp count so that every warp gets many
+// units and the last round is nearly full. The first unit of every warp is fixed, so its
+// weights are requested before the previous kernel in the stream has finished
+// (programmatic dependent launch); the rest come from a shared-memory counter, drawn one
+// unit ahead.
 struct GemvParams {
   const uint8_t* w;
   const void* x;
   void* y;
   uint8_t* scratch;
   int rows, K, row_bytes, nitems, nchunks;
-  int ngroups, stages, stage_bytes, ticket_slot;
+  int ngroups;         // ceil(rows / RW)
+  int cpu;             // chunks per unit
+  int upg;             // units per group = ceil(nchunks / cpu)
+  uint32_t upg_magic;  // ceil(2^32 / upg): u / upg == umulhi(u, magic) for the unit counts that occur
+  int part_floats;     // partial sums kept in shared memory (upg > 1)
+  int stage_bytes;
   unsigned long long* trace;
 };
 
+// Sum RW per-lane values across the warp. Afterwards lane l (l < RW) holds the total of
+// row rev(l) for RW = 4 -- see row_of_lane -- and of row l for RW <= 2.
+template <int RW>
+__device__ __forceinline__ float reduce_rows(const float (&a)[RW], int lane) {
+  constexpr unsigned full = 0xFFFFFFFFu;
+  float v;
+  if (RW == 4) {
+    const bool hi = lane & 1;
+    float k0 = hi ? a[2] : a[0], k1 = hi ? a[3] : a[1];
+    const float s0 = hi ? a[0] : a[2], s1 = hi ? a[1] : a[3];
+    k0 += __shfl_xor_sync(full, s0, 1);
+    k1 += __shfl_xor_sync(full, s1, 1);
+    const bool hi2 = lane & 2;
+    v = hi2 ? k1 : k0;
+    v += __shfl_xor_sync(full, hi2 ? k0 : k1, 2);
+    v += __shfl_xor_sync(full, v, 4);
+  } else if (RW == 2) {
+    const bool hi = lane & 1;
+    v = hi ? a[1] : a[0];
+    v += __shfl_xor_sync(full, hi ? a[0] : a[1], 1);
+    v += __shfl_xor_sync(full, v, 2);
+    v += __shfl_xor_sync(full, v, 4);
+  } else {
+    v = a[0];
+    v += __shfl_xor_sync(full, v, 1);
+    v += __shfl_xor_sync(full, v, 2);
+    v += __shfl_xor_sync(full, v, 4);
+  }
+  v += __shfl_xor_sync(full, v, 8);
+  v += __shfl_xor_sync(full, v, 16);
+  return v;
+}
+template <int RW>
+__device__ __forceinline__ int row_of_lane(int lane) {
+  return RW == 4 ? ((lane & 1) * 2 + ((lane >> 1) & 1)) : lane;
+}
+
 template <uint32_t DT, int RW, class XT, class YT>
-__global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_stream_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = blockDim.x >> 5;
   int4* xg      = reinterpret_cast<int4*>(smem);
   float4* hd    = reinterpret_cast<float4*>(smem + static_cast<size_t>(p.nitems) * 64);
   int4* hs      = reinterpret_cast<int4*>(smem + static_cast<size_t>(p.nitems) * 80);
   size_t off    = static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80);
   off           = (off + 127) & ~size_t(127);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off) + warp * 8;
-  int2* meta     = reinterpret_cast<int2*>(smem + off + kGemvWarps * 64) + warp * 8;   // {group, chunk} per stage
-  off += kGemvWarps * 128;
-  uint8_t* ring = smem + off + static_cast<size_t>(warp) * p.stages * p.stage_bytes;
-  const uint32_t ring_u32 = smem_u32(ring), bar_u32 = smem_u32(bars);
+  const uint32_t bar_u32 = smem_u32(smem + off) + warp * (kGemvStages * 8);
+  off += kGemvMaxWarps * kGemvStages * 8;
+  int& s_next_unit = *reinterpret_cast<int*>(smem + off);   // work counter of this CTA
+  off += 128;
+  float* part = reinterpret_cast<float*>(smem + off);        // [local row][unit of the row]
+  off += (static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127);
+  const uint32_t ring_u32 = smem_u32(smem + off) + warp * (kGemvStages * p.stage_bytes);
   KDNN_TRACE(0);
 
-  const int G  = gridDim.x * kGemvWarps;
-  const int gw = warp * gridDim.x + blockIdx.x;
-  int is_group = gw, is_chunk = 0, is_n = 0;
-  bool is_done = gw >= p.ngroups;
-  int is_next  = 0x7fffffff;
-  auto fetch_next = [&]() {
-    is_next = G + static_cast<int>(atomicAdd(&g_gemv_tickets[p.ticket_slot], 1u));
-  };
-  auto issue = [&]() {  // lane 0 only
-    const int s = is_n % p.stages;
-    ++is_n;
-    if (is_done) {
-      meta[s] = make_int2(-1, 0);
-      return;
-    }
-    meta[s] = make_int2(is_group, is_chunk);
-    const int items   = min(kChunkItems, p.nitems - is_chunk * kChunkItems);
-    const uint32_t cb = chunk_bytes<DT>(items);
-    const int row0 = is_group * RW;
-    const int nrow = min(RW, p.rows - row0);
-    const uint32_t bar = bar_u32 + s * 8;
-    mbar_expect_tx(bar, cb * nrow);
-    const uint8_t* src = p.w + static_cast<size_t>(row0) * p.row_bytes +
-                         static_cast<size_t>(is_chunk) * chunk_bytes_full<DT>();
-    const uint32_t dst = ring_u32 + s * p.stage_bytes;
-#pragma unroll
-    for (int r = 0; r < RW; ++r)
-      if (r < nrow)
-        bulk_g2s(dst + r * chunk_bytes_full<DT>(), src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
-    if (++is_chunk == p.nchunks) {
-      is_chunk = 0;
-      is_group = is_next;
-      if (is_group >= p.ngroups) is_done = true; else fetch_next();
-    }
-  };
+  // this CTA's slice of the row groups and its units
+  const int c0 = static_cast<int>(static_cast<long long>(blockIdx.x) * p.ngroups / gridDim.x);
+  const int c1 = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * p.ngroups / gridDim.x);
+  const int U  = (c1 - c0) * p.upg;
+  if (threadIdx.x == 0) s_next_unit = W;
   if (lane == 0) {
-    for (int s = 0; s < p.stages; ++s) mbar_init(bar_u32 + s * 8, 1);
+#pragma unroll
+    for (int s = 0; s < kGemvStages; ++s) mbar_init(bar_u32 + s * 8, 1);
     fence_barrier_init();
     fence_proxy_async();
-    if (!is_done) fetch_next();
-    for (int s = 0; s < p.stages; ++s) issue();
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0)
-    g_gemv_tickets[(p.ticket_slot + kTicketSlots / 2) % kTicketSlots] = 0;  // a slot not in use
+  __syncthreads();
+
+  // ---- producer state (uniform across the warp; lane 0 issues the copies) ----
+  int pu = warp, pnext = 0x7fffffff, pg = 0, pchunk0 = 0, pchunks = 1, pc = 0, pui = 0;
+  bool pdone = pu >= U;
+  auto decode = [&](int u) {
+    pg      = p.upg == 1 ? u : static_cast<int>(__umulhi(static_cast<uint32_t>(u), p.upg_magic));
+    pui     = u - pg * p.upg;
+    pchunk0 = pui * p.cpu;
+    pchunks = min(p.cpu, p.nchunks - pchunk0);
+  };
+  auto draw = [&]() {
+    int v = 0;
+    if (lane == 0) v = atomicAdd(&s_next_unit, 1);
+    pnext = __shfl_sync(0xFFFFFFFFu, v, 0);
+  };
+  // per-stage description of what the consumer will find: first local row (or -1),
+  // chunk index, partial-sum slot (or -1 when the unit ends elsewhere / writes y).
+  int m_row[kGemvStages], m_chunk[kGemvStages], m_end[kGemvStages];
+  auto issue = [&](int s) {
+    if (pdone) {
+      m_row[s] = -1;
+      return;
+    }
+    const int chunk = pchunk0 + pc;
+    m_row[s]        = pg * RW;
+    m_chunk[s]      = chunk;
+    m_end[s]        = (pc == pchunks - 1) ? pui : -1;
+    const int items   = min(kChunkItems, p.nitems - chunk * kChunkItems);
+    const uint32_t cb = chunk_bytes<DT>(items);
+    const int row0    = (c0 + pg) * RW;
+    const int nrow    = min(RW, p.rows - row0);
+    if (lane == 0) {
+      const uint32_t bar = bar_u32 + s * 8;
+      mbar_expect_tx(bar, cb * nrow);
+      const uint8_t* src = p.w + static_cast<size_t>(row0) * p.row_bytes +
+                           static_cast<size_t>(chunk) * chunk_bytes_full<DT>();
+      const uint32_t dst = ring_u32 + s * p.stage_bytes;
+#pragma unroll
+      for (int r = 0; r < RW; ++r)
+        if (r < nrow)
+          bulk_g2s(dst + r * chunk_bytes_full<DT>(), src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
+    }
+    if (++pc == pchunks) {
+      pc = 0;
+      pu = pnext;
+      if (pu >= U) {
+        pdone = true;
+      } else {
+        decode(pu);
+        draw();
+      }
+    }
+  };
+  if (!pdone) {
+    decode(pu);
+    draw();
+  }
+#pragma unroll
+  for (int s = 0; s < kGemvStages; ++s) issue(s);
   KDNN_TRACE(1);
   pdl_launch_dependents();
   pdl_wait();
@@ -355,41 +428,60 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_stream_kernel(const G
   float acc[RW];
 #pragma unroll
   for (int r = 0; r < RW; ++r) acc[r] = 0.f;
-  YT* y = static_cast<YT*>(p.y);
-  for (int n = 0;; ++n) {
-    const int s  = n % p.stages;
-    const int2 m = meta[s];
-    if (m.x < 0) break;
-    if (!mbar_wait_bounded(bar_u32 + s * 8, (n / p.stages) & 1)) {
-      if (lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
-      return;
-    }
-    if (n == 0) KDNN_TRACE(4);
-    const int item = m.y * kChunkItems + lane;
-    if (item < p.nitems) {
-      ItemX x;
+  YT* y         = static_cast<YT*>(p.y);
+  const int my_r = row_of_lane<RW>(lane);
+  uint32_t phase = 0;
+  bool ok = true, more = true;
+  while (more) {
 #pragma unroll
-      for (int g = 0; g < 4; ++g) x.g[g] = xg[static_cast<size_t>(g) * p.nitems + item];
-      x.hd = hd[item];
-      if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
-      const uint32_t st = ring_u32 + s * p.stage_bytes;
-#pragma unroll
-      for (int r = 0; r < RW; ++r) acc[r] += item_dot<DT>(st + r * chunk_bytes_full<DT>(), lane, x);
-    }
-    if (m.y == p.nchunks - 1) {
-      const int row0 = m.x * RW;
-#pragma unroll
-      for (int r = 0; r < RW; ++r) {
-        const float v = warp_sum(acc[r]);
-        if (lane == 0 && row0 + r < p.rows) store_scalar(y + row0 + r, v);
-        acc[r] = 0.f;
+    for (int s = 0; s < kGemvStages; ++s) {
+      if (!more) break;
+      if (m_row[s] < 0) {
+        more = false;
+        break;
       }
+      if (!mbar_wait_bounded(bar_u32 + s * 8, phase)) {
+        ok = more = false;
+        break;
+      }
+      const int item = m_chunk[s] * kChunkItems + lane;
+      if (item < p.nitems) {
+        ItemX x;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) x.g[g] = xg[static_cast<size_t>(g) * p.nitems + item];
+        x.hd = hd[item];
+        if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
+        const uint32_t st = ring_u32 + s * p.stage_bytes;
+#pragma unroll
+        for (int r = 0; r < RW; ++r) acc[r] += item_dot<DT>(st + r * chunk_bytes_full<DT>(), lane, x);
+      }
+      if (m_end[s] >= 0) {   // last chunk of the unit
+        const float v = reduce_rows<RW>(acc, lane);
+        const int lrow = m_row[s] + my_r;
+        if (lane < RW && c0 * RW + lrow < p.rows) {
+          if (p.upg == 1) store_scalar(y + c0 * RW + lrow, v);
+          else part[lrow * p.upg + m_end[s]] = v;
+        }
+#pragma unroll
+        for (int r = 0; r < RW; ++r) acc[r] = 0.f;
+      }
+      __syncwarp();   // every lane has read this stage
+      issue(s);
+      __syncwarp();
     }
-    __syncwarp();
-    if (lane == 0) issue();
-    __syncwarp();
+    phase ^= 1u;
   }
+  if (!ok && lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
   KDNN_TRACE(6);
+  if (p.upg > 1) {   // add up the partial sums of every local row in chunk order
+    __syncthreads();
+    const int nloc = min((c1 - c0) * RW, p.rows - c0 * RW);
+    for (int r = threadIdx.x; r < nloc; r += blockDim.x) {
+      float v = 0.f;
+      for (int j = 0; j < p.upg; ++j) v += part[r * p.upg + j];
+      store_scalar(y + c0 * RW + r, v);
+    }
+  }
 }
 
 // ---- generic kernels (any alignment; also the parity probe) ------------------------
@@ -566,7 +658,20 @@ static int env_int(const char* name, int dflt) {
 static unsigned long long* g_trace_buffer = nullptr;
 void gemv_set_trace(void* buf) { g_trace_buffer = static_cast<unsigned long long*>(buf); }
 
-static std::atomic<unsigned> g_launch_counter{0};
+static thread_local bool t_ring_does_not_fit = false;
+
+// Work split of one launch. All 16 warps (the kernel is bound by instruction issue, and
+// fewer warps measured slower even where they would fill the last round better); a unit is
+// a whole row group when every warp gets several of them, otherwise the rows are cut into
+// chunk ranges until there are about two units per warp.
+struct GemvSplit { int cpu, upg, warps; };
+static GemvSplit choose_split(int ngroups, int nchunks, int grid) {
+  const int gpc = (ngroups + grid - 1) / grid;   // row groups of the largest CTA slice
+  int upg = 1;
+  if (gpc < kGemvMaxWarps) upg = min(nchunks, (2 * kGemvMaxWarps + gpc - 1) / gpc);
+  const int cpu = (nchunks + upg - 1) / upg;
+  return GemvSplit{cpu, (nchunks + cpu - 1) / cpu, kGemvMaxWarps};
+}
 
 template <uint32_t DT, int RW, class XT, class YT>
 static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
@@ -574,21 +679,31 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   GemvParams p = base;
   p.ngroups     = (p.rows + RW - 1) / RW;
   p.stage_bytes = (RW * chunk_bytes_full<DT>() + 127) & ~127;
+  const int grid = max(1, min(di.sms, p.ngroups));
+  GemvSplit sp = choose_split(p.ngroups, p.nchunks, grid);
+  if (const int w = env_int("KDNN_GEMV_WARPS", 0)) sp.warps = max(1, min(kGemvMaxWarps, w));
+  if (const int c = env_int("KDNN_GEMV_CPU", 0)) {
+    sp.cpu = max(1, min(p.nchunks, c));
+    sp.upg = (p.nchunks + sp.cpu - 1) / sp.cpu;
+  }
+  const int gpc = (p.ngroups + grid - 1) / grid;
+  if (sp.upg > 1 && static_cast<size_t>(gpc + 1) * RW * sp.upg * 4 > 48 * 1024) {   // partial sums would not fit
+    sp.cpu = p.nchunks;
+    sp.upg = 1;
+  }
+  p.cpu         = sp.cpu;
+  p.upg         = sp.upg;
+  p.upg_magic   = static_cast<uint32_t>((0x100000000ull + sp.upg - 1) / sp.upg);
+  p.part_floats = sp.upg > 1 ? (gpc + 1) * RW * sp.upg : 0;
   const size_t act = ((static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80)) + 127) & ~size_t(127);
-  auto smem_need = [&](int st) {
-    return act + kGemvWarps * 128 + static_cast<size_t>(kGemvWarps) * st * p.stage_bytes + 128;
-  };
-  // Two stages per warp keep about one bandwidth-delay product in flight per SM; deeper
-  // rings measured slower (their requests queue ahead of the activation loads).
-  int stages = env_int("KDNN_GEMV_STAGES", 2);
-  stages     = stages < 2 ? 2 : (stages > 8 ? 8 : stages);
-  while (stages > 2 && smem_need(stages) > static_cast<size_t>(di.max_smem)) --stages;
-  if (smem_need(stages) > static_cast<size_t>(di.max_smem)) return cudaErrorInvalidConfiguration;
-  p.stages      = stages;
-  p.ticket_slot = static_cast<int>(g_launch_counter.fetch_add(1) % kTicketSlots);
-  p.trace       = g_trace_buffer;
-  const int grid = min(di.sms, (p.ngroups + kGemvWarps - 1) / kGemvWarps);
-  const size_t smem = smem_need(stages);
+  const size_t smem = act + kGemvMaxWarps * kGemvStages * 8 + 128 +
+                      ((static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127)) +
+                      static_cast<size_t>(kGemvMaxWarps) * kGemvStages * p.stage_bytes + 128;
+  if (smem > static_cast<size_t>(di.max_smem)) {
+    t_ring_does_not_fit = true;   // the caller takes the plain-load kernel instead
+    return cudaSuccess;
+  }
+  p.trace = g_trace_buffer;
   auto kern = gemv_stream_kernel<DT, RW, XT, YT>;
   static thread_local size_t configured = 0;
   if (smem > configured) {
@@ -597,7 +712,7 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
     configured = di.max_smem;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kGemvWarps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(sp.warps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -607,15 +722,11 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
 
 template <uint32_t DT, class XT, class YT>
 static cudaError_t launch_stream_rw(const GemvParams& p, cudaStream_t stream) {
-  const DeviceInfo& di = device_info();
-  // Rows per group. One row per group gives the finest work units and measured fastest
-  // for tall matrices; when there are at most two rows per warp, two-row groups (one
-  // group per warp, shared activation window) win for the 144- and 34-byte formats.
+  // Rows per group: two rows share one load of the activation window and one pass of
+  // the loop bookkeeping.
   int rw = env_int("KDNN_GEMV_RW", 0);
-  if (rw == 0) {
-    const int warps = di.sms * kGemvWarps;
-    rw = (DT != KDNN_GGML_Q6_K && p.rows > warps && p.rows <= 2 * warps) ? 2 : 1;
-  }
+  if (rw == 0) rw = p.rows >= 2 ? 2 : 1;
+  if (rw >= 4 && DT == KDNN_GGML_Q4_K) return launch_stream<DT, 4, XT, YT>(p, stream);
   if (rw >= 2) return launch_stream<DT, 2, XT, YT>(p, stream);
   return launch_stream<DT, 1, XT, YT>(p, stream);
 }
@@ -667,13 +778,14 @@ cudaError_t gemv_launch(uint32_t dt, const void* w, size_t rows, size_t cols, co
     p.nitems    = static_cast<int>(cols / 64);
     p.nchunks   = (p.nitems + kChunkItems - 1) / kChunkItems;
     cudaError_t e;
+    t_ring_does_not_fit = false;
     switch (dt) {
       case KDNN_GGML_Q4_K: e = launch_stream_dt<KDNN_GGML_Q4_K>(p, xs, ys, stream); break;
       case KDNN_GGML_Q6_K: e = launch_stream_dt<KDNN_GGML_Q6_K>(p, xs, ys, stream); break;
       default: e = launch_stream_dt<KDNN_GGML_Q8_0>(p, xs, ys, stream); break;
     }
-    if (e != cudaErrorInvalidConfiguration) return e;
-    (void)cudaGetLastError();  // row too long for the shared-memory ring: plain loads
+    if (!t_ring_does_not_fit) return e;   // launched, or a real error: never masked by the plain-load kernel
+    // activation row too long for shared memory next to the ring: plain loads
   }
   const uint8_t* wb = static_cast<const uint8_t*>(w);
   uint8_t* sb       = static_cast<uint8_t*>(scratch);

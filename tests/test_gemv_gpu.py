@@ -181,3 +181,40 @@ def test_golden_fixture(kd):
             assert np.all(np.abs(got - yr) <= np.abs(yr) * 2.0 ** -7 + 1e-30)
         else:
             assert np.abs(y.cpu().numpy() - yr).max() <= 1e-3 * np.abs(yr).max()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_graph_replays_recompute_every_row(kd, port, dtype):
+    """A captured sequence of GEMVs must do all of its work on every replay: tall matrices
+    (more row groups than resident warps, so the in-kernel work distribution is exercised),
+    outputs poisoned before each replay, each replay checked against the checker."""
+    dev = torch.device("cuda:0")
+    rows, K = 9000, 2048
+    mats, outs, refs = [], [], []
+    g = torch.Generator().manual_seed(77)
+    x_t = torch.randn(K, generator=g)
+    for i in range(3):
+        packed = kd.ggml_pack.random_payload(dtype, rows, K, 500 + i)
+        mats.append(kd.QuantWeight.from_numpy(packed, dtype, rows, K, dev))
+        outs.append(torch.empty(rows, dtype=torch.float32, device=dev))
+        refs.append(port.gemv_int8(dtype, O.aligned_copy(packed), rows, K, x_t.numpy())[0])
+    x = x_t.to(dev)
+    scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for w, y in zip(mats, outs):
+            kd.quant_gemv(x, w, y, scratch)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for w, y in zip(mats, outs):
+                kd.quant_gemv(x, w, y, scratch)
+        for _ in range(4):
+            for y in outs:
+                y.fill_(float("nan"))
+            graph.replay()
+            torch.cuda.synchronize()
+            for y, ref in zip(outs, refs):
+                got = y.cpu().numpy()
+                assert np.abs(got - ref).max() <= 1e-3 * np.abs(ref).max()
+    assert kd.device_status() == 0
