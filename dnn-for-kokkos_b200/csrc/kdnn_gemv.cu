@@ -56,10 +56,13 @@ __device__ __forceinline__ void granule_of(int b, int p, int& item, int& g) {
   }
 }
 
-template <uint32_t DT, class XT>
+struct NoHook { __device__ void operator()() const {} };
+// `after_loads` runs once, after this thread's first batch of global loads has been issued
+// and before their values are used: work that needs no activation bytes goes there.
+template <uint32_t DT, class XT, class Hook = NoHook>
 __device__ __forceinline__ void stage_activations(const XT* __restrict__ x, int K, int nitems,
                                                   int4* xg, float4* hd, int4* hs,
-                                                  uint8_t* gscratch) {
+                                                  uint8_t* gscratch, Hook after_loads = Hook()) {
   const int nblk     = K / 32;
   const int lane     = threadIdx.x & 31;
   const int l4       = lane & 3;          // four lanes per 32-element block, eight elements each
@@ -71,6 +74,7 @@ __device__ __forceinline__ void stage_activations(const XT* __restrict__ x, int 
   // prologue is one memory round trip, not one per block.
   constexpr int U = 4;
   const int step  = warps * 8;
+  bool first_batch = true;
   for (int base0 = (threadIdx.x >> 5) * 8; base0 < nblk; base0 += step * U) {
     float v[U][8];
 #pragma unroll
@@ -80,6 +84,8 @@ __device__ __forceinline__ void stage_activations(const XT* __restrict__ x, int 
       for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
       if (b < nblk) load8<XT>(x, static_cast<size_t>(b) * 32 + l4 * 8, vec_ok, v[u]);
     }
+    if (first_batch) after_loads();
+    first_batch = false;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (base0 + u * step >= nblk) break;  // uniform across the warp
@@ -108,6 +114,7 @@ __device__ __forceinline__ void stage_activations(const XT* __restrict__ x, int 
       }
     }
   }
+  if (first_batch) after_loads();   // a warp without blocks still runs the hook
 }
 
 // ---- per-format item evaluation ------------------------------------------------
@@ -282,6 +289,7 @@ struct GemvParams {
   uint8_t* scratch;
   int rows, K, row_bytes, nitems, nchunks;
   int ngroups;         // ceil(rows / RW)
+  int gq, gr;          // ngroups / grid and ngroups % grid
   int cpu;             // chunks per unit
   int upg;             // units per group = ceil(nchunks / cpu)
   uint32_t upg_magic;  // ceil(2^32 / upg): u / upg == umulhi(u, magic) for the unit counts that occur
@@ -346,8 +354,9 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_stream_kernel(cons
   KDNN_TRACE(0);
 
   // this CTA's slice of the row groups and its units
-  const int c0 = static_cast<int>(static_cast<long long>(blockIdx.x) * p.ngroups / gridDim.x);
-  const int c1 = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * p.ngroups / gridDim.x);
+  // even contiguous split of the row groups over the CTAs (quotient and remainder from the host)
+  const int c0 = static_cast<int>(blockIdx.x) * p.gq + min(static_cast<int>(blockIdx.x), p.gr);
+  const int c1 = c0 + p.gq + (static_cast<int>(blockIdx.x) < p.gr ? 1 : 0);
   const int U  = (c1 - c0) * p.upg;
   if (threadIdx.x == 0) s_next_unit = W;
   if (lane == 0) {
@@ -414,14 +423,19 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_stream_kernel(cons
     decode(pu);
     draw();
   }
-#pragma unroll
-  for (int s = 0; s < kGemvStages; ++s) issue(s);
+  // Only the first stage is requested before the dependency: a deeper burst ahead of the
+  // activation loads makes those loads (a few KB that everything waits for) queue behind
+  // megabytes of weights. The rest of the ring follows once those loads are in flight.
+  issue(0);
   KDNN_TRACE(1);
   pdl_launch_dependents();
   pdl_wait();
   KDNN_TRACE(2);
   stage_activations<DT, XT>(static_cast<const XT*>(p.x), p.K, p.nitems, xg, hd, hs,
-                            blockIdx.x == 0 ? p.scratch : nullptr);
+                            blockIdx.x == 0 ? p.scratch : nullptr, [&]() {
+#pragma unroll
+                              for (int s = 1; s < kGemvStages; ++s) issue(s);
+                            });
   __syncthreads();
   KDNN_TRACE(3);
 
@@ -479,6 +493,523 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_stream_kernel(cons
     for (int r = threadIdx.x; r < nloc; r += blockDim.x) {
       float v = 0.f;
       for (int j = 0; j < p.upg; ++j) v += part[r * p.upg + j];
+      store_scalar(y + c0 * RW + r, v);
+    }
+  }
+}
+
+// ---- Q4_K: one lane per (row, super-block) ----------------------------------------
+// The item mapping above spends most of its instructions on work that four lanes repeat
+// for the same super-block (header load, 6-bit scale unpack) and on loop bookkeeping per
+// 1152 bytes. Here a lane owns a whole 144-byte super-block of one row: nine 128-bit
+// shared-memory loads, one unpack of all eight (scale, min) pairs, 64 dp4a. A stage holds
+// two rows x up to 16 super-blocks (lanes 0..csb-1: row 0, csb..2csb-1: row 1), so a
+// warp iteration consumes up to 4608 bytes.
+//
+// Activations in shared memory: one 336-byte record per super-block -- 256 int8, the eight
+// block scales d, the eight products d * block sum, 16 bytes of padding (21 granules: an
+// odd pitch, so the lanes of a row hit different banks and every load is base + constant).
+constexpr int kWideRec     = 336;
+constexpr int kWideSb      = 16;                 // super-blocks per row per stage
+constexpr int kWideRowPitch = kWideSb * 144;
+constexpr int kWideStage   = 2 * kWideRowPitch;  // bytes
+
+template <class XT, class Hook = NoHook>
+__device__ __forceinline__ void stage_activations_wide(const XT* __restrict__ x, int K, uint8_t* xrec,
+                                                       uint8_t* gscratch, Hook after_loads = Hook()) {
+  const int nblk    = K / 32;
+  const int lane    = threadIdx.x & 31;
+  const int l4      = lane & 3;
+  const int warps   = blockDim.x >> 5;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+  int8_t* gq        = reinterpret_cast<int8_t*>(gscratch);
+  ActHdr* gh        = gscratch ? reinterpret_cast<ActHdr*>(gscratch + act_hdr_offset(K)) : nullptr;
+  constexpr int U = 4;
+  const int step  = warps * 8;
+  bool first_batch = true;
+  for (int base0 = (threadIdx.x >> 5) * 8; base0 < nblk; base0 += step * U) {
+    float v[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int b = base0 + u * step + (lane >> 2);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
+      if (b < nblk) load8<XT>(x, static_cast<size_t>(b) * 32 + l4 * 8, vec_ok, v[u]);
+    }
+    if (first_batch) after_loads();
+    first_batch = false;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (base0 + u * step >= nblk) break;  // uniform across the warp
+      const int b = base0 + u * step + (lane >> 2);
+      float d;
+      int part, total;
+      const uint2 packed = quantize_block_lane8(v[u], d, part, total);
+      if (b >= nblk) continue;
+      const int sb = b >> 3, jb = b & 7;
+      uint8_t* rec = xrec + static_cast<size_t>(sb) * kWideRec;
+      reinterpret_cast<uint2*>(rec + (jb * 2 + (l4 >> 1)) * 16)[l4 & 1] = packed;
+      if (l4 == 0) {
+        reinterpret_cast<float*>(rec + 256)[jb] = d;
+        reinterpret_cast<float*>(rec + 288)[jb] = __fmul_rn(static_cast<float>(total), d);
+      }
+      if (gscratch) {
+        reinterpret_cast<uint2*>(gq + static_cast<size_t>(b) * 32)[l4] = packed;
+        if (l4 == 0) gh[b] = ActHdr{d, part, total - part, 0};
+      }
+    }
+  }
+  if (first_batch) after_loads();   // a warp without blocks still runs the hook
+}
+
+// One super-block (144 bytes at shared address `blk`) against its activation record `xr`.
+__device__ __forceinline__ float q4k_superblock_dot(uint32_t blk, uint32_t xr) {
+  const int4 h = lds128(blk);
+  const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
+  // all eight 6-bit scales / mins as bytes: [0] sub-blocks 0-3, [1] sub-blocks 4-7
+  const uint32_t sc[2] = {s0 & 0x3F3F3F3Fu, (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u)};
+  const uint32_t mn[2] = {s1 & 0x3F3F3F3Fu, ((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u)};
+  float dxs[8], dss[8];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int4 a = lds128(xr + 256 + 16 * i), c = lds128(xr + 288 + 16 * i);
+    dxs[4 * i] = __int_as_float(a.x); dxs[4 * i + 1] = __int_as_float(a.y);
+    dxs[4 * i + 2] = __int_as_float(a.z); dxs[4 * i + 3] = __int_as_float(a.w);
+    dss[4 * i] = __int_as_float(c.x); dss[4 * i + 1] = __int_as_float(c.y);
+    dss[4 * i + 2] = __int_as_float(c.z); dss[4 * i + 3] = __int_as_float(c.w);
+  }
+  float p = 0.f, m = 0.f;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int4 qa = lds128(blk + 16 + it * 32), qb = lds128(blk + 32 + it * 32);
+    const int4 x0 = lds128(xr + 64 * it), x1 = lds128(xr + 64 * it + 16);
+    const int4 x2 = lds128(xr + 64 * it + 32), x3 = lds128(xr + 64 * it + 48);
+    const uint32_t q[8] = {(uint32_t)qa.x, (uint32_t)qa.y, (uint32_t)qa.z, (uint32_t)qa.w,
+                           (uint32_t)qb.x, (uint32_t)qb.y, (uint32_t)qb.z, (uint32_t)qb.w};
+    uint32_t lo0[4], lo1[4], hi0[4], hi1[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo0[i] = q[i] & 0x0F0F0F0Fu;
+      hi0[i] = q[i] & 0xF0F0F0F0u;      // 16 * high nibble, used as unsigned bytes
+      lo1[i] = q[4 + i] & 0x0F0F0F0Fu;
+      hi1[i] = q[4 + i] & 0xF0F0F0F0u;
+    }
+    const int dotA = dot16(lo1, x1, dot16(lo0, x0, 0));
+    const int dotB = dot16_us(hi1, x3, dot16_us(hi0, x2, 0)) >> 4;  // exact: the sum is a multiple of 16
+    const int jA = 2 * it, jB = 2 * it + 1;
+    const int scA = (sc[jA >> 2] >> (8 * (jA & 3))) & 0xFF, scB = (sc[jB >> 2] >> (8 * (jB & 3))) & 0xFF;
+    const int mnA = (mn[jA >> 2] >> (8 * (jA & 3))) & 0xFF, mnB = (mn[jB >> 2] >> (8 * (jB & 3))) & 0xFF;
+    p = fmaf(static_cast<float>(scA * dotA), dxs[jA], p);
+    p = fmaf(static_cast<float>(scB * dotB), dxs[jB], p);
+    m = fmaf(static_cast<float>(mnA), dss[jA], m);
+    m = fmaf(static_cast<float>(mnB), dss[jB], m);
+  }
+  const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+  return dd.x * p - dd.y * m;
+}
+
+struct WideParams {
+  const uint8_t* w;
+  const void* x;
+  void* y;
+  uint8_t* scratch;
+  int rows, K, row_bytes, nsb;
+  int nchunks, csb;    // chunks per row and super-blocks per chunk (the last chunk may hold fewer)
+  int ngroups;         // ceil(rows / 2)
+  int gq, gr;          // ngroups / grid and ngroups % grid
+  int cpu, upg;        // chunks per unit, units per group
+  uint32_t upg_magic;
+  int part_floats;
+  unsigned long long* trace;
+};
+
+// MAXW = 16: one CTA per SM. MAXW = 8: two CTAs per SM, so the next GEMV in the stream is
+// resident (weights requested, waiting for its dependency) while this one still streams.
+template <class XT, class YT, int MAXW, int STAGES>
+__global__ void __launch_bounds__(MAXW * 32, MAXW == 8 ? 2 : 1) gemv_q4k_wide_kernel(const WideParams p) {
+  constexpr int RW = 2;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = blockDim.x >> 5;
+  const uint32_t x_u32 = smem_u32(smem);   // activation records
+  size_t off    = (static_cast<size_t>(p.nsb) * kWideRec + 127) & ~size_t(127);
+  const uint32_t bar_u32 = smem_u32(smem + off) + warp * (STAGES * 8);
+  off += MAXW * STAGES * 8;
+  int& s_next_unit = *reinterpret_cast<int*>(smem + off);
+  off += 128;
+  float* part = reinterpret_cast<float*>(smem + off);
+  off += (static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127);
+  const uint32_t ring_u32 = smem_u32(smem + off) + warp * (STAGES * kWideStage);
+  KDNN_TRACE(0);
+
+  // even contiguous split of the row groups over the CTAs (quotient and remainder from the host)
+  const int c0 = static_cast<int>(blockIdx.x) * p.gq + min(static_cast<int>(blockIdx.x), p.gr);
+  const int c1 = c0 + p.gq + (static_cast<int>(blockIdx.x) < p.gr ? 1 : 0);
+  const int U  = (c1 - c0) * p.upg;
+  if (threadIdx.x == 0) s_next_unit = W;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + s * 8, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+
+  int pu = warp, pnext = 0x7fffffff, pg = 0, pchunk0 = 0, pchunks = 1, pc = 0, pui = 0;
+  bool pdone = pu >= U;
+  auto decode = [&](int u) {
+    pg      = p.upg == 1 ? u : static_cast<int>(__umulhi(static_cast<uint32_t>(u), p.upg_magic));
+    pui     = u - pg * p.upg;
+    pchunk0 = pui * p.cpu;
+    pchunks = min(p.cpu, p.nchunks - pchunk0);
+  };
+  auto draw = [&]() {
+    int v = 0;
+    if (lane == 0) v = atomicAdd(&s_next_unit, 1);
+    pnext = __shfl_sync(0xFFFFFFFFu, v, 0);
+  };
+  int m_row[STAGES], m_chunk[STAGES], m_end[STAGES];
+  auto issue = [&](int s) {
+    if (pdone) {
+      m_row[s] = -1;
+      return;
+    }
+    const int chunk = pchunk0 + pc;
+    m_row[s]        = pg * RW;
+    m_chunk[s]      = chunk;
+    m_end[s]        = (pc == pchunks - 1) ? pui : -1;
+    const uint32_t cb = static_cast<uint32_t>(min(p.csb, p.nsb - chunk * p.csb)) * 144u;
+    const int row0    = (c0 + pg) * RW;
+    const int nrow    = min(RW, p.rows - row0);
+    if (lane == 0) {
+      const uint32_t bar = bar_u32 + s * 8;
+      mbar_expect_tx(bar, cb * nrow);
+      const uint8_t* src = p.w + static_cast<size_t>(row0) * p.row_bytes + static_cast<size_t>(chunk) * p.csb * 144;
+      const uint32_t dst = ring_u32 + s * kWideStage;
+      bulk_g2s(dst, src, cb, bar);
+      if (nrow > 1) bulk_g2s(dst + kWideRowPitch, src + p.row_bytes, cb, bar);
+    }
+    if (++pc == pchunks) {
+      pc = 0;
+      pu = pnext;
+      if (pu >= U) {
+        pdone = true;
+      } else {
+        decode(pu);
+        draw();
+      }
+    }
+  };
+  if (!pdone) {
+    decode(pu);
+    draw();
+  }
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s) issue(s);
+  KDNN_TRACE(1);
+  pdl_launch_dependents();
+  pdl_wait();
+  KDNN_TRACE(2);
+  stage_activations_wide<XT>(static_cast<const XT*>(p.x), p.K, smem, blockIdx.x == 0 ? p.scratch : nullptr);
+  __syncthreads();
+  KDNN_TRACE(3);
+
+  float acc[RW] = {0.f, 0.f};   // per-lane sums of this unit: [0] as a row-0 lane, [1] as a row-1 lane
+  YT* y = static_cast<YT*>(p.y);
+  uint32_t phase = 0;
+  bool ok = true, more = true, first_round = true;
+  while (more) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      if (!more) break;
+      if (m_row[s] < 0) {
+        more = false;
+        break;
+      }
+      if (!mbar_wait_bounded(bar_u32 + s * 8, phase)) {
+        ok = more = false;
+        break;
+      }
+      if (first_round) { if (s == 0) KDNN_TRACE(4); if (s == 1) KDNN_TRACE(5); } else if (s == 0 && phase == 1) KDNN_TRACE(7);
+      const int lrow0 = m_row[s];
+      const int nrow  = min(RW, p.rows - (c0 * RW + lrow0));
+      const int sb0   = m_chunk[s] * p.csb;
+      const int csb   = min(p.csb, p.nsb - sb0);
+      const int r     = lane >= csb ? 1 : 0;
+      const int sb    = lane - r * csb;
+      if (sb < csb && r < nrow) {
+        const float v = q4k_superblock_dot(ring_u32 + s * kWideStage + r * kWideRowPitch + sb * 144,
+                                           x_u32 + (sb0 + sb) * kWideRec);
+        if (r == 0) acc[0] += v; else acc[1] += v;
+      }
+      if (m_end[s] >= 0) {   // last chunk of the unit
+        const float v = reduce_rows<RW>(acc, lane);
+        const int lrow = lrow0 + lane;
+        if (lane < nrow) {
+          if (p.upg == 1) store_scalar(y + c0 * RW + lrow, v);
+          else part[lrow * p.upg + m_end[s]] = v;
+        }
+        acc[0] = acc[1] = 0.f;
+      }
+      __syncwarp();   // every lane has read this stage
+      issue(s);
+      __syncwarp();
+    }
+    first_round = false;
+    phase ^= 1u;
+  }
+  if (!ok && lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
+  KDNN_TRACE(6);
+  if (p.upg > 1) {
+    __syncthreads();
+    const int nloc = min((c1 - c0) * RW, p.rows - c0 * RW);
+    for (int r = threadIdx.x; r < nloc; r += blockDim.x) {
+      float v = 0.f;
+      for (int j = 0; j < p.upg; ++j) v += part[r * p.upg + j];
+      store_scalar(y + c0 * RW + r, v);
+    }
+  }
+}
+
+// ---- Q4_K with the activation window in registers --------------------------------------
+// In the kernel above two thirds of the shared-memory reads are activation bytes that
+// every warp iteration fetches again. Here a warp is bound to one chunk of K (up to 16
+// super-blocks) for the whole launch and each lane keeps its half super-block of the
+// quantized activations (128 int8, four scales, four scaled sums: 40 registers) from the
+// prologue on, so the main loop reads only weight bytes from shared memory: one header
+// and four 16-byte nibble words per lane and row.
+//   lane = (sb, half): sb = lane / 2 super-block inside the chunk, half = sub-blocks
+//   4*half .. 4*half+3. A stage holds RW rows x one chunk (RW * 2304 bytes).
+// Warps w, w + nchunks, ... share chunk w % nchunks and draw row groups from that chunk's
+// counter; with more than one chunk the per-chunk row sums meet in shared memory and are
+// added in chunk order at the end.
+struct XregParams {
+  const uint8_t* w;
+  const void* x;
+  void* y;
+  uint8_t* scratch;
+  int rows, K, row_bytes, nsb;
+  int nchunks, csb;   // chunks per row (<= 16) and super-blocks per chunk (<= 16; the last chunk may hold fewer)
+  int ngroups;        // ceil(rows / RW)
+  int gq, gr;         // ngroups / grid and ngroups % grid
+  int wpc;            // warps per chunk
+  uint32_t nch_magic; // ceil(65536 / nchunks): warp / nchunks == (warp * magic) >> 16 for warp < 16
+  int part_floats;
+  int ablate;         // debug: 1 = skip the dot products (stream only)
+  int early;          // ring stages requested before the activation window is quantized
+  unsigned long long* trace;
+};
+
+// Half a super-block of one row: 128 weights against the lane's register window.
+__device__ __forceinline__ float q4k_half_dot(uint32_t blk, uint32_t qoff, int half, const int4 (&xg)[8],
+                                              const float4& dxv, const float4& dsv) {
+  const int4 h = lds128(blk);
+  const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
+  const uint32_t sc4 = half ? ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u)) : (s0 & 0x3F3F3F3Fu);
+  const uint32_t mn4 = half ? (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u)) : (s1 & 0x3F3F3F3Fu);
+  const float dx[4] = {dxv.x, dxv.y, dxv.z, dxv.w}, ds[4] = {dsv.x, dsv.y, dsv.z, dsv.w};
+  // int -> float without the conversion unit: for |i| < 2^22, bits(i + 0x4B400000) is the
+  // float 12582912 + i, and one exact subtraction gives float(i). The integer add rides
+  // on the multiply-add that forms scale * dot; the 6-bit mins go straight from their byte
+  // into the mantissa of 8388608.0f with one byte permute.
+  constexpr int kMagicI   = 0x4B400000;
+  constexpr float kMagicF = 12582912.0f;
+  float p = 0.f, m = 0.f;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int4 qa = lds128(blk + qoff + 32 * t), qb = lds128(blk + qoff + 32 * t + 16);
+    const uint32_t q[8] = {(uint32_t)qa.x, (uint32_t)qa.y, (uint32_t)qa.z, (uint32_t)qa.w,
+                           (uint32_t)qb.x, (uint32_t)qb.y, (uint32_t)qb.z, (uint32_t)qb.w};
+    uint32_t lo0[4], lo1[4], hi0[4], hi1[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo0[i] = q[i] & 0x0F0F0F0Fu;
+      hi0[i] = q[i] & 0xF0F0F0F0u;      // 16 * high nibble, used as unsigned bytes
+      lo1[i] = q[4 + i] & 0x0F0F0F0Fu;
+      hi1[i] = q[4 + i] & 0xF0F0F0F0u;
+    }
+    const int dotA = dot16(lo0, xg[4 * t], 0) + dot16(lo1, xg[4 * t + 1], 0);
+    const int dotB = (dot16_us(hi0, xg[4 * t + 2], 0) + dot16_us(hi1, xg[4 * t + 3], 0)) >> 4;  // exact
+    const int jA = 2 * t, jB = 2 * t + 1;
+    const int scA = static_cast<int>(__byte_perm(sc4, 0u, 0x4440u | jA));
+    const int scB = static_cast<int>(__byte_perm(sc4, 0u, 0x4440u | jB));
+    const float fA = __int_as_float(scA * dotA + kMagicI) - kMagicF;   // |scale * dot| <= 63 * 60960 < 2^22
+    const float fB = __int_as_float(scB * dotB + kMagicI) - kMagicF;
+    const float mA = __uint_as_float(__byte_perm(mn4, 0x4B000000u, 0x7650u | jA)) - 8388608.0f;
+    const float mB = __uint_as_float(__byte_perm(mn4, 0x4B000000u, 0x7650u | jB)) - 8388608.0f;
+    p = fmaf(fA, dx[jA], p);
+    p = fmaf(fB, dx[jB], p);
+    m = fmaf(mA, ds[jA], m);
+    m = fmaf(mB, ds[jB], m);
+  }
+  const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+  return dd.x * p - dd.y * m;
+}
+
+template <class XT, class YT, int RW, int STAGES>
+__global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_q4k_xreg_kernel(const XregParams p) {
+  constexpr int kStage = RW * kWideRowPitch;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t x_u32 = smem_u32(smem);   // activation records (see kWideRec)
+  size_t off = (static_cast<size_t>(p.nsb) * kWideRec + 127) & ~size_t(127);
+  const uint32_t bar_u32 = smem_u32(smem + off) + warp * (STAGES * 8);
+  off += kGemvMaxWarps * STAGES * 8;
+  int* s_next = reinterpret_cast<int*>(smem + off);   // [chunk] next local row group
+  off += 128;
+  float* part = reinterpret_cast<float*>(smem + off);  // [local row][chunk]
+  off += (static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127);
+  const uint32_t ring_u32 = smem_u32(smem + off) + warp * (STAGES * kStage);
+  KDNN_TRACE(0);
+
+  // even contiguous split of the row groups over the CTAs (quotient and remainder from the host)
+  const int c0 = static_cast<int>(blockIdx.x) * p.gq + min(static_cast<int>(blockIdx.x), p.gr);
+  const int c1 = c0 + p.gq + (static_cast<int>(blockIdx.x) < p.gr ? 1 : 0);
+  const int G  = c1 - c0;                       // row groups of this CTA = units per chunk
+  const int widx = static_cast<int>((static_cast<uint32_t>(warp) * p.nch_magic) >> 16), chunk = warp - widx * p.nchunks;
+  const int sb0   = chunk * p.csb;
+  const int csb   = min(p.csb, p.nsb - sb0);
+  const uint32_t cb = static_cast<uint32_t>(csb) * 144u;
+  if (threadIdx.x < p.nchunks) s_next[threadIdx.x] = p.wpc;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + s * 8, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncwarp();
+
+  // ---- producer (state uniform across the warp; lane 0 issues the copies) ----
+  int m_group[STAGES];
+  const uint8_t* wsrc = p.w + static_cast<size_t>(sb0) * 144;
+  const bool contiguous = p.nchunks == 1 && p.row_bytes == kWideRowPitch;
+  auto issue_unit = [&](int s, int u) {
+    m_group[s]     = u;
+    const int row0 = (c0 + u) * RW;
+    const int nrow = min(RW, p.rows - row0);
+    if (lane == 0) {
+      const uint32_t bar = bar_u32 + s * 8;
+      mbar_expect_tx(bar, cb * nrow);
+      const uint8_t* src = wsrc + static_cast<size_t>(row0) * p.row_bytes;
+      const uint32_t dst = ring_u32 + s * kStage;
+      if (contiguous) {   // one chunk per row and full rows: the unit is one run of bytes
+        bulk_g2s(dst, src, cb * nrow, bar);
+      } else {
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+          if (r < nrow) bulk_g2s(dst + r * kWideRowPitch, src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
+      }
+    }
+  };
+  // The first unit of every warp is fixed and requested at once, before the CTA has even
+  // synchronised. Only this one stage goes out before the dependency: a deeper burst ahead
+  // of the activation loads makes those loads (a few KB that everything waits for) queue
+  // behind megabytes of weights. The rest of the ring is requested right after the
+  // activation loads have been issued.
+  bool pdone = widx >= G;
+  if (!pdone) issue_unit(0, widx); else m_group[0] = -1;
+  __syncthreads();   // the chunk counters are set
+  int pu = 0, pnext = 0x7fffffff;
+  auto draw = [&]() {
+    int v = 0;
+    if (lane == 0) v = atomicAdd(&s_next[chunk], 1);
+    pnext = __shfl_sync(0xFFFFFFFFu, v, 0);
+  };
+  auto advance = [&]() {
+    pu = pnext;
+    if (pu >= G) pdone = true; else draw();
+  };
+  auto issue = [&](int s) {
+    if (pdone) {
+      m_group[s] = -1;
+      return;
+    }
+    issue_unit(s, pu);
+    advance();
+  };
+  if (!pdone) {
+    draw();
+    advance();
+  }
+  KDNN_TRACE(1);
+  pdl_launch_dependents();
+  pdl_wait();
+  KDNN_TRACE(2);
+  // ring stages 1 .. early-1 are requested once the activation loads are in flight, the
+  // rest after the quantized window has been written
+  stage_activations_wide<XT>(static_cast<const XT*>(p.x), p.K, smem, blockIdx.x == 0 ? p.scratch : nullptr, [&]() {
+#pragma unroll
+    for (int s = 1; s < STAGES; ++s)
+      if (s < p.early) issue(s);
+  });
+  KDNN_TRACE(7);
+#pragma unroll
+  for (int s = 1; s < STAGES; ++s)
+    if (s >= p.early) issue(s);
+  __syncthreads();
+
+  // ---- this lane's activation window: registers for the rest of the kernel ----
+  const int half = lane & 1;
+  const int sbl  = lane >> 1;
+  const bool active = sbl < csb;
+  const int sb   = active ? sbl : 0;
+  const uint32_t xr = x_u32 + (sb0 + sb) * kWideRec;
+  int4 xg[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) xg[j] = lds128(xr + (8 * half + j) * 16);
+  const int4 dxi = lds128(xr + 256 + 16 * half), dsi = lds128(xr + 288 + 16 * half);
+  const float4 dxv = make_float4(__int_as_float(dxi.x), __int_as_float(dxi.y), __int_as_float(dxi.z), __int_as_float(dxi.w));
+  const float4 dsv = make_float4(__int_as_float(dsi.x), __int_as_float(dsi.y), __int_as_float(dsi.z), __int_as_float(dsi.w));
+  const uint32_t lane_blk = sb * 144, qoff = 16 + 64 * half;
+  KDNN_TRACE(3);
+
+  YT* y = static_cast<YT*>(p.y);
+  uint32_t phase = 0;
+  bool ok = true, more = true, first_round = true;
+  while (more) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      if (!more) break;
+      if (m_group[s] < 0) {
+        more = false;
+        break;
+      }
+      if (!mbar_wait_bounded(bar_u32 + s * 8, phase)) {
+        ok = more = false;
+        break;
+      }
+      if (first_round && s == 0) KDNN_TRACE(4);
+      const int lrow0 = m_group[s] * RW;
+      const int nrow  = min(RW, p.rows - (c0 * RW + lrow0));
+      float acc[RW];
+#pragma unroll
+      for (int r = 0; r < RW; ++r) {
+        acc[r] = 0.f;
+        if (r < nrow && !(p.ablate & 1)) {
+          const float v = q4k_half_dot(ring_u32 + s * kStage + r * kWideRowPitch + lane_blk, qoff, half, xg, dxv, dsv);
+          acc[r] = active ? v : 0.f;
+        }
+      }
+      const float v = reduce_rows<RW>(acc, lane);
+      if (lane < nrow) {
+        const int lrow = lrow0 + lane;
+        if (p.nchunks == 1) store_scalar(y + c0 * RW + lrow, v);
+        else part[lrow * p.nchunks + chunk] = v;
+      }
+      __syncwarp();   // every lane has read this stage
+      issue(s);
+      __syncwarp();
+    }
+    phase ^= 1u;
+    first_round = false;
+  }
+  if (!ok && lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
+  KDNN_TRACE(6);
+  if (p.nchunks > 1) {
+    __syncthreads();
+    const int nloc = min(G * RW, p.rows - c0 * RW);
+    for (int r = threadIdx.x; r < nloc; r += blockDim.x) {
+      float v = 0.f;
+      for (int j = 0; j < p.nchunks; ++j) v += part[r * p.nchunks + j];
       store_scalar(y + c0 * RW + r, v);
     }
   }
@@ -680,6 +1211,8 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   p.ngroups     = (p.rows + RW - 1) / RW;
   p.stage_bytes = (RW * chunk_bytes_full<DT>() + 127) & ~127;
   const int grid = max(1, min(di.sms, p.ngroups));
+  p.gq = p.ngroups / grid;
+  p.gr = p.ngroups % grid;
   GemvSplit sp = choose_split(p.ngroups, p.nchunks, grid);
   if (const int w = env_int("KDNN_GEMV_WARPS", 0)) sp.warps = max(1, min(kGemvMaxWarps, w));
   if (const int c = env_int("KDNN_GEMV_CPU", 0)) {
@@ -720,11 +1253,144 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
+// Returns false when the shape is outside what the register-window kernel covers.
+template <class XT, class YT, int RW>
+static bool launch_q4k_xreg(const GemvParams& base, cudaStream_t stream, cudaError_t& err) {
+  const DeviceInfo& di = device_info();
+  XregParams p{};
+  p.w = base.w; p.x = base.x; p.y = base.y; p.scratch = base.scratch;
+  p.rows = base.rows; p.K = base.K; p.row_bytes = base.row_bytes;
+  p.nsb     = base.K / 256;
+  p.nchunks = (p.nsb + kWideSb - 1) / kWideSb;
+  if (p.nchunks > kGemvMaxWarps) return false;
+  p.csb     = (p.nsb + p.nchunks - 1) / p.nchunks;   // near-equal chunks
+  p.nchunks = (p.nsb + p.csb - 1) / p.csb;
+  p.ngroups = (p.rows + RW - 1) / RW;
+  p.wpc     = kGemvMaxWarps / p.nchunks;
+  const int warps = p.wpc * p.nchunks;
+  const int grid  = max(1, min(di.sms, p.ngroups));
+  p.gq = p.ngroups / grid;
+  p.gr = p.ngroups % grid;
+  p.nch_magic = static_cast<uint32_t>((65536 + p.nchunks - 1) / p.nchunks);
+  const int gpc   = (p.ngroups + grid - 1) / grid;
+  p.part_floats   = p.nchunks > 1 ? (gpc + 1) * RW * p.nchunks : 0;
+  if (static_cast<size_t>(p.part_floats) * 4 > 32 * 1024) return false;
+  const size_t fixed = ((static_cast<size_t>(p.nsb) * kWideRec + 127) & ~size_t(127)) + 128 +
+                       ((static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127)) + 128;
+  constexpr int kStage = RW * kWideRowPitch;
+  auto smem_for = [&](int st) { return fixed + static_cast<size_t>(kGemvMaxWarps) * st * (8 + kStage); };
+  const int units_per_warp = (gpc + p.wpc - 1) / p.wpc;
+  int stages = env_int("KDNN_GEMV_STAGES", 0);
+  if (stages == 0) stages = 3;
+  stages = max(2, min(4, min(stages, max(2, units_per_warp))));
+  while (stages > 2 && smem_for(stages) > static_cast<size_t>(di.max_smem)) --stages;
+  if (smem_for(stages) > static_cast<size_t>(di.max_smem)) return false;
+  const size_t smem = smem_for(stages);
+  p.trace = g_trace_buffer;
+  p.ablate = env_int("KDNN_GEMV_ABLATE", 0);
+  p.early  = env_int("KDNN_GEMV_EARLY", 2);
+  using Kern = void (*)(const XregParams);
+  const Kern kern = stages == 2 ? gemv_q4k_xreg_kernel<XT, YT, RW, 2>
+                  : stages == 3 ? gemv_q4k_xreg_kernel<XT, YT, RW, 3> : gemv_q4k_xreg_kernel<XT, YT, RW, 4>;
+  static thread_local bool configured[5] = {};
+  if (!configured[stages]) {
+    err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem);
+    if (err != cudaSuccess) return true;
+    configured[stages] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(warps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = use_pdl() ? 1 : 0;
+  err = cudaLaunchKernelEx(&cfg, kern, p);
+  return true;
+}
+
+template <class XT, class YT>
+static cudaError_t launch_q4k_wide(const GemvParams& base, cudaStream_t stream) {
+  const DeviceInfo& di = device_info();
+  WideParams p{};
+  p.w = base.w; p.x = base.x; p.y = base.y; p.scratch = base.scratch;
+  p.rows = base.rows; p.K = base.K; p.row_bytes = base.row_bytes;
+  p.nsb     = base.K / 256;
+  p.nchunks = (p.nsb + kWideSb - 1) / kWideSb;
+  p.csb     = (p.nsb + p.nchunks - 1) / p.nchunks;   // near-equal chunks
+  p.nchunks = (p.nsb + p.csb - 1) / p.csb;
+  p.ngroups = (p.rows + 1) / 2;
+  const int grid = max(1, min(di.sms, p.ngroups));
+  p.gq = p.ngroups / grid;
+  p.gr = p.ngroups % grid;
+  GemvSplit sp = choose_split(p.ngroups, p.nchunks, grid);
+  if (const int w = env_int("KDNN_GEMV_WARPS", 0)) sp.warps = max(1, min(kGemvMaxWarps, w));
+  if (const int c = env_int("KDNN_GEMV_CPU", 0)) {
+    sp.cpu = max(1, min(p.nchunks, c));
+    sp.upg = (p.nchunks + sp.cpu - 1) / sp.cpu;
+  }
+  const int gpc = (p.ngroups + grid - 1) / grid;
+  if (sp.upg > 1 && static_cast<size_t>(gpc + 1) * 2 * sp.upg * 4 > 32 * 1024) {
+    sp.cpu = p.nchunks;
+    sp.upg = 1;
+  }
+  p.cpu         = sp.cpu;
+  p.upg         = sp.upg;
+  p.upg_magic   = static_cast<uint32_t>((0x100000000ull + sp.upg - 1) / sp.upg);
+  p.part_floats = sp.upg > 1 ? (gpc + 1) * 2 * sp.upg : 0;
+  const int maxw = sp.warps <= 8 ? 8 : kGemvMaxWarps;
+  // Ring depth: as many stages as fit (up to 4) but no more than a warp has units to fetch;
+  // with few units per warp the whole slice is requested at kernel entry.
+  const size_t fixed = ((static_cast<size_t>(p.nsb) * kWideRec + 127) & ~size_t(127)) + 128 +
+                       ((static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127)) + 128;
+  auto smem_for = [&](int st) { return fixed + static_cast<size_t>(maxw) * st * (8 + kWideStage); };
+  const size_t cap = maxw == 8 ? static_cast<size_t>(di.max_smem) / 2 - 1024 : static_cast<size_t>(di.max_smem);
+  const int chunks_per_warp = (gpc * p.nchunks + sp.warps - 1) / sp.warps;
+  int stages = env_int("KDNN_GEMV_STAGES", 0);
+  if (stages == 0) stages = max(2, min(4, chunks_per_warp));
+  stages = max(2, min(4, stages));
+  while (stages > 2 && smem_for(stages) > cap) --stages;
+  if (smem_for(stages) > cap) {
+    t_ring_does_not_fit = true;
+    return cudaSuccess;
+  }
+  const size_t smem = smem_for(stages);
+  p.trace = g_trace_buffer;
+  using Kern = void (*)(const WideParams);
+  Kern kern;
+  if (maxw == 8)
+    kern = stages == 2 ? gemv_q4k_wide_kernel<XT, YT, 8, 2> : stages == 3 ? gemv_q4k_wide_kernel<XT, YT, 8, 3>
+                                                                            : gemv_q4k_wide_kernel<XT, YT, 8, 4>;
+  else
+    kern = stages == 2 ? gemv_q4k_wide_kernel<XT, YT, 16, 2> : stages == 3 ? gemv_q4k_wide_kernel<XT, YT, 16, 3>
+                                                                             : gemv_q4k_wide_kernel<XT, YT, 16, 4>;
+  static thread_local bool configured[2][5] = {};
+  if (!configured[maxw == 8][stages]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(cap));
+    if (e != cudaSuccess) return e;
+    configured[maxw == 8][stages] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(sp.warps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = use_pdl() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
 template <uint32_t DT, class XT, class YT>
 static cudaError_t launch_stream_rw(const GemvParams& p, cudaStream_t stream) {
   // Rows per group: two rows share one load of the activation window and one pass of
   // the loop bookkeeping.
   int rw = env_int("KDNN_GEMV_RW", 0);
+  if (DT == KDNN_GGML_Q4_K && !env_int("KDNN_GEMV_ITEM", 0)) {
+    const int mode = env_int("KDNN_GEMV_Q4K", 0);   // 0: register window, 1: shared-memory window
+    cudaError_t err = cudaSuccess;
+    if (mode == 0) {
+      if (rw == 1 ? launch_q4k_xreg<XT, YT, 1>(p, stream, err) : launch_q4k_xreg<XT, YT, 2>(p, stream, err)) return err;
+    }
+    return launch_q4k_wide<XT, YT>(p, stream);
+  }
   if (rw == 0) rw = p.rows >= 2 ? 2 : 1;
   if (rw >= 4 && DT == KDNN_GGML_Q4_K) return launch_stream<DT, 4, XT, YT>(p, stream);
   if (rw >= 2) return launch_stream<DT, 2, XT, YT>(p, stream);
