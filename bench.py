@@ -339,7 +339,7 @@ def run_ours(args):
         per_kernel[f"{name}_{rows}x{K}"] = {"us_per_launch": us, "algorithmic_bytes": ab,
                                             "achieved_GBps": ab / us / 1e3, "frac": ab / us / 1e3 / peak}
     dom = per_kernel["Q4_K_14336x4096"]
-    roofline = {"kernel": "gemv_stream_kernel<Q4_K> 14336x4096", "bound": "hbm", "achieved": dom["achieved_GBps"],
+    roofline = {"kernel": "gemv_q4k_xreg_kernel 14336x4096", "bound": "hbm", "achieved": dom["achieved_GBps"],
                 "peak": peak, "peak_source": f"{peak_kind} HBM copy bandwidth (MEASURED_PEAKS.json)",
                 "unit": "GB/s", "frac": dom["frac"], "frac_of_nominal_8TBps": dom["achieved_GBps"] / 8000.0,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in

@@ -275,7 +275,12 @@ constexpr size_t mma_smem_bytes() {
 }
 
 template <int MODE, class YT>
+static cudaError_t launch_grouped_mma2(const MmaParams& p, int groups, cudaStream_t st);
+
+template <int MODE, class YT>
 static cudaError_t launch_grouped_mma(const MmaParams& p, int groups, cudaStream_t st) {
+  static const bool v1 = [] { const char* e = getenv("KDNN_MMA_V1"); return e && e[0] == '1'; }();
+  if (!v1) return launch_grouped_mma2<MODE, YT>(p, groups, st);
   auto kern = grouped_mma_q4k_kernel<MODE, YT>;
   constexpr size_t smem = mma_smem_bytes<MODE>();
   static thread_local bool configured = false;
@@ -286,6 +291,343 @@ static cudaError_t launch_grouped_mma(const MmaParams& p, int groups, cudaStream
   }
   dim3 grid((p.N + kMmaRows - 1) / kMmaRows, groups);
   kern<<<grid, kMmaWarps * 32, smem, st>>>(p);
+  return cudaGetLastError();
+}
+
+// ---- second version: more warps in flight, fewer instructions per tile ---------------
+// Same numerics as above. Differences:
+//  * a warp owns 16 rows of ONE matrix (MODE 1: even warps gate, odd warps up, the two
+//    meet in shared memory for the SwiGLU epilogue), so a CTA needs half the shared memory
+//    and registers and two CTAs fit on an SM;
+//  * up to 32 activation rows per pass (1..4 n8 tiles chosen at run time), staged in
+//    512-element chunks with cp.async, double buffered: one __syncthreads per chunk;
+//  * the 6-bit scales of a super-block are expanded once per warp (one lane per row and
+//    half) into a per-warp table instead of by every lane that needs them;
+//  * packed bytes are read 64 bits at a time in a K order that both operands share
+//    (mma k-slot 4*tig+i <- element 8*tig+i, slot 16+4*tig+i <- element 8*tig+4+i);
+//  * the MMA accumulator starts at the bit pattern of 12582912.0f, so the int32 result is
+//    already the float 12582912 + dot and one exact subtraction replaces the int->float
+//    conversion; the high nibbles are used in place as unsigned bytes (16 * nibble), their
+//    factor 16 goes into the scale.
+constexpr int kM2Warps   = 8;
+constexpr int kM2NT      = 32;                 // activation rows per pass
+constexpr int kM2KC      = 512;                // activation elements per staged chunk
+constexpr int kM2XPitch  = kM2KC + 32;         // int8 row pitch: 8 words mod 32 (conflict-free 64-bit B loads)
+constexpr int kM2WPitch  = 160;                // packed row pitch in a weight stage (same property)
+constexpr int kM2Stages  = 2;                  // weight ring depth per warp, in super-blocks
+constexpr int kM2StageBytes = 16 * kM2WPitch;
+constexpr int kM2MagicI  = 0x4B400000;
+constexpr float kM2MagicF = 12582912.0f;
+
+__device__ __forceinline__ void mma_u8s8_magic(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(kM2MagicI));
+}
+// Shared loads with a compile-time byte offset folded into the instruction.
+template <int OFF>
+__device__ __forceinline__ uint2 lds64_o(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(a), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ int4 lds128_o(uint32_t a) {
+  int4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64_g(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;   // 0: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 8 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int MODE>
+struct M2Layout {
+  static constexpr int kRowsPerCta = MODE == 1 ? 64 : 128;
+  static constexpr size_t xq    = 0;                                                   // [2][NT][XPitch] int8
+  static constexpr size_t xs    = xq + 2 * kM2NT * kM2XPitch;                          // [2][KC/32][NT] float2
+  static constexpr size_t rowp  = xs + 2 * (kM2KC / 32) * kM2NT * 8;                   // [NT] activation row offsets
+  static constexpr size_t bars  = rowp + kM2NT * 8;                                    // [warps][stages]
+  static constexpr size_t tab   = bars + kM2Warps * kM2Stages * 8;                     // [warps][16 rows][4] float4
+  static constexpr size_t ring  = (tab + kM2Warps * 16 * 4 * 16 + 127) & ~size_t(127); // [warps][stages][16][WPitch]
+  static constexpr size_t total = ring + kM2Warps * kM2Stages * kM2StageBytes + 128;
+};
+
+// One super-block (16 rows in stage `st`, scale table `tab`) against NTILES n8 tiles of
+// activations: `xb` / `sx` point at the super-block's first 32-block in the staged chunk.
+template <int NTILES, int IT, int PAR, int T>
+__device__ __forceinline__ void m2_tile(float (&acc)[4][4], const uint32_t (&a)[4], float swA, float mwA, float swB,
+                                        float mwB, uint32_t b_addr, uint32_t s_addr) {
+  constexpr int blk = 2 * IT + PAR;
+  const uint2 b  = lds64_o<T * (8 * kM2XPitch) + blk * 32>(b_addr);
+  const int4 sxv = lds128_o<(blk * kM2NT + 8 * T) * 8>(s_addr);   // {dx0, dxs0, dx1, dxs1}
+  int cfrag[4];
+  mma_u8s8_magic(cfrag, a, b.x, b.y);
+  const float dx0 = __int_as_float(sxv.x), ds0 = __int_as_float(sxv.y);
+  const float dx1 = __int_as_float(sxv.z), ds1 = __int_as_float(sxv.w);
+  const float f0 = __int_as_float(cfrag[0]) - kM2MagicF, f1 = __int_as_float(cfrag[1]) - kM2MagicF;
+  const float f2 = __int_as_float(cfrag[2]) - kM2MagicF, f3 = __int_as_float(cfrag[3]) - kM2MagicF;
+  acc[T][0] = fmaf(swA * dx0, f0, fmaf(mwA, ds0, acc[T][0]));
+  acc[T][1] = fmaf(swA * dx1, f1, fmaf(mwA, ds1, acc[T][1]));
+  acc[T][2] = fmaf(swB * dx0, f2, fmaf(mwB, ds0, acc[T][2]));
+  acc[T][3] = fmaf(swB * dx1, f3, fmaf(mwB, ds1, acc[T][3]));
+}
+
+template <int NTILES, int IT>
+__device__ __forceinline__ void m2_it(float (&acc)[4][4], uint32_t wa_addr, uint32_t ta_addr, uint32_t b_addr,
+                                      uint32_t s_addr) {
+  const uint2 wa = lds64_o<IT * 32>(wa_addr);
+  const uint2 wb = lds64_o<8 * kM2WPitch + IT * 32>(wa_addr);
+  const int4 ta = lds128_o<IT * 16>(ta_addr);
+  const int4 tb = lds128_o<8 * 64 + IT * 16>(ta_addr);
+  {
+    const uint32_t a[4] = {wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu};
+    const float swA = __int_as_float(ta.x), mwA = __int_as_float(ta.y), swB = __int_as_float(tb.x), mwB = __int_as_float(tb.y);
+    m2_tile<NTILES, IT, 0, 0>(acc, a, swA, mwA, swB, mwB, b_addr, s_addr);
+    if (NTILES > 1) m2_tile<NTILES, IT, 0, 1>(acc, a, swA, mwA, swB, mwB, b_addr, s_addr);
+    if (NTILES > 2) m2_tile<NTILES, IT, 0, 2>(acc, a, swA, mwA, swB, mwB, b_addr, s_addr);
+    if (NTILES > 3) m2_tile<NTILES, IT, 0, 3>(acc, a, swA, mwA, swB, mwB, b_addr, s_addr);
+  }
+  {
+    const uint32_t a[4] = {wa.x & 0xF0F0F0F0u, wb.x & 0xF0F0F0F0u, wa.y & 0xF0F0F0F0u, wb.y & 0xF0F0F0F0u};
+    const float swA = __int_as_float(ta.z), mwA = __int_as_float(ta.w), swB = __int_as_float(tb.z), mwB = __int_as_float(tb.w);
+    m2_tile<NTILES, IT, 1, 0>(acc, a, swA, mwA, swB, mwB, b_addr, s_addr);
+    if (NTILES > 1) m2_tile<NTILES, IT, 1, 1>(acc, a, swA, mwA, swB, mwB, b_addr, s_addr);
+    if (NTILES > 2) m2_tile<NTILES, IT, 1, 2>(acc, a, swA, mwA, swB, mwB, b_addr, s_addr);
+    if (NTILES > 3) m2_tile<NTILES, IT, 1, 3>(acc, a, swA, mwA, swB, mwB, b_addr, s_addr);
+  }
+}
+
+// One super-block (16 rows in stage `st`, scale table `tab`) against NTILES n8 tiles of
+// activations: `xb` / `sx` point at the super-block's first 32-block in the staged chunk.
+template <int NTILES>
+__device__ __forceinline__ void m2_superblock(float (&acc)[4][4], uint32_t st, uint32_t tab, uint32_t xb, uint32_t sx,
+                                              int gid, int tig) {
+  const uint32_t wa_addr = st + gid * kM2WPitch + 16 + 8 * tig;
+  const uint32_t ta_addr = tab + gid * 64;
+  const uint32_t b_addr  = xb + gid * kM2XPitch + 8 * tig;
+  const uint32_t s_addr  = sx + tig * 16;
+  m2_it<NTILES, 0>(acc, wa_addr, ta_addr, b_addr, s_addr);
+  m2_it<NTILES, 1>(acc, wa_addr, ta_addr, b_addr, s_addr);
+  m2_it<NTILES, 2>(acc, wa_addr, ta_addr, b_addr, s_addr);
+  m2_it<NTILES, 3>(acc, wa_addr, ta_addr, b_addr, s_addr);
+}
+
+template <int MODE, class YT>
+__global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(const MmaParams p) {
+  using L = M2Layout<MODE>;
+  extern __shared__ __align__(128) uint8_t m2_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int g   = blockIdx.y;
+  const int beg = p.offs[g], n_g = p.offs[g + 1] - beg;
+  if (n_g <= 0) return;
+
+  const uint32_t xq_u32 = smem_u32(m2_smem + L::xq), xs_u32 = smem_u32(m2_smem + L::xs);
+  long long* rowp = reinterpret_cast<long long*>(m2_smem + L::rowp);
+  const uint32_t bar_u32 = smem_u32(m2_smem + L::bars) + warp * (kM2Stages * 8);
+  const uint32_t tab_u32 = smem_u32(m2_smem + L::tab) + warp * (16 * 4 * 16);
+  const uint32_t ring_u32 = smem_u32(m2_smem + L::ring) + warp * (kM2Stages * kM2StageBytes);
+
+  const int mat  = MODE == 1 ? (warp & 1) : 0;
+  const int slab = MODE == 1 ? (warp >> 1) : warp;
+  const int row_base = blockIdx.x * L::kRowsPerCta + slab * 16;
+  const int nsb  = p.K / 256;
+  // lanes 0-15 copy one packed row each (rows past the end re-read the last row)
+  const uint8_t* src = nullptr;
+  if (lane < 16)
+    src = reinterpret_cast<const uint8_t*>((mat == 0 ? p.w0 : p.w1)[p.g_first + g]) +
+          static_cast<size_t>(min(row_base + lane, p.N - 1)) * p.row_bytes;
+
+  int issued = 0, consumed = 0;
+  bool ok = true;
+  auto issue = [&](int sb) {   // whole warp
+    const int s = issued % kM2Stages;
+    ++issued;
+    const uint32_t bar = bar_u32 + s * 8;
+    if (lane == 0) mbar_expect_tx(bar, 144u * 16u);
+    __syncwarp();
+    if (lane < 16) bulk_g2s(ring_u32 + s * kM2StageBytes + lane * kM2WPitch, src + static_cast<size_t>(sb) * 144, 144u, bar);
+  };
+  if (lane == 0) {
+    for (int s = 0; s < kM2Stages; ++s) mbar_init(bar_u32 + s * 8, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncwarp();
+
+  const int nchunk = (p.K + kM2KC - 1) / kM2KC;
+  const size_t scale_off = act_bytes(static_cast<size_t>(p.K));
+  // cp.async of one activation chunk: NT rows x kc int8 and NT x kc/32 {d, d*sum} pairs
+  auto stage_chunk = [&](int c) {
+    const int k0 = c * kM2KC, kc = min(kM2KC, p.K - k0);
+    const uint32_t xb = xq_u32 + (c & 1) * (kM2NT * kM2XPitch);
+    const int lg = kc == kM2KC ? 5 : 31 - __clz(kc / 16);   // 16-byte pieces per row: a power of two
+    const int per_row = 1 << lg;
+    for (int f = threadIdx.x; f < kM2NT * per_row; f += blockDim.x) {
+      const int t = f >> lg, c16 = f & (per_row - 1);
+      const long long ro = rowp[t];
+      cp_async16(xb + t * kM2XPitch + c16 * 16, p.xrows + (ro < 0 ? 0 : ro) + k0 + c16 * 16, ro >= 0);
+    }
+    const uint32_t sbuf = xs_u32 + (c & 1) * ((kM2KC / 32) * kM2NT * 8);
+    const int nb = kc / 32;
+    for (int f = threadIdx.x; f < kM2NT * nb; f += blockDim.x) {
+      const int b = f / kM2NT, t = f - b * kM2NT;   // consecutive threads fill consecutive 8-byte slots
+      const long long ro = rowp[t];
+      cp_async8(sbuf + (b * kM2NT + t) * 8, p.xrows + (ro < 0 ? 0 : ro) + scale_off + static_cast<size_t>(k0 / 32 + b) * 8,
+                ro >= 0);
+    }
+    cp_async_commit();
+  };
+
+  for (int t0 = 0; t0 < n_g; t0 += kM2NT) {
+    const int nt = min(kM2NT, n_g - t0);
+    const int ntiles = (nt + 7) >> 3;
+    __syncthreads();   // the previous pass is done with every buffer
+    if (threadIdx.x < kM2NT) {
+      long long ro = -1;
+      if (threadIdx.x < nt) {
+        const int srow = MODE == 0 ? beg + t0 + threadIdx.x : p.list[beg + t0 + threadIdx.x] / p.S;
+        ro = static_cast<long long>(srow) * static_cast<long long>(p.x_pitch);
+      }
+      rowp[threadIdx.x] = ro;
+    }
+    __syncthreads();
+    stage_chunk(0);
+    if (ok)
+      for (int q = 0; q < kM2Stages && q < nsb; ++q) issue(q);
+
+    float acc[4][4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
+
+    // A warp whose bounded wait gives up stops computing but keeps meeting the others at
+    // every barrier, so nobody is left waiting for it.
+    for (int c = 0; c < nchunk; ++c) {
+      cp_async_wait_all();
+      __syncthreads();   // chunk c has landed for everybody; everybody is done with chunk c - 1
+      if (c + 1 < nchunk) stage_chunk(c + 1);
+      const uint32_t xb = xq_u32 + (c & 1) * (kM2NT * kM2XPitch);
+      const uint32_t sbuf = xs_u32 + (c & 1) * ((kM2KC / 32) * kM2NT * 8);
+      const int sb_first = c * (kM2KC / 256), sb_last = min(nsb, sb_first + kM2KC / 256);
+      for (int sb = sb_first; sb < sb_last && ok; ++sb) {
+        const int s = consumed % kM2Stages;
+        if (!mbar_wait_bounded(bar_u32 + s * 8, (consumed / kM2Stages) & 1)) {
+          ok = false;
+          if (lane == 0) atomicExch(p.status, KDNN_ERR_DEVICE_WAIT);
+          break;
+        }
+        ++consumed;
+        const uint32_t st = ring_u32 + s * kM2StageBytes;
+        {  // expand the 6-bit scales: lane = (row, half) -> {sw0, mw0, sw1, mw1} pairs of its four sub-blocks
+          const int r = lane >> 1, half = lane & 1;
+          const int4 h = lds128_g(st + r * kM2WPitch);
+          const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
+          const uint32_t sc4 = half ? ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u)) : (s0 & 0x3F3F3F3Fu);
+          const uint32_t mn4 = half ? (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u)) : (s1 & 0x3F3F3F3Fu);
+          const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+          float sw[4], mw[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float fs = __uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7650u | j)) - 8388608.0f;
+            const float fm = __uint_as_float(__byte_perm(mn4, 0x4B000000u, 0x7650u | j)) - 8388608.0f;
+            sw[j] = dd.x * fs * ((j & 1) ? 0.0625f : 1.0f);   // odd sub-blocks: high nibbles carry a factor 16
+            mw[j] = -(dd.y * fm);
+          }
+          // table entry [row][it] = {sw(2it), mw(2it), sw(2it+1), mw(2it+1)}
+          const uint32_t ta = tab_u32 + (r * 4 + half * 2) * 16;
+          asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(ta), "f"(sw[0]), "f"(mw[0]), "f"(sw[1]), "f"(mw[1]) : "memory");
+          asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(ta + 16), "f"(sw[2]), "f"(mw[2]), "f"(sw[3]), "f"(mw[3]) : "memory");
+        }
+        __syncwarp();
+        const int blk0 = (sb - sb_first) * 8;   // first 32-block of this super-block inside the chunk
+        switch (ntiles) {
+          case 1: m2_superblock<1>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 8), gid, tig); break;
+          case 2: m2_superblock<2>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 8), gid, tig); break;
+          case 3: m2_superblock<3>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 8), gid, tig); break;
+          default: m2_superblock<4>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 8), gid, tig); break;
+        }
+        __syncwarp();   // every lane has read this stage and the table
+        if (sb + kM2Stages < nsb) issue(sb + kM2Stages);
+      }
+    }
+    // ---- epilogue ----
+    if (MODE == 1) {
+      __syncthreads();   // activation buffers are free: the up warps hand their tile to the gate warps
+      float* ex = reinterpret_cast<float*>(m2_smem + L::xq) + slab * (16 * 32 + 32);
+      if (mat == 1) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          if (t < ntiles)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ex[(t * 4 + i) * 32 + lane] = acc[t][i];
+      }
+      __syncthreads();
+      if (mat == 0) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          if (t < ntiles)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int tok = 8 * t + 2 * tig + (i & 1);
+            const int j   = row_base + gid + 8 * (i >> 1);
+            if (tok < nt && j < p.N && ok) {
+              const float u = ex[(t * 4 + i) * 32 + lane];
+              float v = acc[t][i];
+              v = (v / (1.0f + expf(-v))) * u;
+              if (p.round_bf16) v = __bfloat162float(__float2bfloat16_rn(v));
+              static_cast<float*>(p.dst)[static_cast<size_t>(beg + t0 + tok) * p.N + j] = v;
+            }
+          }
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int tok = 8 * t + 2 * tig + (i & 1);
+          const int j   = row_base + gid + 8 * (i >> 1);
+          if (tok < nt && j < p.N && ok) {
+            if (MODE == 2) {
+              const int srow = p.list[beg + t0 + tok] / p.S;
+              store_scalar(static_cast<YT*>(p.dst) + static_cast<size_t>(srow) * p.ld_dst + j, acc[t][i]);
+            } else {
+              static_cast<float*>(p.dst)[static_cast<size_t>(beg + t0 + tok) * p.N + j] = acc[t][i];
+            }
+          }
+        }
+    }
+  }
+}
+
+template <int MODE, class YT>
+static cudaError_t launch_grouped_mma2(const MmaParams& p, int groups, cudaStream_t st) {
+  using L = M2Layout<MODE>;
+  auto kern = grouped_mma2_q4k_kernel<MODE, YT>;
+  static thread_local bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::total);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  dim3 grid((p.N + L::kRowsPerCta - 1) / L::kRowsPerCta, groups);
+  kern<<<grid, kM2Warps * 32, L::total, st>>>(p);
   return cudaGetLastError();
 }
 
@@ -304,6 +646,7 @@ __global__ void quantize_rows_kernel(const SRC* __restrict__ src, size_t ld, int
   const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
   uint8_t* out      = dst + static_cast<size_t>(row) * pitch_bytes;
   ActHdr* gh        = reinterpret_cast<ActHdr*>(out + act_hdr_offset(K));
+  float2* gs        = reinterpret_cast<float2*>(out + act_bytes(K));
   const int gwarp   = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarp   = (gridDim.x * blockDim.x) >> 5;
   for (int base = gwarp * 8; base < nblk; base += nwarp * 8) {
@@ -317,7 +660,10 @@ __global__ void quantize_rows_kernel(const SRC* __restrict__ src, size_t ld, int
     const uint2 packed = quantize_block_lane8(v, d, part, total);
     if (b >= nblk) continue;
     reinterpret_cast<uint2*>(out + static_cast<size_t>(b) * 32)[l4] = packed;
-    if (l4 == 0) gh[b] = ActHdr{d, part, total - part, 0};
+    if (l4 == 0) {
+      gh[b] = ActHdr{d, part, total - part, 0};
+      gs[b] = make_float2(d, __fmul_rn(static_cast<float>(total), d));
+    }
   }
 }
 
@@ -330,6 +676,9 @@ static cudaError_t launch_quantize_rows(const SRC* src, size_t ld, int nrows, in
   return cudaGetLastError();
 }
 
-inline size_t act_row_pitch(size_t K) { return (act_bytes(K) + 255) & ~size_t(255); }
+// Row layout of the quantized activation rows: the reference staging layout (int8 xq[K], at
+// align16(K) one {d, sum_lo, sum_hi, pad} per 32) followed by one float2 {d, d * block sum}
+// per 32, the form the tile kernels consume.
+inline size_t act_row_pitch(size_t K) { return (act_bytes(K) + 8 * (K / 32) + 255) & ~size_t(255); }
 
 }  // namespace kdnn
