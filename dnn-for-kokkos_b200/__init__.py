@@ -38,7 +38,7 @@ EXPORTS = [
     "kdnn_b200_quantize_act_q8",
     "kdnn_b200_unit_dots", "kdnn_b200_gemm_workspace_bytes", "kdnn_b200_quant_gemm",
     "kdnn_b200_moe_route", "kdnn_b200_moe_workspace_bytes", "kdnn_b200_moe_ffn",
-    "kdnn_b200_residual_rmsnorm",
+    "kdnn_b200_residual_rmsnorm", "kdnn_b200_dequant_to_dense",
 ]
 
 
@@ -87,6 +87,8 @@ def _load() -> C.CDLL:
                                       C.POINTER(WeightTableC), C.c_void_p, C.c_void_p, C.c_size_t,
                                       C.c_void_p, C.c_size_t, C.c_int, C.c_size_t, C.c_size_t,
                                       C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_dequant_to_dense.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
+                                               C.c_size_t, C.c_int, C.c_void_p]
     lib.kdnn_b200_residual_rmsnorm.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p,
                                                C.c_size_t, C.c_size_t, C.c_size_t, C.c_float, C.c_int, C.c_void_p]
     return lib
@@ -240,6 +242,20 @@ def quant_gemm(X: torch.Tensor, w: QuantWeight, Y: torch.Tensor, workspace: torc
                                   _scalar(X), Y.data_ptr(), Y.stride(0), _scalar(Y),
                                   workspace.data_ptr(), workspace.numel(), _stream())
     _check(rc, "quant_gemm")
+
+
+def dequant_to_dense(w: QuantWeight, Y: torch.Tensor) -> None:
+    """Y[rows, cols] = Scalar(dequant(W)) (Gguf::dequant_to_dense, src/KokkosDNN_GGUF.hpp:2839-2934)."""
+    if tuple(Y.shape) != (w.rows, w.cols):
+        raise ValueError("dequant_to_dense: dimension mismatch")
+    _quant_check(w, "dequant_to_dense")
+    if w.rows == 0 or w.cols == 0:
+        return
+    if Y.stride(1) != 1:
+        raise ValueError("dequant_to_dense: Y must be LayoutRight")
+    rc = lib.kdnn_b200_dequant_to_dense(w.dtype, w.data.data_ptr(), w.rows, w.cols, Y.data_ptr(), Y.stride(0),
+                                        _scalar(Y), _stream())
+    _check(rc, "dequant_to_dense")
 
 
 def moe_route(logits: torch.Tensor, expert_bias: Optional[torch.Tensor], top_k: int, norm_topk: bool,

@@ -30,6 +30,8 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
                            size_t S, void* Y, size_t ldy, int ys, size_t e_first, size_t e_count,
                            void* ws, cudaStream_t st);
 int moe_take_status();
+cudaError_t dequant_launch(uint32_t dt, const void* w, size_t rows, size_t cols, void* y, size_t ldy, int ys,
+                           cudaStream_t st);
 cudaError_t residual_rmsnorm_launch(const void* h, size_t ldh, const float* y, size_t ldy, void* out,
                                     size_t ldo, size_t T, size_t H, float eps, int scalar, cudaStream_t st);
 }  // namespace kdnn
@@ -221,6 +223,22 @@ int kdnn_b200_residual_rmsnorm(const void* h, size_t ldh, const float* y, size_t
   return cuda_result(kdnn::residual_rmsnorm_launch(h, ldh, y, ldy, out, ldo, T, H, eps, scalar,
                                                    static_cast<cudaStream_t>(stream)),
                      "residual_rmsnorm");
+}
+
+int kdnn_b200_dequant_to_dense(uint32_t ggml_type, const void* w, size_t rows, size_t cols, void* y, size_t ldy,
+                               int y_scalar, void* stream) {
+  if (!scalar_ok(y_scalar)) return fail(KDNN_ERR_INVALID, "dequant_to_dense: bad scalar");
+  if (ggml_type != KDNN_GGML_Q4_K && ggml_type != KDNN_GGML_Q5_K && ggml_type != KDNN_GGML_Q6_K &&
+      ggml_type != KDNN_GGML_Q8_0)
+    return fail(KDNN_ERR_INVALID, "dequant_to_dense: unsupported dtype");
+  if (rows == 0 || cols == 0) return KDNN_OK;
+  if (!kdnn::block_aligned(ggml_type, cols))
+    return fail(KDNN_ERR_INVALID, "dequant_to_dense: cols must be a whole number of blocks");
+  if (ldy < cols || !w || !y || rows > static_cast<size_t>(INT_MAX) || cols > static_cast<size_t>(INT_MAX))
+    return fail(KDNN_ERR_INVALID, "dequant_to_dense: dimension mismatch");
+  return cuda_result(kdnn::dequant_launch(ggml_type, w, rows, cols, y, ldy, y_scalar,
+                                          static_cast<cudaStream_t>(stream)),
+                     "dequant_to_dense");
 }
 
 }  // extern "C"

@@ -16,6 +16,7 @@
 #include "kdnn_mma.cuh"
 #include "kdnn_umma.cuh"
 
+#include <limits.h>
 #include <stdlib.h>
 
 namespace kdnn {
@@ -164,15 +165,34 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_slots, in
     offs[e_count] = run;
   }
   __syncthreads();
-  // stable placement: expert e's run is filled by one thread scanning slot ids upward
-  for (int e = threadIdx.x; e < e_count; e += blockDim.x) {
-    if (counts[e] == 0) continue;
-    int c = cursor[e];
-    for (int i = 0; i < n_slots; ++i)
-      if (idx[i] - e_first == e) {
-        list[c] = i;
-        pos[i]  = c++;
+  // stable placement: a warp owns experts warp, warp + nwarps, ... and sweeps the slot ids
+  // upward 32 at a time, four of its experts per sweep (one coalesced load, one ballot per
+  // expert, ranks from the ballot's population count below the lane)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const unsigned below = (1u << lane) - 1u;
+  for (int e0 = warp; e0 < e_count; e0 += 4 * nwarps) {
+    int ex[4], c[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      ex[j] = e0 + j * nwarps;
+      c[j]  = ex[j] < e_count ? cursor[ex[j]] : 0;
+      if (ex[j] >= e_count || counts[ex[j]] == 0) ex[j] = INT_MIN;   // matches no slot
+    }
+    if (ex[0] < 0 && ex[1] < 0 && ex[2] < 0 && ex[3] < 0) continue;
+    for (int base = 0; base < n_slots; base += 32) {
+      const int i = base + lane;
+      const int v = i < n_slots ? idx[i] - e_first : -1;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const unsigned m = __ballot_sync(0xFFFFFFFFu, v == ex[j]);
+        if (v == ex[j]) {
+          const int ps = c[j] + __popc(m & below);
+          list[ps] = i;
+          pos[i]   = ps;
+        }
+        c[j] += __popc(m);
       }
+    }
   }
   for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
     const int e = idx[i] - e_first;

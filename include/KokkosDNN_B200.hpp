@@ -101,6 +101,21 @@ void quant_gemv(const ExecSpace& space, const XView& x, const QuantWeight& w, co
   fallback();
 }
 
+// Gguf::dequant_to_dense, src/KokkosDNN_GGUF.hpp:2839-2934.
+template <class ExecSpace, class QuantWeight, class YView>
+void dequant_to_dense(const ExecSpace& space, const QuantWeight& w, const YView& Y) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(Y.data())>::type>::type;
+  if (Y.extent(0) != w.rows || Y.extent(1) != w.cols)
+    throw std::invalid_argument("dequant_to_dense: dimension mismatch");
+  if (w.rows == 0 || w.cols == 0) return;
+  if (scalar_tag<Scalar>() < 0 || Y.stride(1) != 1)
+    throw std::invalid_argument("dequant_to_dense: Y must be a LayoutRight float or bhalf_t view");
+  const int rc = kdnn_b200_dequant_to_dense(static_cast<std::uint32_t>(w.dtype), w.data.data(), w.rows, w.cols,
+                                            Y.data(), Y.stride(0), scalar_tag<Scalar>(),
+                                            StreamOf<ExecSpace>::get(space));
+  throw_on_error(rc, "dequant_to_dense");
+}
+
 // Gguf::quant_gemm, src/KokkosDNN_GGUF.hpp:2564-2593 (int8 activations per row).
 // `workspace` is a caller-owned byte view of at least kdnn_b200_gemm_workspace_bytes(M, K).
 template <class ExecSpace, class XView, class QuantWeight, class YView, class WsView, class Fallback>

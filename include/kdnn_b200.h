@@ -190,6 +190,17 @@ int kdnn_b200_moe_ffn(const void* X, size_t ldx, size_t T, int x_scalar,
 int kdnn_b200_residual_rmsnorm(const void* h, size_t ldh, const float* y, size_t ldy, void* out, size_t ldo,
                                size_t T, size_t H, float eps, int scalar, void* stream);
 
+/* Y[r, k] = Scalar(dequant(W[r, k])): replaces KokkosDNN::Gguf::dequant_to_dense,
+ * src/KokkosDNN_GGUF.hpp:2839-2934 (block formulas :300-384). Types Q4_K, Q5_K, Q6_K, Q8_0; fp32 outputs are
+ * bit-identical to the reference's (same association, no fused multiply-add), bf16 outputs are their
+ * round-to-nearest-even.
+ *   w [rows * row_bytes] packed rows; y [rows, cols] Scalar with pitch ldy (elements, >= cols).
+ * KDNN_ERR_INVALID for an unknown type, cols that are not a whole number of blocks (256 for the K-quants,
+ * 32 for Q8_0) or ldy < cols (the reference throws std::invalid_argument for those); zero extents return
+ * KDNN_OK without a launch. */
+int kdnn_b200_dequant_to_dense(uint32_t ggml_type, const void* w, size_t rows, size_t cols, void* y, size_t ldy,
+                               int y_scalar, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
