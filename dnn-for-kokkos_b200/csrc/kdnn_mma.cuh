@@ -49,6 +49,7 @@ struct MmaParams {
   size_t ld_dst;
   int round_bf16;
   int* status;
+  int ablate;            // debug: 1 skip the MMA loop, 2 skip the scale table, 4 skip activation staging
 };
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -301,6 +302,8 @@ static cudaError_t launch_grouped_mma(const MmaParams& p, int groups, cudaStream
 //    and registers and two CTAs fit on an SM;
 //  * up to 32 activation rows per pass (1..4 n8 tiles chosen at run time), staged in
 //    512-element chunks with cp.async, double buffered: one __syncthreads per chunk;
+//    the packed weight rows come the same way (16-byte cp.async pieces into a two-stage
+//    ring per warp), awaited together with the activation chunk;
 //  * the 6-bit scales of a super-block are expanded once per warp (one lane per row and
 //    half) into a per-warp table instead of by every lane that needs them;
 //  * packed bytes are read 64 bits at a time in a K order that both operands share
@@ -439,7 +442,6 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
 
   const uint32_t xq_u32 = smem_u32(m2_smem + L::xq), xs_u32 = smem_u32(m2_smem + L::xs);
   long long* rowp = reinterpret_cast<long long*>(m2_smem + L::rowp);
-  const uint32_t bar_u32 = smem_u32(m2_smem + L::bars) + warp * (kM2Stages * 8);
   const uint32_t tab_u32 = smem_u32(m2_smem + L::tab) + warp * (16 * 4 * 16);
   const uint32_t ring_u32 = smem_u32(m2_smem + L::ring) + warp * (kM2Stages * kM2StageBytes);
 
@@ -447,28 +449,29 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
   const int slab = MODE == 1 ? (warp >> 1) : warp;
   const int row_base = blockIdx.x * L::kRowsPerCta + slab * 16;
   const int nsb  = p.K / 256;
-  // lanes 0-15 copy one packed row each (rows past the end re-read the last row)
-  const uint8_t* src = nullptr;
-  if (lane < 16)
-    src = reinterpret_cast<const uint8_t*>((mat == 0 ? p.w0 : p.w1)[p.g_first + g]) +
-          static_cast<size_t>(min(row_base + lane, p.N - 1)) * p.row_bytes;
-
-  int issued = 0, consumed = 0;
-  bool ok = true;
-  auto issue = [&](int sb) {   // whole warp
-    const int s = issued % kM2Stages;
-    ++issued;
-    const uint32_t bar = bar_u32 + s * 8;
-    if (lane == 0) mbar_expect_tx(bar, 144u * 16u);
-    __syncwarp();
-    if (lane < 16) bulk_g2s(ring_u32 + s * kM2StageBytes + lane * kM2WPitch, src + static_cast<size_t>(sb) * 144, 144u, bar);
-  };
-  if (lane == 0) {
-    for (int s = 0; s < kM2Stages; ++s) mbar_init(bar_u32 + s * 8, 1);
-    fence_barrier_init();
-    fence_proxy_async();
+  // Weight stages are filled with 16-byte cp.async pieces (a stage is 16 rows x 144 bytes = 144 pieces,
+  // spread over the lanes): bulk copies of 144 bytes each were limited by their per-copy cost.
+  // Rows past the end re-read the last row.
+  const uint8_t* wbase = reinterpret_cast<const uint8_t*>((mat == 0 ? p.w0 : p.w1)[p.g_first + g]);
+  uint32_t psrc[5], pdst[5];   // byte offsets of this lane's pieces: source (from wbase), destination (stage 0)
+#pragma unroll
+  for (int j = 0; j < 5; ++j) {
+    const int pc = lane + 32 * j;                      // piece index, valid below 144
+    const int r = (pc * 7282) >> 16, c = pc - 9 * r;   // pc / 9 for pc < 160
+    psrc[j] = static_cast<uint32_t>(min(row_base + min(r, 15), p.N - 1)) * static_cast<uint32_t>(p.row_bytes) + c * 16;
+    pdst[j] = ring_u32 + min(r, 15) * kM2WPitch + c * 16;
   }
-  __syncwarp();
+  // Stage sb % 2 holds super-block sb. Copies are committed per stage and per activation chunk and
+  // awaited all together at the top of every chunk (a chunk is two super-blocks, the ring two stages),
+  // so what is in flight during a chunk's arithmetic is exactly the next chunk's bytes.
+  auto issue = [&](int sb) {   // whole warp
+    const uint32_t so = (sb & 1) * kM2StageBytes;
+    const uint8_t* srcb = wbase + static_cast<size_t>(sb) * 144;
+#pragma unroll
+    for (int j = 0; j < 5; ++j)
+      if (j < 4 || lane < 16) cp_async16(pdst[j] + so, srcb + psrc[j], true);
+    cp_async_commit();
+  };
 
   const int nchunk = (p.K + kM2KC - 1) / kM2KC;
   const size_t scale_off = act_bytes(static_cast<size_t>(p.K));
@@ -508,8 +511,7 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
     }
     __syncthreads();
     stage_chunk(0);
-    if (ok)
-      for (int q = 0; q < kM2Stages && q < nsb; ++q) issue(q);
+    for (int q = 0; q < kM2Stages && q < nsb; ++q) issue(q);
 
     float acc[4][4];
 #pragma unroll
@@ -517,25 +519,17 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
 
-    // A warp whose bounded wait gives up stops computing but keeps meeting the others at
-    // every barrier, so nobody is left waiting for it.
     for (int c = 0; c < nchunk; ++c) {
       cp_async_wait_all();
       __syncthreads();   // chunk c has landed for everybody; everybody is done with chunk c - 1
-      if (c + 1 < nchunk) stage_chunk(c + 1);
+      if (c + 1 < nchunk && !(p.ablate & 4)) stage_chunk(c + 1);
       const uint32_t xb = xq_u32 + (c & 1) * (kM2NT * kM2XPitch);
       const uint32_t sbuf = xs_u32 + (c & 1) * ((kM2KC / 32) * kM2NT * 8);
       const int sb_first = c * (kM2KC / 256), sb_last = min(nsb, sb_first + kM2KC / 256);
-      for (int sb = sb_first; sb < sb_last && ok; ++sb) {
-        const int s = consumed % kM2Stages;
-        if (!mbar_wait_bounded(bar_u32 + s * 8, (consumed / kM2Stages) & 1)) {
-          ok = false;
-          if (lane == 0) atomicExch(p.status, KDNN_ERR_DEVICE_WAIT);
-          break;
-        }
-        ++consumed;
+      for (int sb = sb_first; sb < sb_last; ++sb) {
+        const int s = sb & 1;
         const uint32_t st = ring_u32 + s * kM2StageBytes;
-        {  // expand the 6-bit scales: lane = (row, half) -> {sw0, mw0, sw1, mw1} pairs of its four sub-blocks
+        if (!(p.ablate & 2)) {  // expand the 6-bit scales: lane = (row, half) -> {sw0, mw0, sw1, mw1} pairs of its four sub-blocks
           const int r = lane >> 1, half = lane & 1;
           const int4 h = lds128_g(st + r * kM2WPitch);
           const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
@@ -557,7 +551,7 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
         }
         __syncwarp();
         const int blk0 = (sb - sb_first) * 8;   // first 32-block of this super-block inside the chunk
-        switch (ntiles) {
+        if (!(p.ablate & 1)) switch (ntiles) {
           case 1: m2_superblock<1>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 8), gid, tig); break;
           case 2: m2_superblock<2>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 8), gid, tig); break;
           case 3: m2_superblock<3>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 8), gid, tig); break;
@@ -587,7 +581,7 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
           for (int i = 0; i < 4; ++i) {
             const int tok = 8 * t + 2 * tig + (i & 1);
             const int j   = row_base + gid + 8 * (i >> 1);
-            if (tok < nt && j < p.N && ok) {
+            if (tok < nt && j < p.N) {
               const float u = ex[(t * 4 + i) * 32 + lane];
               float v = acc[t][i];
               v = (v / (1.0f + expf(-v))) * u;
@@ -603,7 +597,7 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
         for (int i = 0; i < 4; ++i) {
           const int tok = 8 * t + 2 * tig + (i & 1);
           const int j   = row_base + gid + 8 * (i >> 1);
-          if (tok < nt && j < p.N && ok) {
+          if (tok < nt && j < p.N) {
             if (MODE == 2) {
               const int srow = p.list[beg + t0 + tok] / p.S;
               store_scalar(static_cast<YT*>(p.dst) + static_cast<size_t>(srow) * p.ld_dst + j, acc[t][i]);
@@ -627,7 +621,10 @@ static cudaError_t launch_grouped_mma2(const MmaParams& p, int groups, cudaStrea
     configured = true;
   }
   dim3 grid((p.N + L::kRowsPerCta - 1) / L::kRowsPerCta, groups);
-  kern<<<grid, kM2Warps * 32, L::total, st>>>(p);
+  MmaParams q = p;
+  static const int ablate = [] { const char* e = getenv("KDNN_TILE_ABLATE"); return e ? atoi(e) : 0; }();
+  q.ablate = ablate;
+  kern<<<grid, kM2Warps * 32, L::total, st>>>(q);
   return cudaGetLastError();
 }
 
