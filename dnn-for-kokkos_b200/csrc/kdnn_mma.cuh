@@ -317,7 +317,7 @@ constexpr int kM2NT      = 32;                 // activation rows per pass
 constexpr int kM2KC      = 512;                // activation elements per staged chunk
 constexpr int kM2XPitch  = kM2KC + 32;         // int8 row pitch: 8 words mod 32 (conflict-free 64-bit B loads)
 constexpr int kM2WPitch  = 160;                // packed row pitch in a weight stage (same property)
-constexpr int kM2Stages  = 2;                  // weight ring depth per warp, in super-blocks
+constexpr int kM2Stages  = 3;                  // weight ring depth per warp, in super-blocks
 constexpr int kM2StageBytes = 16 * kM2WPitch;
 constexpr int kM2MagicI  = 0x4B400000;
 constexpr float kM2MagicF = 12582912.0f;
@@ -357,6 +357,7 @@ __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, bool va
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 template <int MODE>
 struct M2Layout {
@@ -461,15 +462,18 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
     psrc[j] = static_cast<uint32_t>(min(row_base + min(r, 15), p.N - 1)) * static_cast<uint32_t>(p.row_bytes) + c * 16;
     pdst[j] = ring_u32 + min(r, 15) * kM2WPitch + c * 16;
   }
-  // Stage sb % 2 holds super-block sb. Copies are committed per stage and per activation chunk and
-  // awaited all together at the top of every chunk (a chunk is two super-blocks, the ring two stages),
-  // so what is in flight during a chunk's arithmetic is exactly the next chunk's bytes.
+  // Stage sb % 3 holds super-block sb. Every call commits exactly one group (an empty one past the
+  // last super-block), so at the top of chunk c the groups still allowed to be pending are always the
+  // same: the one stage requested last. What is in flight during a chunk's arithmetic is the next
+  // chunk's bytes plus one stage of the chunk after it.
   auto issue = [&](int sb) {   // whole warp
-    const uint32_t so = (sb & 1) * kM2StageBytes;
-    const uint8_t* srcb = wbase + static_cast<size_t>(sb) * 144;
+    if (sb < nsb) {
+      const uint32_t so = (sb % kM2Stages) * kM2StageBytes;
+      const uint8_t* srcb = wbase + static_cast<size_t>(sb) * 144;
 #pragma unroll
-    for (int j = 0; j < 5; ++j)
-      if (j < 4 || lane < 16) cp_async16(pdst[j] + so, srcb + psrc[j], true);
+      for (int j = 0; j < 5; ++j)
+        if (j < 4 || lane < 16) cp_async16(pdst[j] + so, srcb + psrc[j], true);
+    }
     cp_async_commit();
   };
 
@@ -511,7 +515,7 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
     }
     __syncthreads();
     stage_chunk(0);
-    for (int q = 0; q < kM2Stages && q < nsb; ++q) issue(q);
+    for (int q = 0; q < kM2Stages; ++q) issue(q);
 
     float acc[4][4];
 #pragma unroll
@@ -520,15 +524,14 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
       for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
 
     for (int c = 0; c < nchunk; ++c) {
-      cp_async_wait_all();
+      cp_async_wait_but_one();
       __syncthreads();   // chunk c has landed for everybody; everybody is done with chunk c - 1
-      if (c + 1 < nchunk && !(p.ablate & 4)) stage_chunk(c + 1);
+      if (c + 1 < nchunk && !(p.ablate & 4)) stage_chunk(c + 1); else cp_async_commit();
       const uint32_t xb = xq_u32 + (c & 1) * (kM2NT * kM2XPitch);
       const uint32_t sbuf = xs_u32 + (c & 1) * ((kM2KC / 32) * kM2NT * 8);
       const int sb_first = c * (kM2KC / 256), sb_last = min(nsb, sb_first + kM2KC / 256);
       for (int sb = sb_first; sb < sb_last; ++sb) {
-        const int s = sb & 1;
-        const uint32_t st = ring_u32 + s * kM2StageBytes;
+        const uint32_t st = ring_u32 + (sb % kM2Stages) * kM2StageBytes;
         if (!(p.ablate & 2)) {  // expand the 6-bit scales: lane = (row, half) -> {sw0, mw0, sw1, mw1} pairs of its four sub-blocks
           const int r = lane >> 1, half = lane & 1;
           const int4 h = lds128_g(st + r * kM2WPitch);
@@ -558,7 +561,7 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
           default: m2_superblock<4>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 8), gid, tig); break;
         }
         __syncwarp();   // every lane has read this stage and the table
-        if (sb + kM2Stages < nsb) issue(sb + kM2Stages);
+        issue(sb + kM2Stages);
       }
     }
     // ---- epilogue ----
