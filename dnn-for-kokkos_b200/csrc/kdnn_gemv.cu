@@ -787,7 +787,7 @@ struct XregParams {
   const void* x;
   void* y;
   uint8_t* scratch;
-  int rows, K, row_bytes, nsb;
+  int rows, K, row_bytes, nsb, nitems;
   int nchunks, csb;   // chunks per row (<= 16) and super-blocks per chunk (<= 16; the last chunk may hold fewer)
   int ngroups;        // ceil(rows / RW)
   int gq, gr;         // ngroups / grid and ngroups % grid
@@ -987,6 +987,176 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
         if (r < nrow && !(p.ablate & 1)) {
           const float v = q4k_half_dot(ring_u32 + s * kStage + r * kWideRowPitch + lane_blk, qoff, half, xg, dxv, dsv);
           acc[r] = active ? v : 0.f;
+        }
+      }
+      const float v = reduce_rows<RW>(acc, lane);
+      if (lane < nrow) {
+        const int lrow = lrow0 + lane;
+        if (p.nchunks == 1) store_scalar(y + c0 * RW + lrow, v);
+        else part[lrow * p.nchunks + chunk] = v;
+      }
+      __syncwarp();   // every lane has read this stage
+      issue(s);
+      __syncwarp();
+    }
+    phase ^= 1u;
+    first_round = false;
+  }
+  if (!ok && lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
+  KDNN_TRACE(6);
+  if (p.nchunks > 1) {
+    __syncthreads();
+    const int nloc = min(G * RW, p.rows - c0 * RW);
+    for (int r = threadIdx.x; r < nloc; r += blockDim.x) {
+      float v = 0.f;
+      for (int j = 0; j < p.nchunks; ++j) v += part[r * p.nchunks + j];
+      store_scalar(y + c0 * RW + r, v);
+    }
+  }
+}
+
+// The same structure for the formats evaluated per 64-element item (Q6_K, Q8_0): a warp is
+// bound to one 2048-element chunk, lane = item, and the item's activation window (64 int8,
+// block scales, for Q6_K the 32 * partial sums) stays in 20-24 registers.
+template <uint32_t DT, class XT, class YT, int RW, int STAGES>
+__global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(const XregParams p) {
+  constexpr int kRowPitch = chunk_bytes_full<DT>();
+  constexpr int kStage = RW * kRowPitch;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int4* xg      = reinterpret_cast<int4*>(smem);
+  float4* hd    = reinterpret_cast<float4*>(smem + static_cast<size_t>(p.nitems) * 64);
+  int4* hs      = reinterpret_cast<int4*>(smem + static_cast<size_t>(p.nitems) * 80);
+  size_t off    = (static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80) + 127) & ~size_t(127);
+  const uint32_t bar_u32 = smem_u32(smem + off) + warp * (STAGES * 8);
+  off += kGemvMaxWarps * STAGES * 8;
+  int* s_next = reinterpret_cast<int*>(smem + off);   // [chunk] next local row group
+  off += 128;
+  float* part = reinterpret_cast<float*>(smem + off);  // [local row][chunk]
+  off += (static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127);
+  const uint32_t ring_u32 = smem_u32(smem + off) + warp * (STAGES * kStage);
+  KDNN_TRACE(0);
+
+  // even contiguous split of the row groups over the CTAs (quotient and remainder from the host)
+  const int c0 = static_cast<int>(blockIdx.x) * p.gq + min(static_cast<int>(blockIdx.x), p.gr);
+  const int c1 = c0 + p.gq + (static_cast<int>(blockIdx.x) < p.gr ? 1 : 0);
+  const int G  = c1 - c0;                       // row groups of this CTA = units per chunk
+  const int widx = static_cast<int>((static_cast<uint32_t>(warp) * p.nch_magic) >> 16), chunk = warp - widx * p.nchunks;
+  const int items = min(kChunkItems, p.nitems - chunk * kChunkItems);
+  const uint32_t cb = chunk_bytes<DT>(items);
+  if (threadIdx.x < p.nchunks) s_next[threadIdx.x] = p.wpc;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + s * 8, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncwarp();
+
+  // ---- producer (state uniform across the warp; lane 0 issues the copies) ----
+  int m_group[STAGES];
+  const uint8_t* wsrc = p.w + static_cast<size_t>(chunk) * kRowPitch;
+  const bool contiguous = p.nchunks == 1 && p.row_bytes == kRowPitch && cb == static_cast<uint32_t>(kRowPitch);
+  auto issue_unit = [&](int s, int u) {
+    m_group[s]     = u;
+    const int row0 = (c0 + u) * RW;
+    const int nrow = min(RW, p.rows - row0);
+    if (lane == 0) {
+      const uint32_t bar = bar_u32 + s * 8;
+      mbar_expect_tx(bar, cb * nrow);
+      const uint8_t* src = wsrc + static_cast<size_t>(row0) * p.row_bytes;
+      const uint32_t dst = ring_u32 + s * kStage;
+      if (contiguous) {   // one chunk per row and full rows: the unit is one run of bytes
+        bulk_g2s(dst, src, cb * nrow, bar);
+      } else {
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+          if (r < nrow) bulk_g2s(dst + r * kRowPitch, src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
+      }
+    }
+  };
+  // The first unit of every warp is fixed and requested at once, before the CTA has even
+  // synchronised. Only this one stage goes out before the dependency: a deeper burst ahead
+  // of the activation loads makes those loads (a few KB that everything waits for) queue
+  // behind megabytes of weights. The rest of the ring is requested right after the
+  // activation loads have been issued.
+  bool pdone = widx >= G;
+  if (!pdone) issue_unit(0, widx); else m_group[0] = -1;
+  __syncthreads();   // the chunk counters are set
+  int pu = 0, pnext = 0x7fffffff;
+  auto draw = [&]() {
+    int v = 0;
+    if (lane == 0) v = atomicAdd(&s_next[chunk], 1);
+    pnext = __shfl_sync(0xFFFFFFFFu, v, 0);
+  };
+  auto advance = [&]() {
+    pu = pnext;
+    if (pu >= G) pdone = true; else draw();
+  };
+  auto issue = [&](int s) {
+    if (pdone) {
+      m_group[s] = -1;
+      return;
+    }
+    issue_unit(s, pu);
+    advance();
+  };
+  if (!pdone) {
+    draw();
+    advance();
+  }
+  KDNN_TRACE(1);
+  pdl_launch_dependents();
+  pdl_wait();
+  KDNN_TRACE(2);
+  // ring stages 1 .. early-1 are requested once the activation loads are in flight, the
+  // rest after the quantized window has been written
+  stage_activations<DT, XT>(static_cast<const XT*>(p.x), p.K, p.nitems, xg, hd, hs, blockIdx.x == 0 ? p.scratch : nullptr, [&]() {
+#pragma unroll
+    for (int s = 1; s < STAGES; ++s)
+      if (s < p.early) issue(s);
+  });
+  KDNN_TRACE(7);
+#pragma unroll
+  for (int s = 1; s < STAGES; ++s)
+    if (s >= p.early) issue(s);
+  __syncthreads();
+
+  // ---- this lane's activation window: registers for the rest of the kernel ----
+  const bool active = lane < items;
+  const int item = chunk * kChunkItems + (active ? lane : 0);
+  ItemX x;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) x.g[g] = xg[static_cast<size_t>(g) * p.nitems + item];
+  x.hd = hd[item];
+  x.hs = make_int4(0, 0, 0, 0);
+  if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
+  KDNN_TRACE(3);
+
+  YT* y = static_cast<YT*>(p.y);
+  uint32_t phase = 0;
+  bool ok = true, more = true, first_round = true;
+  while (more) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      if (!more) break;
+      if (m_group[s] < 0) {
+        more = false;
+        break;
+      }
+      if (!mbar_wait_bounded(bar_u32 + s * 8, phase)) {
+        ok = more = false;
+        break;
+      }
+      if (first_round && s == 0) KDNN_TRACE(4);
+      const int lrow0 = m_group[s] * RW;
+      const int nrow  = min(RW, p.rows - (c0 * RW + lrow0));
+      float acc[RW];
+#pragma unroll
+      for (int r = 0; r < RW; ++r) {
+        acc[r] = 0.f;
+        if (r < nrow && !(p.ablate & 1)) {
+          if (active) acc[r] = item_dot<DT>(ring_u32 + s * kStage + r * kRowPitch, lane, x);
         }
       }
       const float v = reduce_rows<RW>(acc, lane);
@@ -1308,6 +1478,59 @@ static bool launch_q4k_xreg(const GemvParams& base, cudaStream_t stream, cudaErr
   return true;
 }
 
+// Register-window kernel for the item formats. Returns false when the shape is outside what it covers.
+template <uint32_t DT, class XT, class YT, int RW>
+static bool launch_item_xreg(const GemvParams& base, cudaStream_t stream, cudaError_t& err) {
+  const DeviceInfo& di = device_info();
+  XregParams p{};
+  p.w = base.w; p.x = base.x; p.y = base.y; p.scratch = base.scratch;
+  p.rows = base.rows; p.K = base.K; p.row_bytes = base.row_bytes;
+  p.nitems  = base.nitems;
+  p.nchunks = base.nchunks;
+  if (p.nchunks > kGemvMaxWarps) return false;
+  p.ngroups = (p.rows + RW - 1) / RW;
+  p.wpc     = kGemvMaxWarps / p.nchunks;
+  const int warps = p.wpc * p.nchunks;
+  const int grid  = max(1, min(di.sms, p.ngroups));
+  p.gq = p.ngroups / grid;
+  p.gr = p.ngroups % grid;
+  p.nch_magic = static_cast<uint32_t>((65536 + p.nchunks - 1) / p.nchunks);
+  const int gpc   = (p.ngroups + grid - 1) / grid;
+  p.part_floats   = p.nchunks > 1 ? (gpc + 1) * RW * p.nchunks : 0;
+  if (static_cast<size_t>(p.part_floats) * 4 > 32 * 1024) return false;
+  const size_t fixed = ((static_cast<size_t>(p.nitems) * (DT == KDNN_GGML_Q6_K ? 96 : 80) + 127) & ~size_t(127)) + 128 +
+                       ((static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127)) + 128;
+  constexpr int kStage = RW * chunk_bytes_full<DT>();
+  auto smem_for = [&](int st) { return fixed + static_cast<size_t>(kGemvMaxWarps) * st * (8 + kStage); };
+  const int units_per_warp = (gpc + p.wpc - 1) / p.wpc;
+  int stages = env_int("KDNN_GEMV_STAGES", 0);
+  if (stages == 0) stages = 3;
+  stages = max(2, min(4, min(stages, max(2, units_per_warp))));
+  while (stages > 2 && smem_for(stages) > static_cast<size_t>(di.max_smem)) --stages;
+  if (smem_for(stages) > static_cast<size_t>(di.max_smem)) return false;
+  const size_t smem = smem_for(stages);
+  p.trace  = g_trace_buffer;
+  p.ablate = env_int("KDNN_GEMV_ABLATE", 0);
+  p.early  = env_int("KDNN_GEMV_EARLY", 2);
+  using Kern = void (*)(const XregParams);
+  const Kern kern = stages == 2 ? gemv_item_xreg_kernel<DT, XT, YT, RW, 2>
+                  : stages == 3 ? gemv_item_xreg_kernel<DT, XT, YT, RW, 3> : gemv_item_xreg_kernel<DT, XT, YT, RW, 4>;
+  static thread_local bool configured[5] = {};
+  if (!configured[stages]) {
+    err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem);
+    if (err != cudaSuccess) return true;
+    configured[stages] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(warps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = use_pdl() ? 1 : 0;
+  err = cudaLaunchKernelEx(&cfg, kern, p);
+  return true;
+}
+
 template <class XT, class YT>
 static cudaError_t launch_q4k_wide(const GemvParams& base, cudaStream_t stream) {
   const DeviceInfo& di = device_info();
@@ -1390,6 +1613,10 @@ static cudaError_t launch_stream_rw(const GemvParams& p, cudaStream_t stream) {
       if (rw == 1 ? launch_q4k_xreg<XT, YT, 1>(p, stream, err) : launch_q4k_xreg<XT, YT, 2>(p, stream, err)) return err;
     }
     return launch_q4k_wide<XT, YT>(p, stream);
+  }
+  if (DT != KDNN_GGML_Q4_K && !env_int("KDNN_GEMV_ITEM", 0)) {   // register-window kernel for Q6_K / Q8_0
+    cudaError_t err = cudaSuccess;
+    if (rw == 1 ? launch_item_xreg<DT, XT, YT, 1>(p, stream, err) : launch_item_xreg<DT, XT, YT, 2>(p, stream, err)) return err;
   }
   if (rw == 0) rw = p.rows >= 2 ? 2 : 1;
   if (rw >= 4 && DT == KDNN_GGML_Q4_K) return launch_stream<DT, 4, XT, YT>(p, stream);

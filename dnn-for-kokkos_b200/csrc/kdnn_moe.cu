@@ -139,9 +139,11 @@ cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, 
 //   pos[t*S + s]       position of the slot in `list`, or -1 when the slot's expert
 //                      is out of range / not local (it then contributes nothing,
 //                      src/KokkosDNN_GGUF.hpp:2106-2110)
-// One CTA. Order inside an expert's run is by slot id (token-major), as the
-// reference's host-side counting sort produces
-// (models/lfm2_5/KokkosDNN_LFM25Model.hpp:455-486); results do not depend on it.
+// Order inside an expert's run is by slot id (token-major), as the reference's host-side
+// counting sort produces (models/lfm2_5/KokkosDNN_LFM25Model.hpp:455-486); results do not
+// depend on it. Several small CTAs: every CTA counts all slots (shared-memory atomics) and
+// forms the same prefix sums, then places only its own experts -- a warp per expert sweeps
+// the slot ids upward 32 at a time, ranks come from one ballot per sweep step.
 __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_slots, int e_first,
                                 int e_count, int* __restrict__ offs, int* __restrict__ list,
                                 int* __restrict__ pos) {
@@ -155,46 +157,44 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_slots, in
     if (e >= 0 && e < e_count) atomicAdd(&counts[e], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {   // exclusive prefix sums by one warp, 32 experts per step
     int run = 0;
-    for (int e = 0; e < e_count; ++e) {
-      offs[e]   = run;
-      cursor[e] = run;
-      run += counts[e];
+    for (int e0 = 0; e0 < e_count; e0 += 32) {
+      const int e = e0 + static_cast<int>(threadIdx.x);
+      const int c = e < e_count ? counts[e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+        if (static_cast<int>(threadIdx.x) >= o) incl += v;
+      }
+      if (e < e_count) {
+        cursor[e] = run + incl - c;
+        if (blockIdx.x == 0) offs[e] = run + incl - c;
+      }
+      run += __shfl_sync(0xFFFFFFFFu, incl, 31);
     }
-    offs[e_count] = run;
+    if (blockIdx.x == 0 && threadIdx.x == 0) offs[e_count] = run;
   }
   __syncthreads();
-  // stable placement: a warp owns experts warp, warp + nwarps, ... and sweeps the slot ids
-  // upward 32 at a time, four of its experts per sweep (one coalesced load, one ballot per
-  // expert, ranks from the ballot's population count below the lane)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const unsigned below = (1u << lane) - 1u;
-  for (int e0 = warp; e0 < e_count; e0 += 4 * nwarps) {
-    int ex[4], c[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      ex[j] = e0 + j * nwarps;
-      c[j]  = ex[j] < e_count ? cursor[ex[j]] : 0;
-      if (ex[j] >= e_count || counts[ex[j]] == 0) ex[j] = INT_MIN;   // matches no slot
-    }
-    if (ex[0] < 0 && ex[1] < 0 && ex[2] < 0 && ex[3] < 0) continue;
+  for (int e = blockIdx.x * nwarps + warp; e < e_count; e += gridDim.x * nwarps) {
+    if (counts[e] == 0) continue;
+    int c = cursor[e];
     for (int base = 0; base < n_slots; base += 32) {
       const int i = base + lane;
-      const int v = i < n_slots ? idx[i] - e_first : -1;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const unsigned m = __ballot_sync(0xFFFFFFFFu, v == ex[j]);
-        if (v == ex[j]) {
-          const int ps = c[j] + __popc(m & below);
-          list[ps] = i;
-          pos[i]   = ps;
-        }
-        c[j] += __popc(m);
+      const bool hit = i < n_slots && idx[i] - e_first == e;
+      const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
+      if (hit) {
+        const int ps = c + __popc(m & below);
+        list[ps] = i;
+        pos[i]   = ps;
       }
+      c += __popc(m);
     }
   }
-  for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_slots; i += gridDim.x * blockDim.x) {
     const int e = idx[i] - e_first;
     if (e < 0 || e >= e_count) pos[i] = -1;
   }
@@ -271,8 +271,9 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
   ActItem* actq = reinterpret_cast<ActItem*>(b + L.actq);
   float* out = reinterpret_cast<float*>(b + L.out);
   const int n_slots = static_cast<int>(T * S);
-  moe_sort_kernel<<<1, 1024, 2 * (e_count + 1) * sizeof(int), st>>>(idx, n_slots, (int)e_first,
-                                                                     (int)e_count, offs, list, pos);
+  const int sort_ctas = static_cast<int>(e_count < 4 ? 1 : (e_count + 3) / 4 > 64 ? 64 : (e_count + 3) / 4);
+  moe_sort_kernel<<<sort_ctas, 128, 2 * (e_count + 1) * sizeof(int), st>>>(idx, n_slots, (int)e_first,
+                                                                          (int)e_count, offs, list, pos);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
   const bool all_q4k = gate->ggml_type == KDNN_GGML_Q4_K && down->ggml_type == KDNN_GGML_Q4_K &&
