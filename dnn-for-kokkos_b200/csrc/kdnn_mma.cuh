@@ -30,6 +30,8 @@ struct MmaParams {
   void* dst;             // MODE 0, 1: float [npos, N]; MODE 2: YT [rows, ld_dst] indexed by slot / S
   size_t ld_dst;
   int round_bf16;
+  uint8_t* qdst;         // MODE 1: when set, the epilogue writes quantized activation rows (by position)
+  size_t q_pitch;        //         here instead of floats to dst
   int* status;
   int ablate;            // debug: 1 skip the MMA loop, 2 skip the scale table, 4 skip activation staging
 };
@@ -319,6 +321,8 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
             for (int i = 0; i < 4; ++i) ex[(t * 4 + i) * 32 + lane] = acc[t][i];
       }
       __syncthreads();
+      // act tile of this CTA for the fused quantizer: [token][64 columns], behind the exchange area
+      float* tile = reinterpret_cast<float*>(m2_smem + L::xq) + 4 * (16 * 32 + 32);
       if (mat == 0) {
 #pragma unroll
         for (int t = 0; t < 4; ++t)
@@ -326,15 +330,38 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int tok = 8 * t + 2 * tig + (i & 1);
-            const int j   = row_base + gid + 8 * (i >> 1);
-            if (tok < nt && j < p.N) {
-              const float u = ex[(t * 4 + i) * 32 + lane];
-              float v = acc[t][i];
-              v = (v / (1.0f + expf(-v))) * u;
-              if (p.round_bf16) v = __bfloat162float(__float2bfloat16_rn(v));
-              static_cast<float*>(p.dst)[static_cast<size_t>(beg + t0 + tok) * p.N + j] = v;
-            }
+            const int jl  = slab * 16 + gid + 8 * (i >> 1);
+            const int j   = blockIdx.x * L::kRowsPerCta + jl;
+            const float u = ex[(t * 4 + i) * 32 + lane];
+            float v = acc[t][i];
+            v = (v / (1.0f + expf(-v))) * u;
+            if (p.round_bf16) v = __bfloat162float(__float2bfloat16_rn(v));
+            if (p.qdst) tile[tok * 64 + jl] = j < p.N ? v : 0.f;
+            else if (tok < nt && j < p.N) static_cast<float*>(p.dst)[static_cast<size_t>(beg + t0 + tok) * p.N + j] = v;
           }
+      }
+      if (p.qdst) {
+        // per-32 int8 quantization of the tile (the reference's stage-1 quantizer, four lanes per
+        // block) straight into the rows the down projection reads
+        __syncthreads();
+        const int pair = threadIdx.x >> 2, l4 = threadIdx.x & 3;
+        const int tok = pair >> 1, blk = pair & 1;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = tile[tok * 64 + blk * 32 + l4 * 8 + i];
+        float d;
+        int part, total;
+        const uint2 packed = quantize_block_lane8(v, d, part, total);
+        const int b = blockIdx.x * 2 + blk;   // 32-block index inside the row
+        if (tok < nt && (b + 1) * 32 <= p.N) {
+          uint8_t* row = p.qdst + static_cast<size_t>(beg + t0 + tok) * p.q_pitch;
+          reinterpret_cast<uint2*>(row + static_cast<size_t>(b) * 32)[l4] = packed;
+          if (l4 == 0) {
+            reinterpret_cast<ActHdr*>(row + act_hdr_offset(static_cast<size_t>(p.N)))[b] = ActHdr{d, part, total - part, 0};
+            reinterpret_cast<float2*>(row + act_bytes(static_cast<size_t>(p.N)))[b] =
+                make_float2(d, __fmul_rn(static_cast<float>(total), d));
+          }
+        }
       }
     } else {
 #pragma unroll

@@ -6,10 +6,10 @@
 // routing result is consumed on the device, as in the reference's fused decode
 // kernels, src/KokkosDNN_GGUF.hpp:2329-2332):
 //   1. moe_sort_kernel      slots (t,s) grouped by expert -> offsets, slot list
-//   2. quantize_items       x rows -> per-32 int8 items
-//   3. grouped_gemm<1>      act[pos, j] = Scalar(silu(gate_e x_t)_j * (up_e x_t)_j)
-//   4. quantize_items       act rows -> per-32 int8 items
-//   5. grouped_gemm<0>      out[pos, d] = down_e[d,:] . act[pos,:]
+//   2. quantize rows        x rows -> per-32 int8
+//   3. tile GEMM, MODE 1    act[pos, j] = Scalar(silu(gate_e x_t)_j * (up_e x_t)_j)
+//   4. quantize rows        act rows -> per-32 int8 (inside step 3's epilogue on the mma.sync path)
+//   5. tile GEMM, MODE 0    out[pos, d] = down_e[d,:] . act[pos,:]
 //   6. moe_combine_kernel   Y[t, d] = Scalar(sum_s w[t,s] * out[pos(t,s), d])
 // Workspace (caller-owned): offsets, slot list, slot positions, int8 items, act, out.
 #include "kdnn_grouped.cuh"
@@ -291,11 +291,20 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
     g.N = (int)F; g.K = (int)H; g.offs = offs; g.list = list; g.S = (int)S; g.g_first = (int)e_first;
     g.xrows = xrows; g.x_pitch = act_row_pitch(H); g.dst = act; g.ld_dst = F;
     g.round_bf16 = xs == KDNN_BF16; g.status = moe_status_ptr();
+    // The mma.sync kernel quantizes its SwiGLU output in the epilogue (a CTA owns whole 32-blocks);
+    // the tcgen05 kernel writes floats and the row quantizer follows.
+    const bool fused_q = tile_kind() != 2 && F % 64 == 0;
+    if (fused_q) {
+      g.qdst    = arows;
+      g.q_pitch = act_row_pitch(F);
+    }
     err = tile_kind() == 2 ? launch_grouped_umma<1, float>(g, (int)e_count, st)
                            : launch_grouped_mma<1, float>(g, (int)e_count, st);
     if (err != cudaSuccess) return err;
-    err = launch_quantize_rows<float>(act, F, n_slots, (int)F, offs + e_count, arows, act_row_pitch(F), st);
-    if (err != cudaSuccess) return err;
+    if (!fused_q) {
+      err = launch_quantize_rows<float>(act, F, n_slots, (int)F, offs + e_count, arows, act_row_pitch(F), st);
+      if (err != cudaSuccess) return err;
+    }
     MmaParams d{};
     d.w0 = down->base; d.w1 = nullptr; d.row_bytes = (int)down->row_bytes;
     d.N = (int)H; d.K = (int)F; d.offs = offs; d.list = list; d.S = (int)S; d.g_first = (int)e_first;

@@ -119,7 +119,7 @@ class MoeStack:
         return h
 
     def kernels_per_layer(self) -> int:
-        return 8   # route, sort, quantize x, gate/up tile, quantize act, down tile, combine, residual+norm
+        return 7   # route, sort, quantize x, gate/up tile (+ act quantizer), down tile, combine, residual+norm
 
 
 def bench_moe_stack(kd, dev, rank: int, world: int, steps: int = 5, warmup: int = 3, peak: float = 6553.0,
