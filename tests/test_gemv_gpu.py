@@ -218,3 +218,17 @@ def test_graph_replays_recompute_every_row(kd, port, dtype):
                 got = y.cpu().numpy()
                 assert np.abs(got - ref).max() <= 1e-3 * np.abs(ref).max()
     assert kd.device_status() == 0
+
+
+@pytest.mark.parametrize("env", [{"KDNN_GEMV_Q4K": "1"}, {"KDNN_GEMV_ITEM": "1"}, {"KDNN_GEMV_ITEM": "1", "KDNN_GEMV_RW": "1"},
+                                 {"KDNN_GEMV_STAGES": "2"}, {"KDNN_GEMV_STAGES": "4", "KDNN_GEMV_EARLY": "1"}])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_alternate_streaming_kernels(kd, port, dtype, env, monkeypatch):
+    """The kernels that take over for very long rows (activation window in shared memory, item
+    mapping) and the other ring depths are selected per launch by environment switches; they must
+    give the same results as the default ones."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    _check(kd, port, dtype, 37, 4096, 91, "random")
+    _check(kd, port, dtype, 5000, 2048, 92, "random", probe=False)
+    _check(kd, port, dtype, 300, 6144 if dtype != O.Q4_K else 6656, 93, "random", probe=False)
