@@ -54,8 +54,10 @@ int cuda_result(cudaError_t e, const char* what) {
 }
 bool scalar_ok(int s) { return s == KDNN_F32 || s == KDNN_BF16; }
 bool int8_type(uint32_t t) {
-  return t == KDNN_GGML_Q4_K || t == KDNN_GGML_Q6_K || t == KDNN_GGML_Q8_0;
+  return t == KDNN_GGML_Q4_K || t == KDNN_GGML_Q5_K || t == KDNN_GGML_Q6_K || t == KDNN_GGML_Q8_0;
 }
+// the batched kernels (quant_gemm, moe_ffn) do not take Q5_K yet: such calls decline
+bool tile_type(uint32_t t) { return t == KDNN_GGML_Q4_K || t == KDNN_GGML_Q6_K || t == KDNN_GGML_Q8_0; }
 // KDNN_FORCE_GENERIC=1 routes every GEMV through the plain-load kernels (debug aid).
 int force_generic() {
   static int v = -1;
@@ -100,7 +102,7 @@ int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t 
   if (act_scratch_bytes < kdnn::act_bytes(cols)) return KDNN_DECLINED;
   if ((reinterpret_cast<uintptr_t>(act_scratch) & 15u) != 0u) return KDNN_DECLINED;
   if ((reinterpret_cast<uintptr_t>(w) & 1u) != 0u) return KDNN_DECLINED;
-  if (ggml_type == KDNN_GGML_Q4_K && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u)
+  if ((ggml_type == KDNN_GGML_Q4_K || ggml_type == KDNN_GGML_Q5_K) && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u)
     return KDNN_DECLINED;
   return cuda_result(kdnn::gemv_launch(ggml_type, w, rows, cols, x, x_scalar, y, y_scalar,
                                        act_scratch, force_generic(),
@@ -145,7 +147,7 @@ int kdnn_b200_quant_gemm(uint32_t ggml_type, const void* w, size_t N, size_t K, 
   if (M == 0 || N == 0 || K == 0) return KDNN_OK;  // src/KokkosDNN_GGUF.hpp:2576
   if (ldx < K || ldy < N) return fail(KDNN_ERR_INVALID, "quant_gemm: dimension mismatch");
   if (M * N > static_cast<size_t>(INT_MAX)) return fail(KDNN_ERR_INVALID, "quant_gemm: M*N too large");
-  if (!int8_type(ggml_type) || !kdnn::block_aligned(ggml_type, K)) return KDNN_DECLINED;
+  if (!tile_type(ggml_type) || !kdnn::block_aligned(ggml_type, K)) return KDNN_DECLINED;
   if (!w || !X || !Y || !workspace) return KDNN_DECLINED;
   if (workspace_bytes < kdnn::gemm_workspace_bytes(M, K)) return KDNN_DECLINED;
   if ((reinterpret_cast<uintptr_t>(workspace) & 15u) || (reinterpret_cast<uintptr_t>(w) & 1u))
@@ -190,7 +192,7 @@ int kdnn_b200_moe_ffn(const void* X, size_t ldx, size_t T, int x_scalar,
     return fail(KDNN_ERR_INVALID, "moe_ffn: expert table mismatch");
   if (T == 0 || S == 0 || H == 0 || F == 0) return KDNN_OK;  // :2362
   if (ldx < H || ldy < H) return fail(KDNN_ERR_INVALID, "moe_ffn: dimension mismatch");
-  if (!int8_type(gate->ggml_type) || !int8_type(up->ggml_type) || !int8_type(down->ggml_type))
+  if (!tile_type(gate->ggml_type) || !tile_type(up->ggml_type) || !tile_type(down->ggml_type))
     return KDNN_DECLINED;
   // :2369-2381
   if (H % 256 != 0 || F % 256 != 0)

@@ -31,12 +31,12 @@ constexpr int kChunkItems = 32;    // one item per lane
 
 template <uint32_t DT>
 __host__ __device__ constexpr int chunk_bytes_full() {
-  return DT == KDNN_GGML_Q4_K ? 8 * 144 : DT == KDNN_GGML_Q6_K ? 8 * 210 : 64 * 34;
+  return DT == KDNN_GGML_Q4_K ? 8 * 144 : DT == KDNN_GGML_Q5_K ? 8 * 176 : DT == KDNN_GGML_Q6_K ? 8 * 210 : 64 * 34;
 }
 // bytes of a chunk holding `items` 64-element items
 template <uint32_t DT>
 __host__ __device__ constexpr int chunk_bytes(int items) {
-  return DT == KDNN_GGML_Q4_K ? items * 36 : DT == KDNN_GGML_Q6_K ? (items / 4) * 210 : items * 68;
+  return DT == KDNN_GGML_Q4_K ? items * 36 : DT == KDNN_GGML_Q5_K ? items * 44 : DT == KDNN_GGML_Q6_K ? (items / 4) * 210 : items * 68;
 }
 
 // ---- activation staging in shared memory -------------------------------------
@@ -105,7 +105,7 @@ __device__ __forceinline__ void stage_activations(const XT* __restrict__ x, int 
         } else if (p == 0) {
           float* h = reinterpret_cast<float*>(hd + (b >> 1));
           h[b & 1] = d;
-          if (DT == KDNN_GGML_Q4_K) h[2 + (b & 1)] = __fmul_rn(static_cast<float>(total), d);
+          if (DT == KDNN_GGML_Q4_K || DT == KDNN_GGML_Q5_K) h[2 + (b & 1)] = __fmul_rn(static_cast<float>(total), d);
         }
       }
       if (gscratch) {
@@ -190,6 +190,47 @@ __device__ __forceinline__ float item_dot<KDNN_GGML_Q4_K>(uint32_t rowp, int il,
   // low nibbles <-> elements 0..31 of the item (granules 0,1), high <-> 32..63 (2,3)
   const int dotA = dot16(lo1, x.g[1], dot16(lo0, x.g[0], 0));
   const int dotB = dot16_us(hi1, x.g[3], dot16_us(hi0, x.g[2], 0)) >> 4;  // exact: the sum is a multiple of 16
+  const int sc0 = scp & 0xFF, sc1 = scp >> 8, mn0 = mnp & 0xFF, mn1 = mnp >> 8;
+  const float p = static_cast<float>(sc0 * dotA) * x.hd.x + static_cast<float>(sc1 * dotB) * x.hd.y;
+  const float m = static_cast<float>(mn0) * x.hd.z + static_cast<float>(mn1) * x.hd.w;
+  return dd.x * p - dd.y * m;
+}
+
+// Q5_K: the low four bits as in Q4_K, the fifth bit of sub-block j is bit j of qh[l]. The
+// dot is linear in the weight, so the bit plane gets its own dp4a against the same
+// activation words (kept in place as 2^j * bit, unsigned, the factor removed exactly
+// afterwards) instead of being merged into the nibbles first.
+template <>
+__device__ __forceinline__ float item_dot<KDNN_GGML_Q5_K>(uint32_t rowp, int il, const ItemX& x) {
+  const uint32_t blk = rowp + (il >> 2) * 176;
+  const int it       = il & 3;
+  const int4 h   = lds128(blk);
+  const int4 h0  = lds128(blk + 16), h1 = lds128(blk + 32);           // qh[0..15], qh[16..31]
+  const int4 qa  = lds128(blk + 48 + it * 32), qb = lds128(blk + 64 + it * 32);
+  uint32_t scp, mnp;
+  q4k_scales(h.y, h.z, h.w, it, scp, mnp);
+  const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+  const uint32_t q[8]  = {(uint32_t)qa.x, (uint32_t)qa.y, (uint32_t)qa.z, (uint32_t)qa.w,
+                          (uint32_t)qb.x, (uint32_t)qb.y, (uint32_t)qb.z, (uint32_t)qb.w};
+  const uint32_t hh[8] = {(uint32_t)h0.x, (uint32_t)h0.y, (uint32_t)h0.z, (uint32_t)h0.w,
+                          (uint32_t)h1.x, (uint32_t)h1.y, (uint32_t)h1.z, (uint32_t)h1.w};
+  uint32_t lo0[4], lo1[4], hi0[4], hi1[4], ba0[4], ba1[4], bb0[4], bb1[4];
+  const uint32_t sh = 2 * it;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    lo0[i] = q[i] & 0x0F0F0F0Fu;
+    hi0[i] = q[i] & 0xF0F0F0F0u;          // 16 * high nibble, unsigned bytes
+    lo1[i] = q[4 + i] & 0x0F0F0F0Fu;
+    hi1[i] = q[4 + i] & 0xF0F0F0F0u;
+    const uint32_t t0 = hh[i] >> sh, t1 = hh[4 + i] >> sh;
+    ba0[i] = t0 & 0x01010101u;            // fifth bit of sub-block 2*it
+    ba1[i] = t1 & 0x01010101u;
+    bb0[i] = t0 & 0x02020202u;            // 2 * fifth bit of sub-block 2*it + 1
+    bb1[i] = t1 & 0x02020202u;
+  }
+  const int dotA = dot16(lo1, x.g[1], dot16(lo0, x.g[0], 0)) + 16 * dot16(ba1, x.g[1], dot16(ba0, x.g[0], 0));
+  const int dotB = (dot16_us(hi1, x.g[3], dot16_us(hi0, x.g[2], 0)) >> 4) +
+                   8 * dot16(bb1, x.g[3], dot16(bb0, x.g[2], 0));   // 16 * (sum of 2 * bit * x) / 2
   const int sc0 = scp & 0xFF, sc1 = scp >> 8, mn0 = mnp & 0xFF, mn1 = mnp >> 8;
   const float p = static_cast<float>(sc0 * dotA) * x.hd.x + static_cast<float>(sc1 * dotB) * x.hd.y;
   const float m = static_cast<float>(mn0) * x.hd.z + static_cast<float>(mn1) * x.hd.w;
@@ -1204,6 +1245,8 @@ __device__ float unit_eval_generic(const uint8_t* row, int c, const int8_t* xq, 
   } else if (DT == KDNN_GGML_Q6_K) {
     k0 = blk * 256 + ((c >> 2) & 1) * 128 + ((c >> 1) & 1) * 32 + half * 16; kb = k0 + 64;
     h0 = k0 >> 5; h1 = h0 + 2;
+  } else if (DT == KDNN_GGML_Q5_K) {   // one whole 32-element sub-block, src/KokkosDNN_GGUFGemvInt8.hpp:389-422
+    k0 = c * 32; kb = k0 + 16; h0 = h1 = c;
   } else {
     k0 = c * 32; kb = k0 + 16; h0 = h1 = c;
   }
@@ -1231,6 +1274,28 @@ __device__ float unit_eval_generic(const uint8_t* row, int c, const int8_t* xq, 
     const float fa = dw * (float)(scp & 0xFF) * dx0, ma = dm * (float)(mnp & 0xFF) * dx0;
     const float fb = dw * (float)(scp >> 8) * dx1, mb = dm * (float)(mnp >> 8) * dx1;
     return fa * (float)dotA - ma * (float)sum0 + fb * (float)dotB - mb * (float)sum1;
+  } else if (DT == KDNN_GGML_Q5_K) {
+    const int sub = c & 7, iter = sub >> 1;
+    const bool low = (sub & 1) == 0;
+    const uint8_t* b  = row + static_cast<size_t>(blk) * 176;
+    const uint8_t* qh = b + 16;
+    const uint8_t* ql = b + 48 + iter * 32;
+    uint32_t scp, mnp;
+    q4k_scales(ldg_u16x2(b + 4), ldg_u16x2(b + 8), ldg_u16x2(b + 12), iter, scp, mnp);
+    const int sc = low ? (scp & 0xFF) : (scp >> 8), mn = low ? (mnp & 0xFF) : (mnp >> 8);
+    const float dw = h2f(ldg_u16x2(b) & 0xFFFFu) * (float)sc * dx0;
+    const float dm = h2f(ldg_u16x2(b) >> 16) * (float)mn * dx0;
+    const uint32_t sh = low ? 0u : 4u, bitsh = static_cast<uint32_t>(sub);
+    uint32_t w0[4], w1[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w0[i] = ((ldg_u16x2(ql + 4 * i) >> sh) & 0x0F0F0F0Fu) | (((ldg_u16x2(qh + 4 * i) >> bitsh) & 0x01010101u) << 4);
+      w1[i] = ((ldg_u16x2(ql + 16 + 4 * i) >> sh) & 0x0F0F0F0Fu) |
+              (((ldg_u16x2(qh + 16 + 4 * i) >> bitsh) & 0x01010101u) << 4);
+    }
+    ints[0] = dot16(w1, xb, dot16(w0, xa, 0));
+    ints[1] = 0;
+    return dw * (float)ints[0] - dm * (float)(xh[h0].sum_lo + xh[h0].sum_hi);
   } else if (DT == KDNN_GGML_Q6_K) {
     const int chunk = (c >> 2) & 1, pair = (c >> 1) & 1;
     const uint8_t* b  = row + static_cast<size_t>(blk) * 210;
@@ -1674,6 +1739,7 @@ cudaError_t gemv_launch(uint32_t dt, const void* w, size_t rows, size_t cols, co
     t_ring_does_not_fit = false;
     switch (dt) {
       case KDNN_GGML_Q4_K: e = launch_stream_dt<KDNN_GGML_Q4_K>(p, xs, ys, stream); break;
+      case KDNN_GGML_Q5_K: e = launch_stream_dt<KDNN_GGML_Q5_K>(p, xs, ys, stream); break;
       case KDNN_GGML_Q6_K: e = launch_stream_dt<KDNN_GGML_Q6_K>(p, xs, ys, stream); break;
       default: e = launch_stream_dt<KDNN_GGML_Q8_0>(p, xs, ys, stream); break;
     }
@@ -1684,6 +1750,7 @@ cudaError_t gemv_launch(uint32_t dt, const void* w, size_t rows, size_t cols, co
   uint8_t* sb       = static_cast<uint8_t*>(scratch);
   switch (dt) {
     case KDNN_GGML_Q4_K: return launch_generic_dt<KDNN_GGML_Q4_K>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, sb, stream);
+    case KDNN_GGML_Q5_K: return launch_generic_dt<KDNN_GGML_Q5_K>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, sb, stream);
     case KDNN_GGML_Q6_K: return launch_generic_dt<KDNN_GGML_Q6_K>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, sb, stream);
     default: return launch_generic_dt<KDNN_GGML_Q8_0>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, sb, stream);
   }
@@ -1708,6 +1775,7 @@ cudaError_t unit_dots_launch(uint32_t dt, const void* w, size_t rows, size_t col
   const uint8_t* sb  = static_cast<const uint8_t*>(scratch);
   switch (dt) {
     case KDNN_GGML_Q4_K: unit_dots_kernel<KDNN_GGML_Q4_K><<<blocks, 256, 0, st>>>(wb, rb, (int)rows, (int)cols, sb, out); break;
+    case KDNN_GGML_Q5_K: unit_dots_kernel<KDNN_GGML_Q5_K><<<blocks, 256, 0, st>>>(wb, rb, (int)rows, (int)cols, sb, out); break;
     case KDNN_GGML_Q6_K: unit_dots_kernel<KDNN_GGML_Q6_K><<<blocks, 256, 0, st>>>(wb, rb, (int)rows, (int)cols, sb, out); break;
     default: unit_dots_kernel<KDNN_GGML_Q8_0><<<blocks, 256, 0, st>>>(wb, rb, (int)rows, (int)cols, sb, out); break;
   }
@@ -1769,13 +1837,13 @@ extern "C" int kdnn_b200_quant_gemv_noalloc(uint32_t ggml_type, const void* w, s
     return KDNN_ERR_INVALID;
   }
   // the same decline list as kdnn_b200_quant_gemv, minus the scratch checks
-  if (ggml_type != KDNN_GGML_Q4_K && ggml_type != KDNN_GGML_Q6_K && ggml_type != KDNN_GGML_Q8_0)
+  if (ggml_type != KDNN_GGML_Q4_K && ggml_type != KDNN_GGML_Q5_K && ggml_type != KDNN_GGML_Q6_K && ggml_type != KDNN_GGML_Q8_0)
     return KDNN_DECLINED;
   if (w == nullptr || x == nullptr || y == nullptr) return KDNN_DECLINED;
   if (!block_aligned(ggml_type, cols)) return KDNN_DECLINED;
   if (rows == 0 || rows > static_cast<size_t>(INT_MAX)) return KDNN_DECLINED;
   if ((reinterpret_cast<uintptr_t>(w) & 1u) != 0u) return KDNN_DECLINED;
-  if (ggml_type == KDNN_GGML_Q4_K && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u) return KDNN_DECLINED;
+  if ((ggml_type == KDNN_GGML_Q4_K || ggml_type == KDNN_GGML_Q5_K) && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u) return KDNN_DECLINED;
   uint8_t* staging = nullptr;
   cudaError_t e = noalloc_staging_address(&staging);
   if (e == cudaSuccess)

@@ -146,14 +146,16 @@ cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, 
 // the slot ids upward 32 at a time, ranks come from one ballot per sweep step.
 __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_slots, int e_first,
                                 int e_count, int* __restrict__ offs, int* __restrict__ list,
-                                int* __restrict__ pos) {
-  extern __shared__ int sort_smem[];  // counts[e_count], cursor[e_count]
+                                int* __restrict__ pos, int cache_slots) {
+  extern __shared__ int sort_smem[];  // counts[e_count], cursor[e_count], then (when it fits) the local expert of every slot
   int* counts = sort_smem;
   int* cursor = sort_smem + e_count;
+  int* local  = sort_smem + 2 * (e_count + 1);
   for (int e = threadIdx.x; e < e_count; e += blockDim.x) counts[e] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
     const int e = idx[i] - e_first;
+    if (cache_slots) local[i] = e;
     if (e >= 0 && e < e_count) atomicAdd(&counts[e], 1);
   }
   __syncthreads();
@@ -184,7 +186,7 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_slots, in
     int c = cursor[e];
     for (int base = 0; base < n_slots; base += 32) {
       const int i = base + lane;
-      const bool hit = i < n_slots && idx[i] - e_first == e;
+      const bool hit = i < n_slots && (cache_slots ? local[i] : idx[i] - e_first) == e;
       const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
       if (hit) {
         const int ps = c + __popc(m & below);
@@ -272,8 +274,9 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
   float* out = reinterpret_cast<float*>(b + L.out);
   const int n_slots = static_cast<int>(T * S);
   const int sort_ctas = static_cast<int>(e_count < 4 ? 1 : (e_count + 3) / 4 > 64 ? 64 : (e_count + 3) / 4);
-  moe_sort_kernel<<<sort_ctas, 128, 2 * (e_count + 1) * sizeof(int), st>>>(idx, n_slots, (int)e_first,
-                                                                          (int)e_count, offs, list, pos);
+  const int cache_slots = n_slots <= 8192;   // the sweeps then read shared memory instead of global memory
+  moe_sort_kernel<<<sort_ctas, 128, (2 * (e_count + 1) + (cache_slots ? n_slots : 0)) * sizeof(int), st>>>(
+      idx, n_slots, (int)e_first, (int)e_count, offs, list, pos, cache_slots);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
   const bool all_q4k = gate->ggml_type == KDNN_GGML_Q4_K && down->ggml_type == KDNN_GGML_Q4_K &&

@@ -28,6 +28,7 @@ def test_scratch_bytes_and_supported(kd):
     assert kd.quant_gemv_int8_supported(kd.Q4_K, 512)
     assert kd.quant_gemv_int8_supported(kd.Q6_K, 6656, torch.bfloat16)
     assert kd.quant_gemv_int8_supported(kd.Q8_0, 64)
+    assert kd.quant_gemv_int8_supported(kd.Q5_K, 512) and not kd.quant_gemv_int8_supported(kd.Q5_K, 96)
     assert not kd.quant_gemv_int8_supported(kd.Q8_0, 48)
     assert not kd.quant_gemv_int8_supported(kd.Q4_K, 512, torch.float16)
 
@@ -53,7 +54,8 @@ def test_gemv_declines_without_launching(kd):
     assert call(w=W + 1) == kd.KDNN_DECLINED                  # odd payload
     assert call(w=W + 2) == kd.KDNN_DECLINED                  # Q4_K payload not 16-byte aligned
     assert call(t=0) == kd.KDNN_DECLINED                      # F32 weights keep the portable path
-    assert call(t=kd.Q5_K) == kd.KDNN_DECLINED
+    assert call(t=kd.Q5_K, w=W + 2) == kd.KDNN_DECLINED       # Q5_K payload not 16-byte aligned either
+    assert call(t=kd.Q5_K, cols=128) == kd.KDNN_DECLINED
 
 
 def test_invalid_arguments_raise(kd):

@@ -15,6 +15,7 @@ from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 DTYPES = [O.Q4_K, O.Q6_K, O.Q8_0]
+DTYPES_RANDOM = DTYPES + [O.Q5_K]   # Q5_K has no encoder here: random payloads only
 
 
 def _run(kd, dtype, packed, rows, K, x_t, y_dtype):
@@ -62,13 +63,13 @@ def _check(kd, port, dtype, rows, K, seed, payload, x_dtype=torch.float32, y_dty
     return got, y_ref
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype", DTYPES_RANDOM)
 @pytest.mark.parametrize("K", [512, 1024, 2048, 4096, 6656])
 def test_random_payload_small_rows(kd, port, dtype, K):
     _check(kd, port, dtype, 7, K, 0xC0FFEE, "random")
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype", DTYPES_RANDOM)
 @pytest.mark.parametrize("rows", [1, 3, 5, 17, 256, 1023, 1024, 1025, 1102])
 def test_row_tails(kd, port, dtype, rows):
     _check(kd, port, dtype, rows, 2048 if dtype != O.Q4_K else 512, 11 + rows, "random")
@@ -183,7 +184,7 @@ def test_golden_fixture(kd):
             assert np.abs(y.cpu().numpy() - yr).max() <= 1e-3 * np.abs(yr).max()
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype", DTYPES_RANDOM)
 def test_graph_replays_recompute_every_row(kd, port, dtype):
     """A captured sequence of GEMVs must do all of its work on every replay: tall matrices
     (more row groups than resident warps, so the in-kernel work distribution is exercised),
@@ -222,7 +223,7 @@ def test_graph_replays_recompute_every_row(kd, port, dtype):
 
 @pytest.mark.parametrize("env", [{"KDNN_GEMV_Q4K": "1"}, {"KDNN_GEMV_ITEM": "1"}, {"KDNN_GEMV_ITEM": "1", "KDNN_GEMV_RW": "1"},
                                  {"KDNN_GEMV_STAGES": "2"}, {"KDNN_GEMV_STAGES": "4", "KDNN_GEMV_EARLY": "1"}])
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype", DTYPES_RANDOM)
 def test_alternate_streaming_kernels(kd, port, dtype, env, monkeypatch):
     """The kernels that take over for very long rows (activation window in shared memory, item
     mapping) and the other ring depths are selected per launch by environment switches; they must
@@ -232,3 +233,9 @@ def test_alternate_streaming_kernels(kd, port, dtype, env, monkeypatch):
     _check(kd, port, dtype, 37, 4096, 91, "random")
     _check(kd, port, dtype, 5000, 2048, 92, "random", probe=False)
     _check(kd, port, dtype, 300, 6144 if dtype != O.Q4_K else 6656, 93, "random", probe=False)
+
+
+def test_q5k_lm_head_like_shape(kd, port):
+    """Q4_K_M files keep their largest matrices in Q5_K (src/KokkosDNN_GGUF.hpp:13-19)."""
+    _check(kd, port, O.Q5_K, 16000, 4096, 404, "random", torch.bfloat16, torch.float32, probe=False)
+    _check(kd, port, O.Q5_K, 64, 4096, 405, "random", torch.bfloat16, torch.bfloat16, probe=False)
