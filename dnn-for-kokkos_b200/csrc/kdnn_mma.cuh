@@ -33,6 +33,7 @@ struct MmaParams {
   uint8_t* qdst;         // MODE 1: when set, the epilogue writes quantized activation rows (by position)
   size_t q_pitch;        //         here instead of floats to dst
   int* status;
+  int passes_z;          // CTAs along z that share a group's 32-row passes (0 = 1)
   int ablate;            // debug: 1 skip the MMA loop, 2 skip the scale table, 4 skip activation staging
 };
 
@@ -246,7 +247,9 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
     cp_async_commit();
   };
 
-  for (int t0 = 0; t0 < n_g; t0 += kM2NT) {
+  // passes of 32 activation rows: pass z, z + gridDim.z, ... belong to this CTA, so a group with many rows
+  // is spread over several CTAs instead of keeping one CTA for several passes
+  for (int t0 = blockIdx.z * kM2NT; t0 < n_g; t0 += gridDim.z * kM2NT) {
     const int nt = min(kM2NT, n_g - t0);
     const int ntiles = (nt + 7) >> 3;
     __syncthreads();   // the previous pass is done with every buffer
@@ -393,7 +396,7 @@ static cudaError_t launch_grouped_mma(const MmaParams& p, int groups, cudaStream
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  dim3 grid((p.N + L::kRowsPerCta - 1) / L::kRowsPerCta, groups);
+  dim3 grid((p.N + L::kRowsPerCta - 1) / L::kRowsPerCta, groups, p.passes_z > 0 ? p.passes_z : 1);
   MmaParams q = p;
   static const int ablate = [] { const char* e = getenv("KDNN_TILE_ABLATE"); return e ? atoi(e) : 0; }();
   q.ablate = ablate;

@@ -296,6 +296,11 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
     g.round_bf16 = xs == KDNN_BF16; g.status = moe_status_ptr();
     // The mma.sync kernel quantizes its SwiGLU output in the epilogue (a CTA owns whole 32-blocks);
     // the tcgen05 kernel writes floats and the row quantizer follows.
+    // A group has n_slots / n_experts rows on average; routing is never uniform, so give every group one
+    // CTA more along z than the mean needs (CTAs without a pass return at once).
+    const int mean_rows = static_cast<int>((static_cast<size_t>(n_slots) + gate->n_experts - 1) / gate->n_experts);
+    const int passes_z  = max(1, min(4, 1 + (2 * mean_rows) / 32));
+    g.passes_z = passes_z;
     const bool fused_q = tile_kind() != 2 && F % 64 == 0;
     if (fused_q) {
       g.qdst    = arows;
@@ -312,6 +317,7 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
     d.w0 = down->base; d.w1 = nullptr; d.row_bytes = (int)down->row_bytes;
     d.N = (int)H; d.K = (int)F; d.offs = offs; d.list = list; d.S = (int)S; d.g_first = (int)e_first;
     d.xrows = arows; d.x_pitch = act_row_pitch(F); d.dst = out; d.ld_dst = H; d.status = moe_status_ptr();
+    d.passes_z = passes_z;
     err = tile_kind() == 2 ? launch_grouped_umma<0, float>(d, (int)e_count, st)
                            : launch_grouped_mma<0, float>(d, (int)e_count, st);
     if (err != cudaSuccess) return err;
