@@ -295,6 +295,7 @@ __device__ __forceinline__ float item_dot<KDNN_GGML_Q8_0>(uint32_t rowp, int il,
 
 // ---- the streaming kernel --------------------------------------------------------
 constexpr int kGemvMaxWarps = 16;
+constexpr int kXregMaxWarps = 18;   // the Q4_K register-window kernel may run up to 18 warps (576 threads, <= 113 registers)
 constexpr int kGemvStages   = 2;   // ring depth per warp: about one bandwidth-delay product per SM in flight
 constexpr int kTraceSlots   = 8;   // timestamps per warp when tracing
 
@@ -305,7 +306,7 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 }
 #define KDNN_TRACE(slot)                                                                   \
   do {                                                                                     \
-    if (p.trace && lane == 0)                                                              \
+    if (p.trace && lane == 0 && warp < kGemvMaxWarps)                                      \
       p.trace[(static_cast<size_t>(blockIdx.x) * kGemvMaxWarps + warp) * kTraceSlots + (slot)] = globaltimer_ns(); \
   } while (0)
 
@@ -887,14 +888,14 @@ __device__ __forceinline__ float q4k_half_dot(uint32_t blk, uint32_t qoff, int h
 }
 
 template <class XT, class YT, int RW, int STAGES>
-__global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_q4k_xreg_kernel(const XregParams p) {
+__global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(const XregParams p) {
   constexpr int kStage = RW * kWideRowPitch;
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t x_u32 = smem_u32(smem);   // activation records (see kWideRec)
   size_t off = (static_cast<size_t>(p.nsb) * kWideRec + 127) & ~size_t(127);
   const uint32_t bar_u32 = smem_u32(smem + off) + warp * (STAGES * 8);
-  off += kGemvMaxWarps * STAGES * 8;
+  off += kXregMaxWarps * STAGES * 8;
   int* s_next = reinterpret_cast<int*>(smem + off);   // [chunk] next local row group
   off += 128;
   float* part = reinterpret_cast<float*>(smem + off);  // [local row][chunk]
@@ -1501,9 +1502,25 @@ static bool launch_q4k_xreg(const GemvParams& base, cudaStream_t stream, cudaErr
   p.csb     = (p.nsb + p.nchunks - 1) / p.nchunks;   // near-equal chunks
   p.nchunks = (p.nsb + p.csb - 1) / p.csb;
   p.ngroups = (p.rows + RW - 1) / RW;
-  p.wpc     = kGemvMaxWarps / p.nchunks;
-  const int warps = p.wpc * p.nchunks;
   const int grid  = max(1, min(di.sms, p.ngroups));
+  const int gpc0  = (p.ngroups + grid - 1) / grid;
+  // Warps per chunk: units are equal-sized and handed out dynamically, so a CTA takes
+  // ceil(units / warps) unit times; with one chunk per row one or two warps beyond 16 are added when
+  // that saves a round (49 row groups: 17 warps finish in 3 rounds, 16 need a fourth).
+  p.wpc = kGemvMaxWarps / p.nchunks;
+  if (p.nchunks == 1) {
+    int best = kGemvMaxWarps, best_rounds = (gpc0 + kGemvMaxWarps - 1) / kGemvMaxWarps;
+    for (int w = kGemvMaxWarps + 1; w <= kXregMaxWarps; ++w) {
+      const int rounds = (gpc0 + w - 1) / w;
+      if (rounds < best_rounds) {
+        best = w;
+        best_rounds = rounds;
+      }
+    }
+    p.wpc = best;
+  }
+  if (const int w = env_int("KDNN_GEMV_WARPS", 0)) p.wpc = max(1, max(1, min(kXregMaxWarps, w)) / p.nchunks);
+  const int warps = p.wpc * p.nchunks;
   p.gq = p.ngroups / grid;
   p.gr = p.ngroups % grid;
   p.nch_magic = static_cast<uint32_t>((65536 + p.nchunks - 1) / p.nchunks);
@@ -1513,7 +1530,7 @@ static bool launch_q4k_xreg(const GemvParams& base, cudaStream_t stream, cudaErr
   const size_t fixed = ((static_cast<size_t>(p.nsb) * kWideRec + 127) & ~size_t(127)) + 128 +
                        ((static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127)) + 128;
   constexpr int kStage = RW * kWideRowPitch;
-  auto smem_for = [&](int st) { return fixed + static_cast<size_t>(kGemvMaxWarps) * st * (8 + kStage); };
+  auto smem_for = [&](int st) { return fixed + static_cast<size_t>(kXregMaxWarps) * st * 8 + static_cast<size_t>(warps) * st * kStage; };
   const int units_per_warp = (gpc + p.wpc - 1) / p.wpc;
   int stages = env_int("KDNN_GEMV_STAGES", 0);
   if (stages == 0) stages = 3;
