@@ -838,6 +838,7 @@ struct XregParams {
   int part_floats;
   int ablate;         // debug: 1 = skip the dot products (stream only)
   int early;          // ring stages requested before the activation window is quantized
+  int split_first;    // request only the first row of the first stage before the dependency
   unsigned long long* trace;
 };
 
@@ -924,21 +925,24 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
   int m_group[STAGES];
   const uint8_t* wsrc = p.w + static_cast<size_t>(sb0) * 144;
   const bool contiguous = p.nchunks == 1 && p.row_bytes == kWideRowPitch;
-  auto issue_unit = [&](int s, int u) {
+  // part 0: the whole unit; part 1: its first row only (the barrier already expects all bytes);
+  // part 2: the remaining rows of a unit started with part 1
+  auto issue_unit = [&](int s, int u, int part = 0) {
     m_group[s]     = u;
     const int row0 = (c0 + u) * RW;
     const int nrow = min(RW, p.rows - row0);
     if (lane == 0) {
       const uint32_t bar = bar_u32 + s * 8;
-      mbar_expect_tx(bar, cb * nrow);
+      if (part != 2) mbar_expect_tx(bar, cb * nrow);
       const uint8_t* src = wsrc + static_cast<size_t>(row0) * p.row_bytes;
       const uint32_t dst = ring_u32 + s * kStage;
-      if (contiguous) {   // one chunk per row and full rows: the unit is one run of bytes
+      if (contiguous && part == 0) {   // one chunk per row and full rows: the unit is one run of bytes
         bulk_g2s(dst, src, cb * nrow, bar);
       } else {
 #pragma unroll
         for (int r = 0; r < RW; ++r)
-          if (r < nrow) bulk_g2s(dst + r * kWideRowPitch, src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
+          if (r < nrow && (part == 0 || (part == 1) == (r == 0)))
+            bulk_g2s(dst + r * kWideRowPitch, src + static_cast<size_t>(r) * p.row_bytes, cb, bar);
       }
     }
   };
@@ -948,7 +952,8 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
   // behind megabytes of weights. The rest of the ring is requested right after the
   // activation loads have been issued.
   bool pdone = widx >= G;
-  if (!pdone) issue_unit(0, widx); else m_group[0] = -1;
+  const bool split_first = RW > 1 && p.split_first;   // half of the first stage now, the rest behind the activation loads
+  if (!pdone) issue_unit(0, widx, split_first ? 1 : 0); else m_group[0] = -1;
   __syncthreads();   // the chunk counters are set
   int pu = 0, pnext = 0x7fffffff;
   auto draw = [&]() {
@@ -978,7 +983,9 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
   KDNN_TRACE(2);
   // ring stages 1 .. early-1 are requested once the activation loads are in flight, the
   // rest after the quantized window has been written
+  const bool first_live = m_group[0] >= 0;
   stage_activations_wide<XT>(static_cast<const XT*>(p.x), p.K, smem, blockIdx.x == 0 ? p.scratch : nullptr, [&]() {
+    if (split_first && first_live) issue_unit(0, widx, 2);
 #pragma unroll
     for (int s = 1; s < STAGES; ++s)
       if (s < p.early) issue(s);
@@ -1541,6 +1548,9 @@ static bool launch_q4k_xreg(const GemvParams& base, cudaStream_t stream, cudaErr
   p.trace = g_trace_buffer;
   p.ablate = env_int("KDNN_GEMV_ABLATE", 0);
   p.early  = env_int("KDNN_GEMV_EARLY", 2);
+  // When every warp has at most one unit the whole matrix would be requested before the dependency and
+  // the activation loads would queue behind all of it: request half of it first, the rest behind those loads.
+  p.split_first = env_int("KDNN_GEMV_SPLIT", gpc <= p.wpc ? 1 : 0);
   using Kern = void (*)(const XregParams);
   const Kern kern = stages == 2 ? gemv_q4k_xreg_kernel<XT, YT, RW, 2>
                   : stages == 3 ? gemv_q4k_xreg_kernel<XT, YT, RW, 3> : gemv_q4k_xreg_kernel<XT, YT, RW, 4>;

@@ -222,6 +222,35 @@ __global__ void moe_combine_kernel(const float* __restrict__ out, const int* __r
   store_scalar(Y + static_cast<size_t>(t) * ldy + d, acc);
 }
 
+// The same sums, four columns per thread (16-byte loads of `out`; H % 4 == 0 and 16-byte / 8-byte
+// aligned output rows): every element is accumulated in the same slot order as above.
+template <class YT>
+__global__ void moe_combine4_kernel(const float* __restrict__ out, const int* __restrict__ pos,
+                                    const float* __restrict__ wts, int T, int S, int H, YT* Y,
+                                    size_t ldy) {
+  const int t = blockIdx.y;
+  const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (d >= H) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < S; ++s) {
+    const int ps  = pos[t * S + s];
+    const float w = wts[t * S + s];
+    if (ps < 0 || w == 0.0f) continue;
+    const float4 v = *reinterpret_cast<const float4*>(out + static_cast<size_t>(ps) * H + d);
+    acc.x += w * v.x;
+    acc.y += w * v.y;
+    acc.z += w * v.z;
+    acc.w += w * v.w;
+  }
+  YT* dst = Y + static_cast<size_t>(t) * ldy + d;
+  if (sizeof(YT) == 4) {
+    *reinterpret_cast<float4*>(dst) = acc;
+  } else {
+    __nv_bfloat162 h[2] = {__floats2bfloat162_rn(acc.x, acc.y), __floats2bfloat162_rn(acc.z, acc.w)};
+    *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(h);
+  }
+}
+
 // ---- workspace layout -------------------------------------------------------------------
 struct MoeWs {
   size_t offs, list, pos, xq, act, actq, out, total;
@@ -345,6 +374,17 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
     d.src = actq; d.dst = out; d.ld_dst = H;
     err = launch_grouped_dt<0, float, float>(down->ggml_type, d, (int)e_count, st);
     if (err != cudaSuccess) return err;
+  }
+  const size_t ybytes = ys == KDNN_F32 ? 4 : 2;
+  const bool vec4 = H % 4 == 0 && (reinterpret_cast<uintptr_t>(Y) % (4 * ybytes)) == 0 && (ldy * ybytes) % (4 * ybytes) == 0;
+  if (vec4) {
+    dim3 cgrid((unsigned)((H / 4 + 127) / 128), (unsigned)T);
+    if (ys == KDNN_F32)
+      moe_combine4_kernel<float><<<cgrid, 128, 0, st>>>(out, pos, wts, (int)T, (int)S, (int)H, static_cast<float*>(Y), ldy);
+    else
+      moe_combine4_kernel<__nv_bfloat16><<<cgrid, 128, 0, st>>>(out, pos, wts, (int)T, (int)S, (int)H,
+                                                                static_cast<__nv_bfloat16*>(Y), ldy);
+    return cudaGetLastError();
   }
   dim3 cgrid((unsigned)((H + 255) / 256), (unsigned)T);
   if (ys == KDNN_F32)
