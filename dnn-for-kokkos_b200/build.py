@@ -31,18 +31,38 @@ def is_stale() -> bool:
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
+    """Compiles every translation unit in parallel (objects in a temporary folder), then links.
+    The library is written next to this file under a temporary name and renamed at the end, so a
+    reader never sees a half-written file."""
     if not force and not is_stale():
         return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []),
-           *[os.path.join(HERE, "csrc", s) for s in SOURCES], "-o", LIB]
+    import tempfile
+    from concurrent.futures import ThreadPoolExecutor
     env = dict(os.environ)
     env.pop("CC", None)   # the image's CC/CXX point at a compiler front-end nvcc cannot drive
     env.pop("CXX", None)
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(res.stdout + res.stderr)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed building libkdnn_b200.so")
+    nvcc = _nvcc()
+    flags = [f for f in NVCC_FLAGS if f != "-shared"]
+    with tempfile.TemporaryDirectory(prefix="kdnn_build_") as tmp:
+        def compile_one(src: str):
+            obj = os.path.join(tmp, src.replace(".cu", ".o"))
+            cmd = [nvcc, *flags, *(["-Xptxas", "-v"] if verbose else []), "-c",
+                   os.path.join(HERE, "csrc", src), "-o", obj]
+            return obj, subprocess.run(cmd, env=env, capture_output=True, text=True)
+        with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+            results = list(pool.map(compile_one, SOURCES))
+        for _, res in results:
+            if verbose or res.returncode != 0:
+                sys.stderr.write(res.stdout + res.stderr)
+        if any(res.returncode != 0 for _, res in results):
+            raise RuntimeError("nvcc failed building libkdnn_b200.so")
+        tmp_lib = LIB + ".tmp"
+        link = subprocess.run([nvcc, "-shared", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a",
+                               *[obj for obj, _ in results], "-o", tmp_lib], env=env, capture_output=True, text=True)
+        if link.returncode != 0:
+            sys.stderr.write(link.stdout + link.stderr)
+            raise RuntimeError("nvcc failed linking libkdnn_b200.so")
+        os.replace(tmp_lib, LIB)
     return LIB
 
 
