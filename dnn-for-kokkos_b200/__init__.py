@@ -38,7 +38,7 @@ EXPORTS = [
     "kdnn_b200_quantize_act_q8",
     "kdnn_b200_unit_dots", "kdnn_b200_gemm_workspace_bytes", "kdnn_b200_quant_gemm",
     "kdnn_b200_moe_route", "kdnn_b200_moe_workspace_bytes", "kdnn_b200_moe_ffn",
-    "kdnn_b200_residual_rmsnorm", "kdnn_b200_dequant_to_dense",
+    "kdnn_b200_residual_rmsnorm", "kdnn_b200_dequant_to_dense", "kdnn_b200_quant_gemv_fp",
 ]
 
 
@@ -87,6 +87,8 @@ def _load() -> C.CDLL:
                                       C.POINTER(WeightTableC), C.c_void_p, C.c_void_p, C.c_size_t,
                                       C.c_void_p, C.c_size_t, C.c_int, C.c_size_t, C.c_size_t,
                                       C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_quant_gemv_fp.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int,
+                                            C.c_void_p, C.c_int, C.c_void_p]
     lib.kdnn_b200_dequant_to_dense.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                                C.c_size_t, C.c_int, C.c_void_p]
     lib.kdnn_b200_residual_rmsnorm.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p,
@@ -242,6 +244,21 @@ def quant_gemm(X: torch.Tensor, w: QuantWeight, Y: torch.Tensor, workspace: torc
                                   _scalar(X), Y.data_ptr(), Y.stride(0), _scalar(Y),
                                   workspace.data_ptr(), workspace.numel(), _stream())
     _check(rc, "quant_gemm")
+
+
+def quant_gemv_fp(x: torch.Tensor, w: QuantWeight, y: torch.Tensor) -> None:
+    """y[N] = W[N,K] x[K] on the fp path, no staging buffer (Gguf::quant_gemv(handle, x, w, y),
+    src/KokkosDNN_GGUF.hpp:2394-2493)."""
+    if x.numel() != w.cols or y.numel() != w.rows:
+        raise ValueError("quant_gemv: dimension mismatch")
+    _quant_check(w, "quant_gemv")
+    if w.rows == 0 or w.cols == 0:
+        return
+    if x.stride(0) != 1 or y.stride(0) != 1:
+        raise ValueError("quant_gemv: x and y must have unit stride")
+    rc = lib.kdnn_b200_quant_gemv_fp(w.dtype, w.data.data_ptr(), w.rows, w.cols, x.data_ptr(), _scalar(x),
+                                     y.data_ptr(), _scalar(y), _stream())
+    _check(rc, "quant_gemv_fp")
 
 
 def dequant_to_dense(w: QuantWeight, Y: torch.Tensor) -> None:

@@ -30,6 +30,8 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
                            size_t S, void* Y, size_t ldy, int ys, size_t e_first, size_t e_count,
                            void* ws, cudaStream_t st);
 int moe_take_status();
+cudaError_t gemv_fp_launch(uint32_t dt, const void* w, size_t rows, size_t cols, const void* x, int xs, void* y, int ys,
+                           cudaStream_t st);
 cudaError_t dequant_launch(uint32_t dt, const void* w, size_t rows, size_t cols, void* y, size_t ldy, int ys,
                            cudaStream_t st);
 cudaError_t residual_rmsnorm_launch(const void* h, size_t ldh, const float* y, size_t ldy, void* out,
@@ -241,6 +243,20 @@ int kdnn_b200_dequant_to_dense(uint32_t ggml_type, const void* w, size_t rows, s
   return cuda_result(kdnn::dequant_launch(ggml_type, w, rows, cols, y, ldy, y_scalar,
                                           static_cast<cudaStream_t>(stream)),
                      "dequant_to_dense");
+}
+
+int kdnn_b200_quant_gemv_fp(uint32_t ggml_type, const void* w, size_t rows, size_t cols, const void* x,
+                            int x_scalar, void* y, int y_scalar, void* stream) {
+  if (!scalar_ok(x_scalar) || !scalar_ok(y_scalar)) return fail(KDNN_ERR_INVALID, "quant_gemv_fp: bad scalar");
+  if (!int8_type(ggml_type)) return fail(KDNN_ERR_INVALID, "quant_gemv_fp: unsupported dtype");
+  if (rows == 0 || cols == 0) return KDNN_OK;
+  if (!kdnn::block_aligned(ggml_type, cols))
+    return fail(KDNN_ERR_INVALID, "quant_gemv_fp: cols must be a whole number of blocks");
+  if (!w || !x || !y || rows > static_cast<size_t>(INT_MAX) || cols > static_cast<size_t>(INT_MAX))
+    return fail(KDNN_ERR_INVALID, "quant_gemv_fp: bad argument");
+  return cuda_result(kdnn::gemv_fp_launch(ggml_type, w, rows, cols, x, x_scalar, y, y_scalar,
+                                          static_cast<cudaStream_t>(stream)),
+                     "quant_gemv_fp");
 }
 
 }  // extern "C"

@@ -125,6 +125,88 @@ static cudaError_t dequant_dt(const uint8_t* w, size_t rb, int rows, int cols, v
   return cudaGetLastError();
 }
 
+// ---- fp-path GEMV ------------------------------------------------------------------------
+// y[r] = Scalar(sum_k dequant(W[r, k]) * float(x[k])), fp32 accumulation: the operator behind
+// Gguf::quant_gemv(handle, x, w, y) without a staging buffer (src/KokkosDNN_GGUF.hpp:2394-2493),
+// which is also where a declined int8 call lands. The activation row sits in shared memory as
+// fp32 (in pieces of kFpChunk elements), a warp owns one row at a time and converts 256 weights
+// per step with the dequantizer above, so the weights are exactly the reference's dequantized
+// values and only the order of the fp32 additions differs from its FMA chains.
+constexpr int kFpChunk = 8192;   // activation elements resident per pass (32 KB)
+
+template <uint32_t DT, class XT, class YT>
+__global__ void __launch_bounds__(256) gemv_fp_kernel(const uint8_t* __restrict__ w, size_t row_bytes, int rows,
+                                                       int cols, const XT* __restrict__ x, YT* __restrict__ y) {
+  constexpr int kGroupBytes = DT == KDNN_GGML_Q4_K ? 144 : DT == KDNN_GGML_Q5_K ? 176 : DT == KDNN_GGML_Q6_K ? 210 : 8 * 34;
+  __shared__ float xs[kFpChunk];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int rows_per_cta = (rows + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
+  // rows of this CTA are spread over its warps; partial sums over the chunks stay in registers
+  // (at most kMaxRowsPerWarp rows per warp, the host sizes the grid accordingly)
+  constexpr int kMaxRowsPerWarp = 8;
+  float acc[kMaxRowsPerWarp];
+#pragma unroll
+  for (int i = 0; i < kMaxRowsPerWarp; ++i) acc[i] = 0.f;
+  for (int k0 = 0; k0 < cols; k0 += kFpChunk) {
+    const int kc = min(kFpChunk, cols - k0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < kc; i += blockDim.x) xs[i] = to_f32(x[k0 + i]);
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kMaxRowsPerWarp; ++i) {
+      const int r = r0 + warp + i * nwarp;
+      if (r >= r1) break;
+      const uint8_t* row = w + static_cast<size_t>(r) * row_bytes;
+      float a = 0.f;
+      for (int g = 0; g * 256 < kc; ++g) {
+        const int k = g * 256 + 8 * lane;
+        if (k >= kc) continue;   // Q8_0 rows that are not a multiple of 256
+        float v[8];
+        dequant8<DT>(row + static_cast<size_t>(k0 / 256 + g) * kGroupBytes, lane, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a = fmaf(v[j], xs[k + j], a);
+      }
+      acc[i] += a;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kMaxRowsPerWarp; ++i) {
+    const int r = r0 + warp + i * nwarp;
+    if (r >= r1) break;
+    const float v = warp_sum(acc[i]);
+    if (lane == 0) store_scalar(y + r, v);
+  }
+}
+
+template <uint32_t DT>
+static cudaError_t gemv_fp_dt(const uint8_t* w, size_t rb, int rows, int cols, const void* x, int xs, void* y, int ys,
+                              cudaStream_t st) {
+  // 8 warps per CTA, at most 8 rows per warp: 64 rows per CTA at most
+  const int grid = max(max(1, (rows + 63) / 64), min((rows + 7) / 8, 4 * 148));
+  if (xs == KDNN_F32 && ys == KDNN_F32)
+    gemv_fp_kernel<DT, float, float><<<grid, 256, 0, st>>>(w, rb, rows, cols, static_cast<const float*>(x), static_cast<float*>(y));
+  else if (xs == KDNN_BF16 && ys == KDNN_BF16)
+    gemv_fp_kernel<DT, __nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(w, rb, rows, cols, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y));
+  else if (xs == KDNN_BF16)
+    gemv_fp_kernel<DT, __nv_bfloat16, float><<<grid, 256, 0, st>>>(w, rb, rows, cols, static_cast<const __nv_bfloat16*>(x), static_cast<float*>(y));
+  else
+    gemv_fp_kernel<DT, float, __nv_bfloat16><<<grid, 256, 0, st>>>(w, rb, rows, cols, static_cast<const float*>(x), static_cast<__nv_bfloat16*>(y));
+  return cudaGetLastError();
+}
+
+cudaError_t gemv_fp_launch(uint32_t dt, const void* w, size_t rows, size_t cols, const void* x, int xs, void* y, int ys,
+                           cudaStream_t st) {
+  const uint8_t* wb = static_cast<const uint8_t*>(w);
+  const size_t rb   = row_bytes_of(dt, cols);
+  switch (dt) {
+    case KDNN_GGML_Q4_K: return gemv_fp_dt<KDNN_GGML_Q4_K>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, st);
+    case KDNN_GGML_Q5_K: return gemv_fp_dt<KDNN_GGML_Q5_K>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, st);
+    case KDNN_GGML_Q6_K: return gemv_fp_dt<KDNN_GGML_Q6_K>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, st);
+    default: return gemv_fp_dt<KDNN_GGML_Q8_0>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, st);
+  }
+}
+
 cudaError_t dequant_launch(uint32_t dt, const void* w, size_t rows, size_t cols, void* y, size_t ldy, int ys,
                            cudaStream_t st) {
   const uint8_t* wb = static_cast<const uint8_t*>(w);

@@ -101,6 +101,19 @@ void quant_gemv(const ExecSpace& space, const XView& x, const QuantWeight& w, co
   fallback();
 }
 
+// Gguf::quant_gemv(handle, x, w, y) without staging (fp path), src/KokkosDNN_GGUF.hpp:2394-2493.
+template <class ExecSpace, class XView, class QuantWeight, class YView>
+void quant_gemv_fp(const ExecSpace& space, const XView& x, const QuantWeight& w, const YView& y) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(x.data())>::type>::type;
+  if (x.extent(0) != w.cols || y.extent(0) != w.rows) throw std::invalid_argument("quant_gemv: dimension mismatch");
+  if (w.rows == 0 || w.cols == 0) return;
+  if (scalar_tag<Scalar>() < 0) throw std::invalid_argument("quant_gemv: Scalar must be float or bhalf_t");
+  const int rc = kdnn_b200_quant_gemv_fp(static_cast<std::uint32_t>(w.dtype), w.data.data(), w.rows, w.cols, x.data(),
+                                         scalar_tag<Scalar>(), y.data(), scalar_tag<Scalar>(),
+                                         StreamOf<ExecSpace>::get(space));
+  throw_on_error(rc, "quant_gemv_fp");
+}
+
 // Gguf::dequant_to_dense, src/KokkosDNN_GGUF.hpp:2839-2934.
 template <class ExecSpace, class QuantWeight, class YView>
 void dequant_to_dense(const ExecSpace& space, const QuantWeight& w, const YView& Y) {

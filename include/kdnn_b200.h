@@ -201,6 +201,16 @@ int kdnn_b200_residual_rmsnorm(const void* h, size_t ldh, const float* y, size_t
 int kdnn_b200_dequant_to_dense(uint32_t ggml_type, const void* w, size_t rows, size_t cols, void* y, size_t ldy,
                                int y_scalar, void* stream);
 
+/* y[N] = Scalar(sum_k dequant(W[n,k]) * float(x[k])) with fp32 accumulation: replaces the staging-free
+ * KokkosDNN::Gguf::quant_gemv(handle, x, w, y), src/KokkosDNN_GGUF.hpp:2394-2493 (the fp path a declined
+ * int8 call falls back to). Types Q4_K, Q5_K, Q6_K, Q8_0. The weights are the reference's dequantized values
+ * bit for bit; the order of the fp32 additions differs from its FMA chains, so results agree to fp32 rounding
+ * of the sum, not bit for bit. Any payload alignment; x, y unit stride.
+ * KDNN_ERR_INVALID for an unknown type or cols that are not a whole number of blocks (the reference's
+ * quant_check); zero extents return KDNN_OK without a launch. */
+int kdnn_b200_quant_gemv_fp(uint32_t ggml_type, const void* w, size_t rows, size_t cols, const void* x,
+                            int x_scalar, void* y, int y_scalar, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
