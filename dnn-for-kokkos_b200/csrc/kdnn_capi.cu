@@ -58,8 +58,7 @@ bool scalar_ok(int s) { return s == KDNN_F32 || s == KDNN_BF16; }
 bool int8_type(uint32_t t) {
   return t == KDNN_GGML_Q4_K || t == KDNN_GGML_Q5_K || t == KDNN_GGML_Q6_K || t == KDNN_GGML_Q8_0;
 }
-// the batched kernels (quant_gemm, moe_ffn) do not take Q5_K yet: such calls decline
-bool tile_type(uint32_t t) { return t == KDNN_GGML_Q4_K || t == KDNN_GGML_Q6_K || t == KDNN_GGML_Q8_0; }
+bool tile_type(uint32_t t) { return int8_type(t); }
 // KDNN_FORCE_GENERIC=1 routes every GEMV through the plain-load kernels (debug aid).
 int force_generic() {
   static int v = -1;
@@ -154,6 +153,8 @@ int kdnn_b200_quant_gemm(uint32_t ggml_type, const void* w, size_t N, size_t K, 
   if (workspace_bytes < kdnn::gemm_workspace_bytes(M, K)) return KDNN_DECLINED;
   if ((reinterpret_cast<uintptr_t>(workspace) & 15u) || (reinterpret_cast<uintptr_t>(w) & 1u))
     return KDNN_DECLINED;
+  if ((ggml_type == KDNN_GGML_Q4_K || ggml_type == KDNN_GGML_Q5_K) && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u)
+    return KDNN_DECLINED;   // 16-byte loads of the super-blocks, src/KokkosDNN_GGUFGemvInt8.hpp:741-743
   return cuda_result(kdnn::gemm_launch(ggml_type, w, N, K, X, ldx, M, x_scalar, Y, ldy, y_scalar,
                                        workspace, static_cast<cudaStream_t>(stream)),
                      "quant_gemm");

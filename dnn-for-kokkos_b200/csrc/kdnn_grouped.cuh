@@ -143,7 +143,9 @@ static cudaError_t launch_quantize_items(uint32_t dt, const SRC* src, size_t ld,
   const int bx = max(1, min(8, (K / 32 + 31) / 32));
   dim3 grid(bx, nrows);
   switch (dt) {
-    case KDNN_GGML_Q4_K: quantize_items_kernel<KDNN_GGML_Q4_K, SRC><<<grid, 256, 0, st>>>(src, ld, nrows, K, nrows_dev, dst); break;
+    case KDNN_GGML_Q4_K:
+    case KDNN_GGML_Q5_K:   // same item order as Q4_K
+      quantize_items_kernel<KDNN_GGML_Q4_K, SRC><<<grid, 256, 0, st>>>(src, ld, nrows, K, nrows_dev, dst); break;
     case KDNN_GGML_Q6_K: quantize_items_kernel<KDNN_GGML_Q6_K, SRC><<<grid, 256, 0, st>>>(src, ld, nrows, K, nrows_dev, dst); break;
     default: quantize_items_kernel<KDNN_GGML_Q8_0, SRC><<<grid, 256, 0, st>>>(src, ld, nrows, K, nrows_dev, dst); break;
   }
@@ -169,6 +171,7 @@ template <int MODE, class XT, class YT>
 static cudaError_t launch_grouped_dt(uint32_t dt, const GroupedParams& p, int groups, cudaStream_t st) {
   switch (dt) {
     case KDNN_GGML_Q4_K: return launch_grouped<KDNN_GGML_Q4_K, MODE, XT, YT>(p, groups, st);
+    case KDNN_GGML_Q5_K: return launch_grouped<KDNN_GGML_Q5_K, MODE, XT, YT>(p, groups, st);
     case KDNN_GGML_Q6_K: return launch_grouped<KDNN_GGML_Q6_K, MODE, XT, YT>(p, groups, st);
     default: return launch_grouped<KDNN_GGML_Q8_0, MODE, XT, YT>(p, groups, st);
   }

@@ -101,6 +101,50 @@ struct WItem<KDNN_GGML_Q4_K> {
   }
 };
 
+// Q5_K: Q4_K's nibbles plus the fifth bit of sub-block j in bit j of qh[l] (src/KokkosDNN_GGUFGemvInt8.hpp:389-422);
+// the words hold the complete 5-bit values, the rest is the Q4_K arithmetic.
+template <>
+struct WItem<KDNN_GGML_Q5_K> {
+  uint32_t w[4][4];
+  float s0, s1, m0, m1;  // d*sc0, d*sc1, dmin*mn0, dmin*mn1
+  __device__ __forceinline__ void load(const uint8_t* row, int item) {
+    const uint8_t* blk = row + static_cast<size_t>(item >> 2) * 176;
+    const int it       = item & 3;
+    const int4 h       = ldg128(blk);
+    const int4 h0      = ldg128(blk + 16), h1 = ldg128(blk + 32);
+    const int4 qa      = ldg128(blk + 48 + it * 32);
+    const int4 qb      = ldg128(blk + 64 + it * 32);
+    uint32_t scp, mnp;
+    q4k_scale_pair(h.y, h.z, h.w, it, scp, mnp);
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+    s0 = dd.x * static_cast<float>(scp & 0xFF);
+    s1 = dd.x * static_cast<float>(scp >> 8);
+    m0 = dd.y * static_cast<float>(mnp & 0xFF);
+    m1 = dd.y * static_cast<float>(mnp >> 8);
+    const uint32_t q[8]  = {(uint32_t)qa.x, (uint32_t)qa.y, (uint32_t)qa.z, (uint32_t)qa.w,
+                            (uint32_t)qb.x, (uint32_t)qb.y, (uint32_t)qb.z, (uint32_t)qb.w};
+    const uint32_t hh[8] = {(uint32_t)h0.x, (uint32_t)h0.y, (uint32_t)h0.z, (uint32_t)h0.w,
+                            (uint32_t)h1.x, (uint32_t)h1.y, (uint32_t)h1.z, (uint32_t)h1.w};
+    const uint32_t sh = 2 * it;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t t0 = hh[i] >> sh, t1 = hh[4 + i] >> sh;
+      w[0][i] = (q[i] & 0x0F0F0F0Fu) | ((t0 & 0x01010101u) << 4);
+      w[1][i] = (q[4 + i] & 0x0F0F0F0Fu) | ((t1 & 0x01010101u) << 4);
+      w[2][i] = ((q[i] >> 4) & 0x0F0F0F0Fu) | ((t0 & 0x02020202u) << 3);
+      w[3][i] = ((q[4 + i] >> 4) & 0x0F0F0F0Fu) | ((t1 & 0x02020202u) << 3);
+    }
+  }
+  __device__ __forceinline__ float dot(const ActItem& a) const {
+    const int dA = dot16(w[1], a.g[1], dot16(w[0], a.g[0], 0));
+    const int dB = dot16(w[3], a.g[3], dot16(w[2], a.g[2], 0));
+    const float p = s0 * (static_cast<float>(dA) * a.dx[0]) + s1 * (static_cast<float>(dB) * a.dx[2]);
+    const float m = m0 * (static_cast<float>(a.sum[0] + a.sum[1]) * a.dx[0]) +
+                    m1 * (static_cast<float>(a.sum[2] + a.sum[3]) * a.dx[2]);
+    return p - m;
+  }
+};
+
 template <>
 struct WItem<KDNN_GGML_Q6_K> {
   uint32_t w[4][4];

@@ -145,7 +145,23 @@ def test_moe_decode_one_token_vs_reference_fp_kernel(kd, port):
                             act[:1], Y, ws)
 
 
-@pytest.mark.parametrize("dtype,N,K", [(O.Q4_K, 300, 1024), (O.Q6_K, 130, 2048), (O.Q8_0, 257, 512)])
+@pytest.mark.parametrize("dtypes", [(O.Q5_K, O.Q5_K, O.Q5_K), (O.Q4_K, O.Q4_K, O.Q5_K)])
+def test_moe_ffn_q5k_experts(kd, port, dtypes):
+    """Q5_K expert matrices (random payloads: there is no Q5_K encoder here) through the batched kernels."""
+    E, H, F, T, S = 5, 512, 256, 19, 2
+    gate, up, down = _experts(kd, E, H, F, 70, dtypes, payload="random")
+    tabs = _tables(kd, gate, up, down, dtypes, H, F)
+    rng = np.random.default_rng(9)
+    X = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32))
+    idx = np.stack([rng.permutation(E)[:S] for _ in range(T)]).astype(np.int32)
+    wts = rng.random((T, S)).astype(np.float32)
+    al = lambda lst: [O.aligned_copy(a) for a in lst]
+    ref = port.moe_ffn_int8(X.numpy(), al(gate), al(up), al(down), idx, wts, F, dtypes, bf16=False)
+    got = _ffn(kd, X, tabs, idx, wts, torch.float32)
+    assert np.abs(got - ref).max() <= 1e-3 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("dtype,N,K", [(O.Q4_K, 300, 1024), (O.Q6_K, 130, 2048), (O.Q8_0, 257, 512), (O.Q5_K, 200, 1024)])
 @pytest.mark.parametrize("M", [1, 2, 3, 5, 16, 17, 32])
 def test_quant_gemm_rows_equal_gemv(kd, port, dtype, N, K, M):
     packed = kd.ggml_pack.random_payload(dtype, N, K, N + K)
