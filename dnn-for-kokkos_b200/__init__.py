@@ -23,6 +23,8 @@ import torch
 
 from . import ggml_pack  # noqa: F401  (re-exported: encoders for synthetic weights)
 from .ggml_pack import Q4_K, Q5_K, Q6_K, Q8_0, row_bytes as ggml_row_bytes  # noqa: F401
+from . import gguf_io  # noqa: F401
+from .gguf_io import GgufFile, GgufTensorInfo, write_gguf  # noqa: F401
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libkdnn_b200.so")
@@ -154,6 +156,18 @@ class QuantWeight:
     def from_numpy(packed, dtype: int, rows: int, cols: int, device="cuda") -> "QuantWeight":
         t = torch.from_numpy(packed.reshape(-1)).to(device)
         return QuantWeight(t, dtype, rows, cols)
+
+
+def load_quant_weight(file: GgufFile, info: GgufTensorInfo, device="cuda") -> QuantWeight:
+    """Gguf::load_quant_weight (src/KokkosDNN_GGUF.hpp:864-885)."""
+    import sys
+    return gguf_io.load_quant_weight(sys.modules[__name__], file, info, device)
+
+
+def load_expert_weights(file: GgufFile, info: GgufTensorInfo, device="cuda") -> List[QuantWeight]:
+    """Every expert of a stacked {cols, rows, experts} tensor; feed the list to make_quant_weight_table."""
+    import sys
+    return gguf_io.load_expert_weights(sys.modules[__name__], file, info, device)
 
 
 def _quant_check(w: QuantWeight, what: str) -> None:

@@ -247,6 +247,49 @@ class Ref:
         if rc != 0:
             raise RuntimeError(self.lib.kref_last_error().decode())
 
+    # ---- GGUF container: the reference's own writer and reader ------------------------
+    def gguf_write(self, path, tensors, strings=None, f32=None, u32=None):
+        """tensors: (name, dims in ggml order, ggml type id, uint8 payload). Written by the reference's
+        write_synthetic_gguf."""
+        n = len(tensors)
+        names = (C.c_char_p * n)(*[t[0].encode() for t in tensors])
+        dtypes = (C.c_uint32 * n)(*[t[2] for t in tensors])
+        ndims = (C.c_uint32 * n)(*[len(t[1]) for t in tensors])
+        dims = (C.c_uint64 * (4 * n))()
+        raws = [np.ascontiguousarray(t[3]).view(np.uint8).reshape(-1) for t in tensors]
+        for i, t in enumerate(tensors):
+            for d, v in enumerate(t[1]):
+                dims[4 * i + d] = v
+        ptrs = (C.c_void_p * n)(*[r.ctypes.data for r in raws])
+        sizes = (C.c_size_t * n)(*[r.size for r in raws])
+
+        def kv(m, ctype):
+            m = m or {}
+            keys = (C.c_char_p * len(m))(*[k.encode() for k in m])
+            vals = (ctype * len(m))(*[v.encode() if ctype is C.c_char_p else v for v in m.values()])
+            return C.c_size_t(len(m)), keys, vals
+        self._check(self.lib.kref_gguf_write(path.encode(), C.c_size_t(n), names, dtypes, ndims, dims, ptrs, sizes,
+                                             *kv(strings, C.c_char_p), *kv(f32, C.c_float), *kv(u32, C.c_uint32)))
+
+    def gguf_read_tensor(self, path, name, cap=1 << 24):
+        """The reference's GgufFile on `path`: (dtype, dims, offset, nbytes, data_start, payload)."""
+        out = (C.c_uint64 * 8)()
+        start = C.c_uint64()
+        buf = np.zeros(cap, dtype=np.uint8)
+        self._check(self.lib.kref_gguf_read_tensor(path.encode(), name.encode(), out, C.byref(start),
+                                                   C.c_void_p(buf.ctypes.data), C.c_size_t(cap)))
+        nd = int(out[1])
+        return int(out[0]), [int(out[2 + d]) for d in range(nd)], int(out[6]), int(out[7]), int(start.value), \
+            buf[:min(cap, int(out[7]))]
+
+    def gguf_read_kv(self, path, key, kind):
+        buf = C.create_string_buffer(4096)
+        f, u = C.c_float(), C.c_uint32()
+        k = {"str": 0, "f32": 1, "u32": 2}[kind]
+        self._check(self.lib.kref_gguf_read_kv(path.encode(), key.encode(), k, buf, C.c_size_t(4096),
+                                               C.byref(f), C.byref(u)))
+        return buf.value.decode() if k == 0 else (f.value if k == 1 else u.value)
+
     def set_threads(self, n: int):
         self.lib.kref_set_num_threads(C.c_int(n))
 

@@ -11,6 +11,7 @@
 #include <Kokkos_Core.hpp>
 
 #include "KokkosDNN_GGUF.hpp"
+#include "KokkosDNN_GGUF_Synthetic.hpp"
 #include "KokkosDNN_MoE.hpp"
 
 #include <cstdint>
@@ -382,6 +383,63 @@ int kref_dequant_row(uint32_t dtype, const uint8_t* row, size_t cols, float* out
           G::dequant_q80_block(reinterpret_cast<const G::BlockQ80*>(row + b * 34), out + b * 32);
         break;
       default: throw std::invalid_argument("kref_dequant_row: unsupported dtype");
+    }
+  });
+}
+
+// src/KokkosDNN_GGUF_Synthetic.hpp:49 write_synthetic_gguf — the reference's own container writer,
+// driven with flat arrays: tensor t has n_dims[t] extents at dims[4*t..], payload raw[t] of raw_bytes[t].
+int kref_gguf_write(const char* path, size_t n_tensors, const char* const* names, const uint32_t* dtypes,
+                    const uint32_t* n_dims, const uint64_t* dims, const uint8_t* const* raw,
+                    const size_t* raw_bytes, size_t n_str, const char* const* str_keys,
+                    const char* const* str_vals, size_t n_f32, const char* const* f32_keys,
+                    const float* f32_vals, size_t n_u32, const char* const* u32_keys,
+                    const uint32_t* u32_vals) {
+  return guarded([&] {
+    std::vector<G::SyntheticTensor> ts(n_tensors);
+    for (size_t t = 0; t < n_tensors; ++t) {
+      ts[t].name  = names[t];
+      ts[t].dtype = static_cast<G::GgmlType>(dtypes[t]);
+      ts[t].dims.assign(dims + 4 * t, dims + 4 * t + n_dims[t]);
+      ts[t].raw.assign(raw[t], raw[t] + raw_bytes[t]);
+    }
+    G::SyntheticKV kv;
+    for (size_t i = 0; i < n_str; ++i) kv.strings[str_keys[i]] = str_vals[i];
+    for (size_t i = 0; i < n_f32; ++i) kv.f32[f32_keys[i]] = f32_vals[i];
+    for (size_t i = 0; i < n_u32; ++i) kv.u32[u32_keys[i]] = u32_vals[i];
+    G::write_synthetic_gguf(path, ts, kv);
+  });
+}
+
+// src/KokkosDNN_GGUF.hpp:462 GgufFile(path) + :516 find + :584 payload — the reference's own reader on
+// a file. out8 = {dtype, n_dims, dims[0..3], offset, nbytes}; copies up to `cap` payload bytes.
+int kref_gguf_read_tensor(const char* path, const char* name, uint64_t* out8, uint64_t* data_start,
+                          uint8_t* payload, size_t cap) {
+  return guarded([&] {
+    G::GgufFile f(path);
+    const G::GgufTensorInfo& ti = f.find(name);
+    out8[0] = static_cast<uint64_t>(ti.dtype);
+    out8[1] = ti.n_dims;
+    for (uint32_t d = 0; d < 4; ++d) out8[2 + d] = d < ti.n_dims ? ti.dims[d] : 0;
+    out8[6] = ti.offset;
+    out8[7] = ti.nbytes;
+    *data_start = f.data_start();
+    const size_t n = cap < (size_t)ti.nbytes ? cap : (size_t)ti.nbytes;
+    if (n) std::memcpy(payload, f.payload(ti), n);
+  });
+}
+
+// src/KokkosDNN_GGUF.hpp:527/543/554 kv_string / kv_f32 / kv_u32. kind 0 string (into buf), 1 f32, 2 u32.
+int kref_gguf_read_kv(const char* path, const char* key, int kind, char* buf, size_t cap, float* f32,
+                      uint32_t* u32) {
+  return guarded([&] {
+    G::GgufFile f(path);
+    if (kind == 0) {
+      std::snprintf(buf, cap, "%s", f.kv_string(key).c_str());
+    } else if (kind == 1) {
+      *f32 = f.kv_f32(key);
+    } else {
+      *u32 = f.kv_u32(key);
     }
   });
 }

@@ -15,6 +15,15 @@ from oracle import oracle as O  # noqa: E402
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def gguf_fixture_tensors(gp):
+    """Tensors of the container fixture: seeded, so the reader test regenerates the expected bytes."""
+    return [("token_embd.weight", [256, 4], O.Q6_K, gp.random_payload(O.Q6_K, 4, 256, 901)),
+            ("blk.0.ffn_gate_exps.weight", [256, 5, 3], O.Q4_K, gp.random_payload(O.Q4_K, 15, 256, 902)),
+            ("blk.0.attn_q.weight", [64, 3], O.Q8_0, gp.random_payload(O.Q8_0, 3, 64, 903)),
+            ("blk.1.ffn_down.weight", [512, 2], O.Q5_K, gp.random_payload(O.Q5_K, 2, 512, 904)),
+            ("output_norm.weight", [7], 0, np.arange(7, dtype=np.float32) * 0.5)]
+
+
 def main():
     O.build()
     ref = O.Ref()
@@ -76,6 +85,11 @@ def main():
     m.update(gate=np.stack(gate), up=np.stack(up), down=np.stack(down), x=x, idx=idx, wts=wts, Y=Y, act=act,
              meta=np.array([E, H, F, S], dtype=np.int64))
     np.savez_compressed(os.path.join(HERE, "moe_decode_fp.npz"), **m)
+    # a container written by the reference's own writer (tests/test_gguf_io.py reads it back)
+    ref.gguf_write(os.path.join(HERE, "ref_written.gguf"), gguf_fixture_tensors(gp),
+                   strings={"general.architecture": "lfm2moe", "general.name": "fixture"},
+                   f32={"lfm2moe.attention.layer_norm_rms_epsilon": 1e-5},
+                   u32={"lfm2moe.block_count": 2, "lfm2moe.expert_count": 3})
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
