@@ -343,16 +343,15 @@ def run_ours(args):
                 "peak": peak, "peak_source": f"{peak_kind} HBM copy bandwidth (MEASURED_PEAKS.json)",
                 "unit": "GB/s", "frac": dom["frac"], "frac_of_nominal_8TBps": dom["achieved_GBps"] / 8000.0,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
-                # profiles/gemv_stream_q4k_14336x4096_ncu_full.md (algorithmic bytes: 33,095,680)
+                # profiles/gemv_q4k_14336x4096_ncu_sections.md (algorithmic bytes: 33,095,680)
                 "traffic": 33074944, "by_shape": per_kernel}
 
     # ---- end to end through the public call with host buffers --------------------------
     def e2e_pass():
         for ws in sets:
             for i, w in enumerate(ws):
-                xs[i].copy_(xs_host[i], non_blocking=True)
-                kd.quant_gemv(xs[i], w, ys[i], scr[i])
-                ys_host[i].copy_(ys[i], non_blocking=True)
+                # one C-ABI call: pinned x -> device, GEMV, y -> pinned host memory
+                kd.quant_gemv_host(xs_host[i], w, ys_host[i], xs[i], ys[i], scr[i])
 
     with torch.cuda.stream(stream):
         for _ in range(3):
@@ -365,6 +364,8 @@ def run_ours(args):
             e2e_pass()
         stream.synchronize()
     e2e_s = time.perf_counter() - t0
+    if not all(torch.equal(h, f.cpu()) for h, f in zip(ys_host, ys_first)):
+        raise RuntimeError("the host-buffer pass did not deliver the results of the device-resident pass")
     t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

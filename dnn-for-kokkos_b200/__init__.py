@@ -41,6 +41,7 @@ EXPORTS = [
     "kdnn_b200_unit_dots", "kdnn_b200_gemm_workspace_bytes", "kdnn_b200_quant_gemm",
     "kdnn_b200_moe_route", "kdnn_b200_moe_workspace_bytes", "kdnn_b200_moe_ffn",
     "kdnn_b200_residual_rmsnorm", "kdnn_b200_dequant_to_dense", "kdnn_b200_quant_gemv_fp",
+    "kdnn_b200_quant_gemv_host",
 ]
 
 
@@ -70,6 +71,9 @@ def _load() -> C.CDLL:
                                          C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.kdnn_b200_quant_gemv_noalloc.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                                  C.c_int, C.c_void_p, C.c_int, C.c_void_p]
+    lib.kdnn_b200_quant_gemv_host.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int,
+                                              C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                                              C.c_void_p]
     lib.kdnn_b200_quantize_act_q8.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t,
                                               C.c_void_p]
     lib.kdnn_b200_unit_dots.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
@@ -170,6 +174,12 @@ def load_expert_weights(file: GgufFile, info: GgufTensorInfo, device="cuda") -> 
     return gguf_io.load_expert_weights(sys.modules[__name__], file, info, device)
 
 
+def tensor_to_float(file: GgufFile, info: GgufTensorInfo, device="cuda") -> torch.Tensor:
+    """Gguf::dequant_tensor_to_float (src/KokkosDNN_GGUF.hpp:778-846): any tensor of the file as fp32."""
+    import sys
+    return gguf_io.tensor_to_float(sys.modules[__name__], file, info, device)
+
+
 def _quant_check(w: QuantWeight, what: str) -> None:
     # Impl::quant_check, src/KokkosDNN_GGUF.hpp:1993-2006
     if w.dtype not in (Q8_0, Q4_K, Q5_K, Q6_K):
@@ -206,6 +216,30 @@ def quant_gemv(x: torch.Tensor, w: QuantWeight, y: torch.Tensor, act_scratch: to
                                   y.data_ptr(), _scalar(y), act_scratch.data_ptr(), act_scratch.numel(),
                                   _stream())
     _check(rc, "quant_gemv")
+
+
+def quant_gemv_host(x_host: torch.Tensor, w: QuantWeight, y_host: torch.Tensor, x_dev: torch.Tensor,
+                    y_dev: torch.Tensor, act_scratch: torch.Tensor) -> None:
+    """quant_gemv with the activations and the result in host memory (pinned for the copies to be
+    asynchronous): copy in, GEMV, copy out, all enqueued by one call of kdnn_b200_quant_gemv_host on the
+    current stream. y_host is valid after the stream has been synchronised."""
+    if x_host.numel() != w.cols or y_host.numel() != w.rows or x_dev.numel() != w.cols or y_dev.numel() != w.rows:
+        raise ValueError("quant_gemv: dimension mismatch")
+    _quant_check(w, "quant_gemv")
+    if w.rows == 0 or w.cols == 0:
+        return
+    if x_host.is_cuda or y_host.is_cuda:
+        raise ValueError("quant_gemv_host: x_host / y_host must be host tensors")
+    if x_host.dtype != x_dev.dtype or y_host.dtype != y_dev.dtype:
+        raise ValueError("quant_gemv_host: host and device buffers must share a dtype")
+    for t, n in ((x_dev, "x_dev"), (y_dev, "y_dev"), (w.data, "w"), (act_scratch, "act_scratch")):
+        _cuda(t, n)
+    if not (x_host.is_contiguous() and y_host.is_contiguous() and x_dev.is_contiguous() and y_dev.is_contiguous()):
+        raise Declined("quant_gemv_host: non-unit stride")
+    rc = lib.kdnn_b200_quant_gemv_host(w.dtype, w.data.data_ptr(), w.rows, w.cols, x_host.data_ptr(), _scalar(x_dev),
+                                       y_host.data_ptr(), _scalar(y_dev), x_dev.data_ptr(), y_dev.data_ptr(),
+                                       act_scratch.data_ptr(), act_scratch.numel(), _stream())
+    _check(rc, "quant_gemv_host")
 
 
 NOALLOC_MAX_COLS = 32768

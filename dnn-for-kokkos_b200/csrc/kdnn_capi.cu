@@ -111,6 +111,30 @@ int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t 
                      "quant_gemv");
 }
 
+int kdnn_b200_quant_gemv_host(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                              const void* x_host, int x_scalar, void* y_host, int y_scalar, void* x_dev,
+                              void* y_dev, void* act_scratch, size_t act_scratch_bytes, void* stream) {
+  if (!scalar_ok(x_scalar) || !scalar_ok(y_scalar))
+    return fail(KDNN_ERR_INVALID, "quant_gemv_host: scalar must be KDNN_F32 or KDNN_BF16");
+  if (x_host == nullptr || y_host == nullptr) return fail(KDNN_ERR_INVALID, "quant_gemv_host: null host buffer");
+  // everything that can decline is checked before the first copy is enqueued
+  if (!int8_type(ggml_type) || w == nullptr || act_scratch == nullptr || x_dev == nullptr || y_dev == nullptr ||
+      !kdnn::block_aligned(ggml_type, cols) || rows == 0 || rows > static_cast<size_t>(INT_MAX) ||
+      cols > static_cast<size_t>(INT_MAX) || act_scratch_bytes < kdnn::act_bytes(cols) ||
+      (reinterpret_cast<uintptr_t>(act_scratch) & 15u) != 0u || (reinterpret_cast<uintptr_t>(w) & 1u) != 0u ||
+      ((ggml_type == KDNN_GGML_Q4_K || ggml_type == KDNN_GGML_Q5_K) && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u))
+    return KDNN_DECLINED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t xb = x_scalar == KDNN_F32 ? 4 : 2, yb = y_scalar == KDNN_F32 ? 4 : 2;
+  cudaError_t e = cudaMemcpyAsync(x_dev, x_host, cols * xb, cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) return cuda_result(e, "quant_gemv_host: copy of x");
+  const int rc = kdnn_b200_quant_gemv(ggml_type, w, rows, cols, x_dev, x_scalar, y_dev, y_scalar, act_scratch,
+                                      act_scratch_bytes, stream);
+  if (rc != KDNN_OK) return rc;
+  return cuda_result(cudaMemcpyAsync(y_host, y_dev, rows * yb, cudaMemcpyDeviceToHost, st),
+                     "quant_gemv_host: copy of y");
+}
+
 int kdnn_b200_quantize_act_q8(const void* x, int x_scalar, size_t K, void* scratch,
                               size_t scratch_bytes, void* stream) {
   if (!scalar_ok(x_scalar)) return fail(KDNN_ERR_INVALID, "quantize_act_q8: bad scalar");

@@ -2,6 +2,7 @@
 // geometry, the per-32 int8 activation quantizer, and the mbarrier / bulk-copy
 // (TMA 1-D) wrappers.
 #pragma once
+#include <stdlib.h>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -269,6 +270,40 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 __device__ __forceinline__ void pdl_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Both at the top of a kernel of a chain: the next kernel may be scheduled as soon as SM resources free up
+// (it then sits in its own wait), and nothing of this kernel runs before everything earlier in the stream
+// has completed and is visible. Without the launch attribute below both are no-ops.
+__device__ __forceinline__ void pdl_chain_entry() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+// KDNN_NO_PDL=1 launches without programmatic stream serialization (A/B aid).
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("KDNN_NO_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+// Launches a kernel that begins with pdl_chain_entry() (never one that does not: it would start early).
+// `early` = false gives a plain launch: a grid of about one wave placed while the previous kernel still
+// holds some SMs lands two CTAs on the free SMs and none on the busy ones, and stays that unbalanced.
+template <class... KArgs, class... Args>
+inline cudaError_t launch_chained_if(bool early, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = early && pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+template <class... KArgs, class... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args&&... args) {
+  return launch_chained_if(true, kern, grid, block, smem, st, static_cast<Args&&>(args)...);
 }
 
 }  // namespace kdnn

@@ -49,6 +49,7 @@ cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const vo
     q.N = (int)N; q.K = (int)K; q.offs = offs; q.list = list; q.S = 1; q.g_first = 0;
     q.xrows = xrows; q.x_pitch = act_row_pitch(K); q.dst = Y; q.ld_dst = ldy; q.status = moe_status_ptr();
     q.passes_z = static_cast<int>(M <= 32 ? 1 : (M + 31) / 32 > 4 ? 4 : (M + 31) / 32);
+    q.early = M <= 8;   // the row quantizer in front of it is then a handful of CTAs
     if (tile_kind() == 2)
       return ys == KDNN_F32 ? launch_grouped_umma<2, float>(q, 1, st) : launch_grouped_umma<2, __nv_bfloat16>(q, 1, st);
     return ys == KDNN_F32 ? launch_grouped_mma<2, float>(q, 1, st) : launch_grouped_mma<2, __nv_bfloat16>(q, 1, st);

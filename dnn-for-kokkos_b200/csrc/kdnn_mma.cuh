@@ -35,6 +35,7 @@ struct MmaParams {
   int* status;
   int passes_z;          // CTAs along z that share a group's 32-row passes (0 = 1)
   int ablate;            // debug: 1 skip the MMA loop, 2 skip the scale table, 4 skip activation staging
+  int early;             // launch as a programmatic dependent (only worth it behind a tiny kernel, see launch_chained_if)
 };
 
 __device__ __forceinline__ int4 lds128_g(uint32_t a) {
@@ -181,6 +182,7 @@ template <int MODE, class YT>
 __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(const MmaParams p) {
   using L = M2Layout<MODE>;
   extern __shared__ __align__(128) uint8_t m2_smem[];
+  pdl_chain_entry();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const int g   = blockIdx.y;
@@ -400,8 +402,7 @@ static cudaError_t launch_grouped_mma(const MmaParams& p, int groups, cudaStream
   MmaParams q = p;
   static const int ablate = [] { const char* e = getenv("KDNN_TILE_ABLATE"); return e ? atoi(e) : 0; }();
   q.ablate = ablate;
-  kern<<<grid, kM2Warps * 32, L::total, st>>>(q);
-  return cudaGetLastError();
+  return launch_chained_if(p.early != 0, kern, grid, dim3(kM2Warps * 32), L::total, st, q);
 }
 
 // Batched form of the reference's stage-1 quantizer: row r of `src` (pitch ld
@@ -411,6 +412,7 @@ template <class SRC>
 __global__ void quantize_rows_kernel(const SRC* __restrict__ src, size_t ld, int nrows, int K,
                                      const int* __restrict__ nrows_dev, uint8_t* __restrict__ dst,
                                      size_t pitch_bytes) {
+  pdl_chain_entry();
   const int row = blockIdx.y;
   if (row >= nrows || (nrows_dev && row >= *nrows_dev)) return;
   const int nblk    = K / 32;
@@ -445,8 +447,8 @@ static cudaError_t launch_quantize_rows(const SRC* src, size_t ld, int nrows, in
                                         uint8_t* dst, size_t pitch_bytes, cudaStream_t st) {
   if (nrows <= 0) return cudaSuccess;
   const int bx = max(1, min(8, (K / 32 + 63) / 64));
-  quantize_rows_kernel<SRC><<<dim3(bx, nrows), 256, 0, st>>>(src, ld, nrows, K, nrows_dev, dst, pitch_bytes);
-  return cudaGetLastError();
+  return launch_chained(quantize_rows_kernel<SRC>, dim3(bx, nrows), dim3(256), 0, st, src, ld, nrows, K, nrows_dev, dst,
+                        pitch_bytes);
 }
 
 // Row layout of the quantized activation rows: the reference staging layout (int8 xq[K], at

@@ -39,6 +39,7 @@ __global__ void moe_route_kernel(const ST* __restrict__ logits, size_t ld, int T
                                  const ST* __restrict__ bias, int top_k, int norm_topk,
                                  float routed_scale, int sigmoid, int32_t* __restrict__ top_idx,
                                  float* __restrict__ top_w) {
+  pdl_chain_entry();
   extern __shared__ float route_smem[];
   constexpr float NEG = -3.4028235e38f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
@@ -122,14 +123,13 @@ cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, 
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
   const int blocks = static_cast<int>((T + wpb - 1) / wpb);
   if (scalar == KDNN_F32)
-    moe_route_kernel<float><<<blocks, wpb * 32, smem, st>>>(
-        static_cast<const float*>(logits), ld, (int)T, (int)E, static_cast<const float*>(bias), top_k,
-        norm_topk, routed_scale, sigmoid, top_idx, top_w);
-  else
-    moe_route_kernel<__nv_bfloat16><<<blocks, wpb * 32, smem, st>>>(
-        static_cast<const __nv_bfloat16*>(logits), ld, (int)T, (int)E,
-        static_cast<const __nv_bfloat16*>(bias), top_k, norm_topk, routed_scale, sigmoid, top_idx, top_w);
-  return cudaGetLastError();
+    return launch_chained(moe_route_kernel<float>, dim3(blocks), dim3(wpb * 32), smem, st,
+                          static_cast<const float*>(logits), ld, (int)T, (int)E, static_cast<const float*>(bias),
+                          top_k, norm_topk, routed_scale, sigmoid, top_idx, top_w);
+  return launch_chained(moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(wpb * 32), smem, st,
+                        static_cast<const __nv_bfloat16*>(logits), ld, (int)T, (int)E,
+                        static_cast<const __nv_bfloat16*>(bias), top_k, norm_topk, routed_scale, sigmoid, top_idx,
+                        top_w);
 }
 
 // ---- slot sort ---------------------------------------------------------------------
@@ -147,6 +147,7 @@ cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, 
 __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_slots, int e_first,
                                 int e_count, int* __restrict__ offs, int* __restrict__ list,
                                 int* __restrict__ pos, int cache_slots) {
+  pdl_chain_entry();
   extern __shared__ int sort_smem[];  // counts[e_count], cursor[e_count], then (when it fits) the local expert of every slot
   int* counts = sort_smem;
   int* cursor = sort_smem + e_count;
@@ -209,6 +210,7 @@ template <class YT>
 __global__ void moe_combine_kernel(const float* __restrict__ out, const int* __restrict__ pos,
                                    const float* __restrict__ wts, int T, int S, int H, YT* Y,
                                    size_t ldy) {
+  pdl_chain_entry();
   const int t = blockIdx.y;
   const int d = blockIdx.x * blockDim.x + threadIdx.x;
   if (d >= H) return;
@@ -228,6 +230,7 @@ template <class YT>
 __global__ void moe_combine4_kernel(const float* __restrict__ out, const int* __restrict__ pos,
                                     const float* __restrict__ wts, int T, int S, int H, YT* Y,
                                     size_t ldy) {
+  pdl_chain_entry();
   const int t = blockIdx.y;
   const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (d >= H) return;
@@ -304,9 +307,9 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
   const int n_slots = static_cast<int>(T * S);
   const int sort_ctas = static_cast<int>(e_count < 4 ? 1 : (e_count + 3) / 4 > 64 ? 64 : (e_count + 3) / 4);
   const int cache_slots = n_slots <= 8192;   // the sweeps then read shared memory instead of global memory
-  moe_sort_kernel<<<sort_ctas, 128, (2 * (e_count + 1) + (cache_slots ? n_slots : 0)) * sizeof(int), st>>>(
-      idx, n_slots, (int)e_first, (int)e_count, offs, list, pos, cache_slots);
-  cudaError_t err = cudaGetLastError();
+  cudaError_t err = launch_chained(moe_sort_kernel, dim3(sort_ctas), dim3(128),
+                                   (2 * (e_count + 1) + (cache_slots ? n_slots : 0)) * sizeof(int), st, idx, n_slots,
+                                   (int)e_first, (int)e_count, offs, list, pos, cache_slots);
   if (err != cudaSuccess) return err;
   const bool all_q4k = gate->ggml_type == KDNN_GGML_Q4_K && down->ggml_type == KDNN_GGML_Q4_K &&
                        (reinterpret_cast<uintptr_t>(ws) & 15u) == 0;
@@ -330,6 +333,7 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
     const int mean_rows = static_cast<int>((static_cast<size_t>(n_slots) + gate->n_experts - 1) / gate->n_experts);
     const int passes_z  = max(1, min(4, 1 + (2 * mean_rows) / 32));
     g.passes_z = passes_z;
+    g.early = T <= 8;   // one-token decode: the row quantizer in front of it is a handful of CTAs
     const bool fused_q = tile_kind() != 2 && F % 64 == 0;
     if (fused_q) {
       g.qdst    = arows;
@@ -380,20 +384,17 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
   if (vec4) {
     dim3 cgrid((unsigned)((H / 4 + 127) / 128), (unsigned)T);
     if (ys == KDNN_F32)
-      moe_combine4_kernel<float><<<cgrid, 128, 0, st>>>(out, pos, wts, (int)T, (int)S, (int)H, static_cast<float*>(Y), ldy);
-    else
-      moe_combine4_kernel<__nv_bfloat16><<<cgrid, 128, 0, st>>>(out, pos, wts, (int)T, (int)S, (int)H,
-                                                                static_cast<__nv_bfloat16*>(Y), ldy);
-    return cudaGetLastError();
+      return launch_chained(moe_combine4_kernel<float>, cgrid, dim3(128), 0, st, out, pos, wts, (int)T, (int)S, (int)H,
+                            static_cast<float*>(Y), ldy);
+    return launch_chained(moe_combine4_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, st, out, pos, wts, (int)T, (int)S,
+                          (int)H, static_cast<__nv_bfloat16*>(Y), ldy);
   }
   dim3 cgrid((unsigned)((H + 255) / 256), (unsigned)T);
   if (ys == KDNN_F32)
-    moe_combine_kernel<float><<<cgrid, 256, 0, st>>>(out, pos, wts, (int)T, (int)S, (int)H,
-                                                     static_cast<float*>(Y), ldy);
-  else
-    moe_combine_kernel<__nv_bfloat16><<<cgrid, 256, 0, st>>>(out, pos, wts, (int)T, (int)S, (int)H,
-                                                             static_cast<__nv_bfloat16*>(Y), ldy);
-  return cudaGetLastError();
+    return launch_chained(moe_combine_kernel<float>, cgrid, dim3(256), 0, st, out, pos, wts, (int)T, (int)S, (int)H,
+                          static_cast<float*>(Y), ldy);
+  return launch_chained(moe_combine_kernel<__nv_bfloat16>, cgrid, dim3(256), 0, st, out, pos, wts, (int)T, (int)S,
+                        (int)H, static_cast<__nv_bfloat16*>(Y), ldy);
 }
 
 // out[t,:] = Scalar(r / sqrt(mean(r^2) + eps)) with r = Scalar(float(h[t,:]) + y[t,:]): the residual
@@ -402,6 +403,7 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
 template <class ST>
 __global__ void residual_rmsnorm_kernel(const ST* __restrict__ h, size_t ldh, const float* __restrict__ y,
                                         size_t ldy, ST* __restrict__ out, size_t ldo, int H, float eps) {
+  pdl_chain_entry();
   __shared__ float red[32];
   const int t = blockIdx.x;
   float ss = 0.f;
@@ -431,12 +433,11 @@ __global__ void residual_rmsnorm_kernel(const ST* __restrict__ h, size_t ldh, co
 cudaError_t residual_rmsnorm_launch(const void* h, size_t ldh, const float* y, size_t ldy, void* out,
                                     size_t ldo, size_t T, size_t H, float eps, int scalar, cudaStream_t st) {
   if (scalar == KDNN_F32)
-    residual_rmsnorm_kernel<float><<<(unsigned)T, 256, 0, st>>>(static_cast<const float*>(h), ldh, y, ldy,
-                                                                static_cast<float*>(out), ldo, (int)H, eps);
-  else
-    residual_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)T, 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(h), ldh, y, ldy, static_cast<__nv_bfloat16*>(out), ldo, (int)H, eps);
-  return cudaGetLastError();
+    return launch_chained(residual_rmsnorm_kernel<float>, dim3((unsigned)T), dim3(256), 0, st,
+                          static_cast<const float*>(h), ldh, y, ldy, static_cast<float*>(out), ldo, (int)H, eps);
+  return launch_chained(residual_rmsnorm_kernel<__nv_bfloat16>, dim3((unsigned)T), dim3(256), 0, st,
+                        static_cast<const __nv_bfloat16*>(h), ldh, y, ldy, static_cast<__nv_bfloat16*>(out), ldo,
+                        (int)H, eps);
 }
 
 int moe_take_status() {

@@ -214,6 +214,31 @@ def load_expert_weights(kd, file: GgufFile, info: GgufTensorInfo, device="cuda")
     return [kd.QuantWeight(data[e * stride:e * stride + per], info.dtype, rows, cols) for e in range(experts)]
 
 
+def tensor_to_float(kd, file: GgufFile, info: GgufTensorInfo, device="cuda"):
+    """A whole tensor as fp32 on `device`, shaped [numel / cols, cols] (dequant_tensor_to_float,
+    src/KokkosDNN_GGUF.hpp:778-846). F32 / F16 / BF16 widen exactly on any device; the packed types go to the
+    GPU packed and are expanded there by dequant_to_dense, whose fp32 output equals the reference's block
+    formulas bit for bit -- they need a CUDA device."""
+    import torch
+    cols = info.cols()
+    rows = info.numel // cols if cols else 0
+    raw = file.payload(info)
+    if info.dtype == 0:
+        return torch.from_numpy(np.array(raw).view(np.float32)).view(rows, cols).to(device)
+    if info.dtype == 1:
+        return torch.from_numpy(np.array(raw).view(np.float16)).view(rows, cols).to(device).float()
+    if info.dtype == 30:
+        return torch.from_numpy(np.array(raw).view(np.int16)).view(torch.bfloat16).view(rows, cols).to(device).float()
+    if info.dtype not in COMPUTE_TYPES:
+        raise RuntimeError(f"tensor_to_float: unsupported dtype {info.dtype}")
+    if torch.device(device).type != "cuda":
+        raise RuntimeError("tensor_to_float: packed types are expanded on the GPU; pass a CUDA device")
+    w = kd.QuantWeight(torch.from_numpy(np.array(raw)).to(device), info.dtype, rows, cols)
+    out = torch.empty(rows, cols, dtype=torch.float32, device=device)
+    kd.dequant_to_dense(w, out)
+    return out
+
+
 # ---- writer (tests, synthetic checkpoints) ----------------------------------------------
 def _pack_string(s: str) -> bytes:
     b = s.encode("utf-8")

@@ -109,6 +109,16 @@ int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t 
 int kdnn_b200_quant_gemv_noalloc(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
                                  const void* x, int x_scalar, void* y, int y_scalar, void* stream);
 
+/* kdnn_b200_quant_gemv for a host that keeps activations and results in its own (ideally page-locked)
+ * memory: one call enqueues the copy of x_host[cols] to x_dev, the GEMV, and the copy of y_dev[rows] to
+ * y_host on `stream`, and returns without waiting; y_host is valid once the stream has been synchronised.
+ * x_dev, y_dev and act_scratch are the caller's device buffers (nothing is allocated). A declined or
+ * failed call has enqueued nothing. In the reference this is the host's deep_copy, quant_gemv, deep_copy
+ * sequence around src/KokkosDNN_GGUF.hpp:2531-2551 folded into one call; same decline list and results. */
+int kdnn_b200_quant_gemv_host(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                              const void* x_host, int x_scalar, void* y_host, int y_scalar, void* x_dev,
+                              void* y_dev, void* act_scratch, size_t act_scratch_bytes, void* stream);
+
 /* Stage 1 alone: quantize one activation row into `scratch` (layout above).
  * Stands in for Impl::GgufMvq::QuantizeActQ8Functor, src/KokkosDNN_GGUFGemvInt8.hpp:198-239. */
 int kdnn_b200_quantize_act_q8(const void* x, int x_scalar, size_t K, void* scratch,

@@ -58,6 +58,27 @@ def test_gemv_declines_without_launching(kd):
     assert call(t=kd.Q5_K, cols=128) == kd.KDNN_DECLINED
 
 
+def test_host_gemv_declines_before_any_copy(kd):
+    """kdnn_b200_quant_gemv_host checks the whole decline list first: a declined call has enqueued no copy
+    (the fake pointers would fault one)."""
+    f = kd.lib.kdnn_b200_quant_gemv_host
+    W, XH, YH, XD, YD, S = 0x10000, 0x20000, 0x30000, 0x40000, 0x50000, 0x60000
+    need = kd.quant_gemv_int8_scratch_bytes(512)
+    ok = dict(t=kd.Q4_K, w=W, rows=4, cols=512, xh=XH, yh=YH, xd=XD, yd=YD, s=S, sb=need, xs=0)
+
+    def call(**kw):
+        a = dict(ok, **kw)
+        return f(a["t"], a["w"], a["rows"], a["cols"], a["xh"], a["xs"], a["yh"], 0, a["xd"], a["yd"], a["s"],
+                 a["sb"], None)
+
+    for kw in (dict(w=None), dict(s=None), dict(xd=None), dict(yd=None), dict(cols=128), dict(rows=0),
+               dict(sb=need // 2), dict(s=S + 8), dict(w=W + 1), dict(w=W + 2), dict(t=0)):
+        assert call(**kw) == kd.KDNN_DECLINED, kw
+    assert call(xh=None) == kd.KDNN_ERR_INVALID
+    assert call(yh=None) == kd.KDNN_ERR_INVALID
+    assert call(xs=7) == kd.KDNN_ERR_INVALID
+
+
 def test_invalid_arguments_raise(kd):
     import torch
     w = kd.QuantWeight(torch.zeros(2 * 34, dtype=torch.uint8), kd.Q8_0, 1, 64)

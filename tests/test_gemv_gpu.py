@@ -239,3 +239,26 @@ def test_q5k_lm_head_like_shape(kd, port):
     """Q4_K_M files keep their largest matrices in Q5_K (src/KokkosDNN_GGUF.hpp:13-19)."""
     _check(kd, port, O.Q5_K, 16000, 4096, 404, "random", torch.bfloat16, torch.float32, probe=False)
     _check(kd, port, O.Q5_K, 64, 4096, 405, "random", torch.bfloat16, torch.bfloat16, probe=False)
+
+
+@pytest.mark.parametrize("dtype", DTYPES_RANDOM)
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+def test_host_buffer_call_matches_the_device_call(kd, dtype, x_dtype):
+    """kdnn_b200_quant_gemv_host = copy in, the same GEMV, copy out: bit-identical results."""
+    dev = torch.device("cuda:0")
+    rows, K = 517, 2048
+    w = kd.QuantWeight.from_numpy(kd.ggml_pack.random_payload(dtype, rows, K, 77), dtype, rows, K, dev)
+    x_host = torch.randn(K, generator=torch.Generator().manual_seed(78)).to(x_dtype).pin_memory()
+    y_host = torch.full((rows,), float("nan")).pin_memory()
+    x_dev, y_dev = torch.zeros(K, dtype=x_dtype, device=dev), torch.zeros(rows, device=dev)
+    y_want = torch.empty(rows, device=dev)
+    scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+    kd.quant_gemv(x_host.to(dev), w, y_want, scratch)
+    for _ in range(2):                       # the second call reuses every buffer
+        y_host.fill_(float("nan"))
+        kd.quant_gemv_host(x_host, w, y_host, x_dev, y_dev, scratch)
+        torch.cuda.synchronize()
+        assert torch.equal(y_host, y_want.cpu())
+    assert kd.device_status() == 0
+    with pytest.raises(ValueError, match="host tensors"):
+        kd.quant_gemv_host(x_dev, w, y_host, x_dev, y_dev, scratch)

@@ -212,3 +212,36 @@ def test_reference_writer_round_trip(kd, ref, tmp_path):
     assert (t.dtype, t.dims, t.offset, t.nbytes, f.data_start) == (rd, rdims, roff, rbytes, rstart)
     assert np.array_equal(f.payload(t), payload) and np.array_equal(payload, w.reshape(-1))
     assert f.kv == {"k": "v", "n": 4}
+
+
+def test_dense_tensors_widen_exactly(kd, tmp_path):
+    g = torch.Generator().manual_seed(5)
+    a32 = torch.randn(3, 8, generator=g)
+    a16 = torch.randn(2, 16, generator=g).half()
+    ab = torch.randn(4, 8, generator=g).bfloat16()
+    p = _file(kd, tmp_path, [("a32", [8, 3], 0, a32.numpy()), ("a16", [16, 2], 1, a16.numpy()),
+                             ("ab", [8, 4], 30, ab.view(torch.int16).numpy()), ("v", [5], 0, np.ones(5, np.float32)),
+                             ("q", [256, 1], kd.Q4_K, kd.ggml_pack.random_payload(kd.Q4_K, 1, 256, 1)),
+                             ("i", [4], 26, np.zeros(4, np.int32))])
+    f = kd.GgufFile(p)
+    assert torch.equal(kd.tensor_to_float(f, f.tensor("a32"), "cpu"), a32)
+    assert torch.equal(kd.tensor_to_float(f, f.tensor("a16"), "cpu"), a16.float())
+    assert torch.equal(kd.tensor_to_float(f, f.tensor("ab"), "cpu"), ab.float())
+    assert tuple(kd.tensor_to_float(f, f.tensor("v"), "cpu").shape) == (1, 5)
+    with pytest.raises(RuntimeError, match="CUDA device"):
+        kd.tensor_to_float(f, f.tensor("q"), "cpu")
+    with pytest.raises(RuntimeError, match="unsupported dtype"):
+        kd.tensor_to_float(f, f.tensor("i"), "cpu")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype_name", ["Q4_K", "Q5_K", "Q6_K", "Q8_0"])
+def test_packed_tensor_to_float_matches_the_block_formulas(kd, port, tmp_path, dtype_name):
+    from oracle import oracle as O
+    dtype = getattr(kd, dtype_name)
+    rows, K = 9, 512
+    packed = kd.ggml_pack.random_payload(dtype, rows, K, 41)
+    f = kd.GgufFile(_file(kd, tmp_path, [("w", [K, rows], dtype, packed)]))
+    got = kd.tensor_to_float(f, f.tensor("w")).cpu().numpy()
+    want = port.dequant_rows(dtype, O.aligned_copy(packed), rows, K)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
