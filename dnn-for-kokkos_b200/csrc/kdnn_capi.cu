@@ -68,6 +68,45 @@ int force_generic() {
   }
   return v;
 }
+// Copies between page-locked host memory and device memory done by a kernel over the mapped host
+// pointer instead of by the copy engine: on a stream that alternates small copies and short kernels the
+// engine hand-offs cost more than the kernels. Chained like every other kernel of the library, so the GEMV
+// that follows a pull prefetches its weights while the pull is in flight.
+__global__ void copy_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, size_t bytes) {
+  kdnn::pdl_chain_entry();
+  const size_t n16 = bytes / 16;
+  const size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = i0; i < n16; i += stride)
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  for (size_t i = n16 * 16 + i0; i < bytes; i += stride) dst[i] = src[i];
+}
+cudaError_t copy_bytes_launch(const void* src, void* dst, size_t bytes, cudaStream_t st) {
+  const unsigned blocks = static_cast<unsigned>(bytes / 16 / 256 + 1);
+  return kdnn::launch_chained(copy_bytes_kernel, dim3(blocks > 64 ? 64 : blocks), dim3(256), 0, st,
+                              static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), bytes);
+}
+// The device-side address of a host buffer when a kernel may touch it (page-locked or registered memory,
+// 16-byte aligned), else nullptr: pageable memory goes through cudaMemcpyAsync.
+void* mapped_host_pointer(const void* host) {
+  cudaPointerAttributes a{};
+  if (cudaPointerGetAttributes(&a, host) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (a.type != cudaMemoryTypeHost || a.devicePointer == nullptr) return nullptr;
+  if ((reinterpret_cast<uintptr_t>(a.devicePointer) & 15u) != 0u) return nullptr;
+  return a.devicePointer;
+}
+// KDNN_HOST_COPY=kernel: kdnn_b200_quant_gemv_host moves x and y with copy_bytes_kernel when the host
+// buffers allow it; anything else: cudaMemcpyAsync.
+bool host_copy_by_kernel() {
+  static const bool on = [] {
+    const char* e = getenv("KDNN_HOST_COPY");
+    return e != nullptr && e[0] == 'k';
+  }();
+  return on;
+}
 }  // namespace
 
 extern "C" {
@@ -126,13 +165,22 @@ int kdnn_b200_quant_gemv_host(uint32_t ggml_type, const void* w, size_t rows, si
     return KDNN_DECLINED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t xb = x_scalar == KDNN_F32 ? 4 : 2, yb = y_scalar == KDNN_F32 ? 4 : 2;
-  cudaError_t e = cudaMemcpyAsync(x_dev, x_host, cols * xb, cudaMemcpyHostToDevice, st);
+  void* xm = nullptr;
+  void* ym = nullptr;
+  if (host_copy_by_kernel() && (reinterpret_cast<uintptr_t>(x_dev) & 15u) == 0u &&
+      (reinterpret_cast<uintptr_t>(y_dev) & 15u) == 0u) {
+    xm = mapped_host_pointer(x_host);
+    ym = mapped_host_pointer(y_host);
+  }
+  cudaError_t e = xm ? copy_bytes_launch(xm, x_dev, cols * xb, st)
+                     : cudaMemcpyAsync(x_dev, x_host, cols * xb, cudaMemcpyHostToDevice, st);
   if (e != cudaSuccess) return cuda_result(e, "quant_gemv_host: copy of x");
   const int rc = kdnn_b200_quant_gemv(ggml_type, w, rows, cols, x_dev, x_scalar, y_dev, y_scalar, act_scratch,
                                       act_scratch_bytes, stream);
   if (rc != KDNN_OK) return rc;
-  return cuda_result(cudaMemcpyAsync(y_host, y_dev, rows * yb, cudaMemcpyDeviceToHost, st),
-                     "quant_gemv_host: copy of y");
+  e = ym ? copy_bytes_launch(y_dev, ym, rows * yb, st)
+         : cudaMemcpyAsync(y_host, y_dev, rows * yb, cudaMemcpyDeviceToHost, st);
+  return cuda_result(e, "quant_gemv_host: copy of y");
 }
 
 int kdnn_b200_quantize_act_q8(const void* x, int x_scalar, size_t K, void* scratch,
