@@ -113,7 +113,10 @@ int kdnn_b200_quant_gemv_noalloc(uint32_t ggml_type, const void* w, size_t rows,
  * memory: one call enqueues the copy of x_host[cols] to x_dev, the GEMV, and the copy of y_dev[rows] to
  * y_host on `stream`, and returns without waiting; y_host is valid once the stream has been synchronised.
  * x_dev, y_dev and act_scratch are the caller's device buffers (nothing is allocated). A declined or
- * failed call has enqueued nothing. In the reference this is the host's deep_copy, quant_gemv, deep_copy
+ * failed call has enqueued nothing. When the host buffers are page-locked (or registered) and 16-byte
+ * aligned the two copies are small kernels over the mapped host pointers, chained with the GEMV like every
+ * kernel of the library (the copy engine's hand-offs cost more than these kernels do); pageable buffers,
+ * or KDNN_HOST_COPY=dma in the environment, take cudaMemcpyAsync. In the reference this is the host's deep_copy, quant_gemv, deep_copy
  * sequence around src/KokkosDNN_GGUF.hpp:2531-2551 folded into one call; same decline list and results. */
 int kdnn_b200_quant_gemv_host(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
                               const void* x_host, int x_scalar, void* y_host, int y_scalar, void* x_dev,
