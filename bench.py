@@ -13,8 +13,10 @@ Metric: GB/s of algorithmic bytes (packed weight bytes + x + y per GEMV, the
 reference's own convention of counting the packed payload). ``roofline`` is the Q4_K
 14336x4096 GEMV alone, timed with CUDA events on the launch stream, against the
 measured HBM copy bandwidth in MEASURED_PEAKS.json. ``e2e`` is the same pass driven
-from pinned host buffers: per GEMV the activation row is copied host->device and the
-result row device->host inside the timed region. ``moe_decode`` carries the second
+from pinned host buffers through kdnn_b200_quant_gemv_host: per GEMV the activation row
+goes host->device and the result row device->host inside the timed region (the library
+moves page-locked buffers with small kernels over the mapped pointers; KDNN_HOST_COPY=dma
+in the environment times the copy engine instead), and the host results are checked. ``moe_decode`` carries the second
 headline number (tokens/s of the 48-layer, 128-expert, top-8 MoE stack at 256 tokens).
 
 With --gpus N > 1 (launched under torchrun) every rank runs the same GEMV pass on its

@@ -262,3 +262,20 @@ def test_host_buffer_call_matches_the_device_call(kd, dtype, x_dtype):
     assert kd.device_status() == 0
     with pytest.raises(ValueError, match="host tensors"):
         kd.quant_gemv_host(x_dev, w, y_host, x_dev, y_dev, scratch)
+
+
+def test_host_buffer_call_with_pageable_memory(kd):
+    """Pageable host buffers cannot be touched by a kernel: the call takes the copy engine for them."""
+    dev = torch.device("cuda:0")
+    rows, K = 129, 1024
+    w = kd.QuantWeight.from_numpy(kd.ggml_pack.random_payload(kd.Q4_K, rows, K, 79), kd.Q4_K, rows, K, dev)
+    x_host = torch.randn(K, generator=torch.Generator().manual_seed(80))
+    y_host = torch.full((rows,), float("nan"))
+    x_dev, y_dev = torch.zeros(K, device=dev), torch.zeros(rows, device=dev)
+    y_want = torch.empty(rows, device=dev)
+    scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+    kd.quant_gemv(x_host.to(dev), w, y_want, scratch)
+    kd.quant_gemv_host(x_host, w, y_host, x_dev, y_dev, scratch)
+    torch.cuda.synchronize()
+    assert torch.equal(y_host, y_want.cpu())
+    assert kd.device_status() == 0
