@@ -101,6 +101,27 @@ void quant_gemv(const ExecSpace& space, const XView& x, const QuantWeight& w, co
   fallback();
 }
 
+// The host's deep_copy(x_dev, x_host); quant_gemv(...); deep_copy(y_host, y_dev) around
+// src/KokkosDNN_GGUF.hpp:2531-2551 as one call: x_host / y_host are host views (page-locked for the
+// copies to be asynchronous), x_dev / y_dev / act_scratch device views. Returns false when the int8
+// path declined (nothing was enqueued); y_host is valid once the space has been fenced.
+template <class ExecSpace, class XHost, class QuantWeight, class YHost, class XView, class YView, class SView>
+bool quant_gemv_host(const ExecSpace& space, const XHost& x_host, const QuantWeight& w, const YHost& y_host,
+                     const XView& x_dev, const YView& y_dev, const SView& act_scratch) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(x_dev.data())>::type>::type;
+  if (x_host.extent(0) != w.cols || y_host.extent(0) != w.rows || x_dev.extent(0) != w.cols ||
+      y_dev.extent(0) != w.rows)
+    throw std::invalid_argument("quant_gemv: dimension mismatch");
+  if (w.rows == 0 || w.cols == 0) return true;
+  if (scalar_tag<Scalar>() < 0) throw std::invalid_argument("quant_gemv: Scalar must be float or bhalf_t");
+  const int rc = kdnn_b200_quant_gemv_host(static_cast<std::uint32_t>(w.dtype), w.data.data(), w.rows, w.cols,
+                                           x_host.data(), scalar_tag<Scalar>(), y_host.data(), scalar_tag<Scalar>(),
+                                           x_dev.data(), y_dev.data(), act_scratch.data(), act_scratch.extent(0),
+                                           StreamOf<ExecSpace>::get(space));
+  throw_on_error(rc, "quant_gemv_host");
+  return rc == KDNN_OK;
+}
+
 // Gguf::quant_gemv(handle, x, w, y) without staging (fp path), src/KokkosDNN_GGUF.hpp:2394-2493.
 template <class ExecSpace, class XView, class QuantWeight, class YView>
 void quant_gemv_fp(const ExecSpace& space, const XView& x, const QuantWeight& w, const YView& y) {

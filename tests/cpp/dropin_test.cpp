@@ -101,6 +101,14 @@ int main() {
     try { V1<float> bad(xv.data(), K / 2); B::quant_gemv(space, bad, w, yv, scratch, [] {}); }
     catch (const std::invalid_argument&) { threw = true; }
     CHECK(threw);
+    // host-resident activations: copy in, GEMV, copy out as one call; same bits as the device call
+    {
+      std::vector<float> yh(N, -1.f);
+      V1<float> xh(x.data(), K), yhv(yh.data(), N), yd(dmalloc<float>(N), N);
+      CHECK(B::quant_gemv_host(space, xh, w, yhv, xv, yd, scratch));
+      cudaDeviceSynchronize();
+      CHECK(std::memcmp(yh.data(), got.data(), N * sizeof(float)) == 0);
+    }
     CHECK((B::quant_gemv_int8_supported<Dev, float>(dt, K)));
     CHECK(!(B::quant_gemv_int8_supported<Dev, double>(dt, K)));
   }
