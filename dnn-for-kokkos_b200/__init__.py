@@ -35,9 +35,10 @@ F32, BF16 = 0, 1
 
 # every symbol include/kdnn_b200.h declares (checked by the CPU test-suite)
 EXPORTS = [
-    "kdnn_b200_last_error", "kdnn_b200_device_status", "kdnn_b200_debug_set_trace", "kdnn_b200_gemv_scratch_bytes",
-    "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quant_gemv_noalloc",
-    "kdnn_b200_quantize_act_q8",
+    "kdnn_b200_last_error", "kdnn_b200_device_status", "kdnn_b200_gemv_scratch_bytes",
+    "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quant_gemv_ex", "kdnn_b200_quant_gemv_noalloc",
+    "kdnn_b200_quant_gemv_noalloc_ex", "kdnn_b200_quantize_act_q8", "kdnn_b200_quant_gemm_dots", "kdnn_b200_tile_kind",
+    "kdnn_b200_weight_table_tma_bytes", "kdnn_b200_weight_table_tma_encode",
     "kdnn_b200_unit_dots", "kdnn_b200_gemm_workspace_bytes", "kdnn_b200_quant_gemm",
     "kdnn_b200_moe_route", "kdnn_b200_moe_workspace_bytes", "kdnn_b200_moe_ffn",
     "kdnn_b200_residual_rmsnorm", "kdnn_b200_dequant_to_dense", "kdnn_b200_quant_gemv_fp",
@@ -52,7 +53,18 @@ class Declined(RuntimeError):
 
 class WeightTableC(C.Structure):
     _fields_ = [("base", C.c_void_p), ("ggml_type", C.c_uint32), ("rows", C.c_size_t),
-                ("cols", C.c_size_t), ("row_bytes", C.c_size_t), ("n_experts", C.c_size_t)]
+                ("cols", C.c_size_t), ("row_bytes", C.c_size_t), ("n_experts", C.c_size_t),
+                ("tma", C.c_void_p)]
+
+
+class GemvLayoutC(C.Structure):
+    """kdnn_b200_gemv_layout: optional tuning of one GEMV call (all zero = defaults)."""
+    _fields_ = [("kernel", C.c_int), ("rows_per_group", C.c_int), ("stages", C.c_int),
+                ("early_stages", C.c_int), ("warps", C.c_int), ("no_pdl", C.c_int)]
+
+
+KERNEL_AUTO, KERNEL_XREG, KERNEL_SMEM_WINDOW, KERNEL_ITEM_STREAM, KERNEL_PLAIN_LOADS = 0, 1, 2, 3, 4
+TILE_DP4A, TILE_MMA_SYNC, TILE_TCGEN05 = 0, 1, 2
 
 
 def _load() -> C.CDLL:
@@ -62,15 +74,26 @@ def _load() -> C.CDLL:
             "(there is no CPU or PyTorch fallback)")
     lib = C.CDLL(LIB_PATH)
     lib.kdnn_b200_last_error.restype = C.c_char_p
-    lib.kdnn_b200_debug_set_trace.argtypes = [C.c_void_p]
-    lib.kdnn_b200_debug_set_trace.restype = None
     lib.kdnn_b200_gemv_scratch_bytes.restype = C.c_size_t
     lib.kdnn_b200_gemv_scratch_bytes.argtypes = [C.c_size_t]
     lib.kdnn_b200_gemv_supported.argtypes = [C.c_uint32, C.c_size_t, C.c_int]
     lib.kdnn_b200_quant_gemv.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                          C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_quant_gemv_ex.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
+                                            C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t,
+                                            C.POINTER(GemvLayoutC), C.c_void_p]
     lib.kdnn_b200_quant_gemv_noalloc.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                                  C.c_int, C.c_void_p, C.c_int, C.c_void_p]
+    lib.kdnn_b200_quant_gemv_noalloc_ex.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
+                                                    C.c_int, C.c_void_p, C.c_int, C.POINTER(GemvLayoutC), C.c_void_p]
+    lib.kdnn_b200_quant_gemm_dots.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
+                                              C.c_size_t, C.c_size_t, C.c_int, C.c_void_p, C.c_size_t, C.c_int,
+                                              C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_tile_kind.argtypes = [C.c_int]
+    lib.kdnn_b200_weight_table_tma_bytes.restype = C.c_size_t
+    lib.kdnn_b200_weight_table_tma_bytes.argtypes = [C.c_size_t]
+    lib.kdnn_b200_weight_table_tma_encode.argtypes = [C.c_void_p, C.c_uint32, C.c_size_t, C.c_size_t, C.c_size_t,
+                                                      C.c_void_p]
     lib.kdnn_b200_quant_gemv_host.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int,
                                               C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                               C.c_void_p]
@@ -198,11 +221,26 @@ def quant_gemv_int8_supported(dtype: int, K: int, scalar: torch.dtype = torch.fl
     return bool(lib.kdnn_b200_gemv_supported(dtype, K, s))
 
 
-def quant_gemv(x: torch.Tensor, w: QuantWeight, y: torch.Tensor, act_scratch: torch.Tensor) -> None:
+def tile_kind(kind: int = -1) -> int:
+    """Selects the tile kernel of the batched Q4_K calls (TILE_TCGEN05 default, TILE_MMA_SYNC, TILE_DP4A);
+    returns the previous selection. A negative kind only queries."""
+    return int(lib.kdnn_b200_tile_kind(kind))
+
+
+def _layout(layout):
+    if layout is None:
+        return None
+    if isinstance(layout, GemvLayoutC):
+        return C.byref(layout)
+    return C.byref(GemvLayoutC(**layout))
+
+
+def quant_gemv(x: torch.Tensor, w: QuantWeight, y: torch.Tensor, act_scratch: torch.Tensor, layout=None) -> None:
     """y[N] = W[N,K] x[K] on the int8 path (Gguf::quant_gemv(handle, x, w, y,
     act_scratch), src/KokkosDNN_GGUF.hpp:2531-2551). Raises ValueError where the
     reference throws std::invalid_argument and Declined where its launcher returns
-    false."""
+    false. `layout`: optional tuning (a GemvLayoutC or a dict of its fields), the counterpart of
+    Impl::GgufMvq::Int8Layout."""
     if x.numel() != w.cols or y.numel() != w.rows:
         raise ValueError("quant_gemv: dimension mismatch")
     _quant_check(w, "quant_gemv")
@@ -212,9 +250,9 @@ def quant_gemv(x: torch.Tensor, w: QuantWeight, y: torch.Tensor, act_scratch: to
         _cuda(t, n)
     if x.stride(0) != 1 or y.stride(0) != 1:
         raise Declined("quant_gemv: non-unit stride")
-    rc = lib.kdnn_b200_quant_gemv(w.dtype, w.data.data_ptr(), w.rows, w.cols, x.data_ptr(), _scalar(x),
-                                  y.data_ptr(), _scalar(y), act_scratch.data_ptr(), act_scratch.numel(),
-                                  _stream())
+    rc = lib.kdnn_b200_quant_gemv_ex(w.dtype, w.data.data_ptr(), w.rows, w.cols, x.data_ptr(), _scalar(x),
+                                     y.data_ptr(), _scalar(y), act_scratch.data_ptr(), act_scratch.numel(),
+                                     _layout(layout), _stream())
     _check(rc, "quant_gemv")
 
 
@@ -245,7 +283,7 @@ def quant_gemv_host(x_host: torch.Tensor, w: QuantWeight, y_host: torch.Tensor, 
 NOALLOC_MAX_COLS = 32768
 
 
-def quant_gemv_noalloc(x: torch.Tensor, w: QuantWeight, y: torch.Tensor) -> None:
+def quant_gemv_noalloc(x: torch.Tensor, w: QuantWeight, y: torch.Tensor, layout=None) -> None:
     """quant_gemv without a caller-owned staging buffer: for hosts that may not allocate device memory
     (see kdnn_b200_quant_gemv_noalloc). K is limited to NOALLOC_MAX_COLS; calls that overlap on the GPU
     race on the shared built-in staging."""
@@ -256,8 +294,10 @@ def quant_gemv_noalloc(x: torch.Tensor, w: QuantWeight, y: torch.Tensor) -> None
         return
     for t, n in ((x, "x"), (y, "y"), (w.data, "w")):
         _cuda(t, n)
-    rc = lib.kdnn_b200_quant_gemv_noalloc(w.dtype, w.data.data_ptr(), w.rows, w.cols, x.data_ptr(), _scalar(x),
-                                          y.data_ptr(), _scalar(y), _stream())
+    if x.stride(0) != 1 or y.stride(0) != 1:
+        raise Declined("quant_gemv_noalloc: non-unit stride")
+    rc = lib.kdnn_b200_quant_gemv_noalloc_ex(w.dtype, w.data.data_ptr(), w.rows, w.cols, x.data_ptr(), _scalar(x),
+                                             y.data_ptr(), _scalar(y), _layout(layout), _stream())
     _check(rc, "quant_gemv_noalloc")
 
 
@@ -292,6 +332,21 @@ def quant_gemm(X: torch.Tensor, w: QuantWeight, Y: torch.Tensor, workspace: torc
                                   _scalar(X), Y.data_ptr(), Y.stride(0), _scalar(Y),
                                   workspace.data_ptr(), workspace.numel(), _stream())
     _check(rc, "quant_gemm")
+
+
+def quant_gemm_dots(X: torch.Tensor, w: QuantWeight, Y: torch.Tensor, workspace: torch.Tensor) -> torch.Tensor:
+    """quant_gemm on the tcgen05 tile kernel, also returning the raw int32 sub-block dots [M, N, K/32] the
+    tensor cores produced (parity probe, see kdnn_b200_quant_gemm_dots)."""
+    M, K = X.shape
+    if w.cols != K or Y.shape[0] != M or Y.shape[1] != w.rows:
+        raise ValueError("quant_gemm: dimension mismatch")
+    _quant_check(w, "quant_gemm")
+    dots = torch.zeros((M, w.rows, K // 32), dtype=torch.int32, device=X.device)
+    rc = lib.kdnn_b200_quant_gemm_dots(w.dtype, w.data.data_ptr(), w.rows, K, X.data_ptr(), X.stride(0), M,
+                                       _scalar(X), Y.data_ptr(), Y.stride(0), _scalar(Y), dots.data_ptr(),
+                                       workspace.data_ptr(), workspace.numel(), _stream())
+    _check(rc, "quant_gemm_dots")
+    return dots
 
 
 def quant_gemv_fp(x: torch.Tensor, w: QuantWeight, y: torch.Tensor) -> None:
@@ -358,13 +413,31 @@ class QuantWeightTable:
     cols: int
     row_bytes: int
     keepalive: Sequence[QuantWeight] = ()
+    tma: Optional[torch.Tensor] = None   # uint8 [n_experts * 128] TMA descriptors for the tcgen05 tile kernel
+
+    def __post_init__(self):
+        if self.tma is None and self.base.numel() and self.base.is_cuda:
+            self.tma = encode_table_tma(self.base, self.dtype, self.rows, self.cols)
 
     def size(self) -> int:
         return int(self.base.numel())
 
     def c_struct(self) -> WeightTableC:
         return WeightTableC(self.base.data_ptr(), self.dtype, self.rows, self.cols, self.row_bytes,
-                            self.size())
+                            self.size(), self.tma.data_ptr() if self.tma is not None else None)
+
+
+def encode_table_tma(base: torch.Tensor, dtype: int, rows: int, cols: int) -> Optional[torch.Tensor]:
+    """One TMA descriptor per expert matrix (kdnn_b200_weight_table_tma_encode), uploaded next to the
+    pointer table; None when the table's format has no tensor-core kernel."""
+    import numpy as np
+    host = np.ascontiguousarray(base.cpu().numpy().astype(np.uint64))
+    out = np.zeros(host.size * 128, dtype=np.uint8)
+    rc = lib.kdnn_b200_weight_table_tma_encode(host.ctypes.data, dtype, rows, cols, host.size, out.ctypes.data)
+    if rc == KDNN_DECLINED:
+        return None
+    _check(rc, "weight_table_tma_encode")
+    return torch.from_numpy(out).to(base.device)
 
 
 def make_quant_weight_table(ws: List[QuantWeight], what: str = "table") -> QuantWeightTable:

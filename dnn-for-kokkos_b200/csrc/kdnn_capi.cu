@@ -5,20 +5,23 @@
 
 #include <limits.h>
 #include <stdio.h>
+#include <string.h>
 #include <string>
 
 namespace kdnn {
 cudaError_t gemv_launch(uint32_t dt, const void* w, size_t rows, size_t cols, const void* x, int xs,
-                        void* y, int ys, void* scratch, int force_generic, cudaStream_t stream);
+                        void* y, int ys, void* scratch, const kdnn_b200_gemv_layout* layout, cudaStream_t stream);
 cudaError_t quantize_act_launch(const void* x, int xs, size_t K, void* scratch, cudaStream_t st);
 cudaError_t unit_dots_launch(uint32_t dt, const void* w, size_t rows, size_t cols,
                              const void* scratch, int32_t* out, cudaStream_t st);
 int gemv_take_status();
-void gemv_set_trace(void* buf);
 
 size_t gemm_workspace_bytes(size_t M, size_t K);
 cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const void* X, size_t ldx,
-                        size_t M, int xs, void* Y, size_t ldy, int ys, void* ws, cudaStream_t st);
+                        size_t M, int xs, void* Y, size_t ldy, int ys, void* ws, int32_t* dots, cudaStream_t st);
+int tile_kind();
+int set_tile_kind(int k);
+cudaError_t tc_encode_matrix_host(void* out128, const void* w, size_t rows, size_t row_bytes);
 
 cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, int scalar,
                              const void* bias, int top_k, int norm_topk, float routed_scale,
@@ -59,15 +62,6 @@ bool int8_type(uint32_t t) {
   return t == KDNN_GGML_Q4_K || t == KDNN_GGML_Q5_K || t == KDNN_GGML_Q6_K || t == KDNN_GGML_Q8_0;
 }
 bool tile_type(uint32_t t) { return int8_type(t); }
-// KDNN_FORCE_GENERIC=1 routes every GEMV through the plain-load kernels (debug aid).
-int force_generic() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("KDNN_FORCE_GENERIC");
-    v             = (e && e[0] == '1') ? 1 : 0;
-  }
-  return v;
-}
 // Copies between page-locked host memory and device memory done by a kernel over the mapped host
 // pointer instead of by the copy engine: on a stream that alternates small copies and short kernels the
 // engine hand-offs cost more than the kernels. Chained like every other kernel of the library, so the GEMV
@@ -120,8 +114,6 @@ int kdnn_b200_device_status(void) {
   return a != 0 ? a : b;
 }
 
-void kdnn_b200_debug_set_trace(void* device_buffer) { kdnn::gemv_set_trace(device_buffer); }
-
 size_t kdnn_b200_gemv_scratch_bytes(size_t K) { return kdnn::act_bytes(K); }
 
 int kdnn_b200_gemv_supported(uint32_t ggml_type, size_t K, int scalar) {
@@ -132,6 +124,13 @@ int kdnn_b200_gemv_supported(uint32_t ggml_type, size_t K, int scalar) {
 int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
                          const void* x, int x_scalar, void* y, int y_scalar, void* act_scratch,
                          size_t act_scratch_bytes, void* stream) {
+  return kdnn_b200_quant_gemv_ex(ggml_type, w, rows, cols, x, x_scalar, y, y_scalar, act_scratch, act_scratch_bytes,
+                                 nullptr, stream);
+}
+
+int kdnn_b200_quant_gemv_ex(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                            const void* x, int x_scalar, void* y, int y_scalar, void* act_scratch,
+                            size_t act_scratch_bytes, const kdnn_b200_gemv_layout* layout, void* stream) {
   if (!scalar_ok(x_scalar) || !scalar_ok(y_scalar))
     return fail(KDNN_ERR_INVALID, "quant_gemv: scalar must be KDNN_F32 or KDNN_BF16");
   // the reference launcher's decline list, src/KokkosDNN_GGUFGemvInt8.hpp:724-745
@@ -146,7 +145,7 @@ int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t 
   if ((ggml_type == KDNN_GGML_Q4_K || ggml_type == KDNN_GGML_Q5_K) && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u)
     return KDNN_DECLINED;
   return cuda_result(kdnn::gemv_launch(ggml_type, w, rows, cols, x, x_scalar, y, y_scalar,
-                                       act_scratch, force_generic(),
+                                       act_scratch, layout,
                                        static_cast<cudaStream_t>(stream)),
                      "quant_gemv");
 }
@@ -213,9 +212,39 @@ size_t kdnn_b200_gemm_workspace_bytes(size_t M, size_t K) {
   return kdnn::gemm_workspace_bytes(M, K);
 }
 
+int kdnn_b200_tile_kind(int kind) { return kdnn::set_tile_kind(kind); }
+
+size_t kdnn_b200_weight_table_tma_bytes(size_t n_experts) { return n_experts * 128; }
+
+int kdnn_b200_weight_table_tma_encode(const uintptr_t* host_base, uint32_t ggml_type, size_t rows, size_t cols,
+                                      size_t n_experts, void* host_out) {
+  if (!host_base || !host_out) return fail(KDNN_ERR_INVALID, "weight_table_tma_encode: null argument");
+  if (ggml_type != KDNN_GGML_Q4_K || cols == 0 || cols % 256 != 0 || rows == 0) return KDNN_DECLINED;
+  const size_t rb = kdnn::row_bytes_of(ggml_type, cols);
+  for (size_t e = 0; e < n_experts; ++e) {
+    if (host_base[e] == 0) {   // an expert this rank does not hold: never addressed by the kernels
+      memset(static_cast<uint8_t*>(host_out) + e * 128, 0, 128);
+      continue;
+    }
+    if (host_base[e] & 15u) return KDNN_DECLINED;
+    const cudaError_t err = kdnn::tc_encode_matrix_host(static_cast<uint8_t*>(host_out) + e * 128,
+                                                        reinterpret_cast<const void*>(host_base[e]), rows, rb);
+    if (err == cudaErrorNotSupported) return KDNN_DECLINED;   // driver without the tensor-map encoder
+    if (err != cudaSuccess) return fail(KDNN_ERR_CUDA, "weight_table_tma_encode: cuTensorMapEncodeTiled failed");
+  }
+  return KDNN_OK;
+}
+
 int kdnn_b200_quant_gemm(uint32_t ggml_type, const void* w, size_t N, size_t K, const void* X,
                          size_t ldx, size_t M, int x_scalar, void* Y, size_t ldy, int y_scalar,
                          void* workspace, size_t workspace_bytes, void* stream) {
+  return kdnn_b200_quant_gemm_dots(ggml_type, w, N, K, X, ldx, M, x_scalar, Y, ldy, y_scalar, nullptr, workspace,
+                                   workspace_bytes, stream);
+}
+
+int kdnn_b200_quant_gemm_dots(uint32_t ggml_type, const void* w, size_t N, size_t K, const void* X,
+                              size_t ldx, size_t M, int x_scalar, void* Y, size_t ldy, int y_scalar, int32_t* dots,
+                              void* workspace, size_t workspace_bytes, void* stream) {
   if (!scalar_ok(x_scalar) || !scalar_ok(y_scalar))
     return fail(KDNN_ERR_INVALID, "quant_gemm: scalar must be KDNN_F32 or KDNN_BF16");
   if (M == 0 || N == 0 || K == 0) return KDNN_OK;  // src/KokkosDNN_GGUF.hpp:2576
@@ -228,8 +257,9 @@ int kdnn_b200_quant_gemm(uint32_t ggml_type, const void* w, size_t N, size_t K, 
     return KDNN_DECLINED;
   if ((ggml_type == KDNN_GGML_Q4_K || ggml_type == KDNN_GGML_Q5_K) && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u)
     return KDNN_DECLINED;   // 16-byte loads of the super-blocks, src/KokkosDNN_GGUFGemvInt8.hpp:741-743
+  if (dots != nullptr && (ggml_type != KDNN_GGML_Q4_K || kdnn::tile_kind() != 2)) return KDNN_DECLINED;
   return cuda_result(kdnn::gemm_launch(ggml_type, w, N, K, X, ldx, M, x_scalar, Y, ldy, y_scalar,
-                                       workspace, static_cast<cudaStream_t>(stream)),
+                                       workspace, dots, static_cast<cudaStream_t>(stream)),
                      "quant_gemm");
 }
 

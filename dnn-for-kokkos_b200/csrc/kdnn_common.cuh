@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/kdnn_b200.h"
 
 namespace kdnn {
@@ -304,6 +306,24 @@ template <class... KArgs, class... Args>
 inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                                   Args&&... args) {
   return launch_chained_if(true, kern, grid, block, smem, st, static_cast<Args&&>(args)...);
+}
+
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to the (kernel, device) pair, so a host thread that
+// moves to another device must set it there too: one bit per device, set on the first launch there.
+struct SmemAttrOnce {
+  std::atomic<unsigned long long> done{0};
+};
+template <class Kern>
+inline cudaError_t set_max_smem_once(SmemAttrOnce& once, Kern kern, int bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (once.done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) once.done.fetch_or(bit, std::memory_order_release);
+  return e;
 }
 
 }  // namespace kdnn

@@ -27,6 +27,9 @@ namespace kdnn {
 
 __device__ int g_gemv_status = 0;
 
+// Tuning of the call in flight on this host thread (kdnn_b200_gemv_layout; all zero = the defaults).
+static thread_local kdnn_b200_gemv_layout t_lay = {};
+
 constexpr int kChunkItems = 32;    // one item per lane
 
 template <uint32_t DT>
@@ -297,18 +300,6 @@ __device__ __forceinline__ float item_dot<KDNN_GGML_Q8_0>(uint32_t rowp, int il,
 constexpr int kGemvMaxWarps = 16;
 constexpr int kXregMaxWarps = 18;   // the Q4_K register-window kernel may run up to 18 warps (576 threads, <= 113 registers)
 constexpr int kGemvStages   = 2;   // ring depth per warp: about one bandwidth-delay product per SM in flight
-constexpr int kTraceSlots   = 8;   // timestamps per warp when tracing
-
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define KDNN_TRACE(slot)                                                                   \
-  do {                                                                                     \
-    if (p.trace && lane == 0 && warp < kGemvMaxWarps)                                      \
-      p.trace[(static_cast<size_t>(blockIdx.x) * kGemvMaxWarps + warp) * kTraceSlots + (slot)] = globaltimer_ns(); \
-  } while (0)
 
 // One CTA per SM, up to 16 warps. Every warp is an independent streaming engine with a
 // private two-stage ring in shared memory (bulk copies, mbarrier completion, bounded
@@ -337,7 +328,6 @@ struct GemvParams {
   uint32_t upg_magic;  // ceil(2^32 / upg): u / upg == umulhi(u, magic) for the unit counts that occur
   int part_floats;     // partial sums kept in shared memory (upg > 1)
   int stage_bytes;
-  unsigned long long* trace;
 };
 
 // Sum RW per-lane values across the warp. Afterwards lane l (l < RW) holds the total of
@@ -393,7 +383,6 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_stream_kernel(cons
   float* part = reinterpret_cast<float*>(smem + off);        // [local row][unit of the row]
   off += (static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127);
   const uint32_t ring_u32 = smem_u32(smem + off) + warp * (kGemvStages * p.stage_bytes);
-  KDNN_TRACE(0);
 
   // this CTA's slice of the row groups and its units
   // even contiguous split of the row groups over the CTAs (quotient and remainder from the host)
@@ -469,17 +458,14 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_stream_kernel(cons
   // activation loads makes those loads (a few KB that everything waits for) queue behind
   // megabytes of weights. The rest of the ring follows once those loads are in flight.
   issue(0);
-  KDNN_TRACE(1);
   pdl_launch_dependents();
   pdl_wait();
-  KDNN_TRACE(2);
   stage_activations<DT, XT>(static_cast<const XT*>(p.x), p.K, p.nitems, xg, hd, hs,
                             blockIdx.x == 0 ? p.scratch : nullptr, [&]() {
 #pragma unroll
                               for (int s = 1; s < kGemvStages; ++s) issue(s);
                             });
   __syncthreads();
-  KDNN_TRACE(3);
 
   float acc[RW];
 #pragma unroll
@@ -528,7 +514,6 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_stream_kernel(cons
     phase ^= 1u;
   }
   if (!ok && lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
-  KDNN_TRACE(6);
   if (p.upg > 1) {   // add up the partial sums of every local row in chunk order
     __syncthreads();
     const int nloc = min((c1 - c0) * RW, p.rows - c0 * RW);
@@ -662,7 +647,6 @@ struct WideParams {
   int cpu, upg;        // chunks per unit, units per group
   uint32_t upg_magic;
   int part_floats;
-  unsigned long long* trace;
 };
 
 // MAXW = 16: one CTA per SM. MAXW = 8: two CTAs per SM, so the next GEMV in the stream is
@@ -681,7 +665,6 @@ __global__ void __launch_bounds__(MAXW * 32, MAXW == 8 ? 2 : 1) gemv_q4k_wide_ke
   float* part = reinterpret_cast<float*>(smem + off);
   off += (static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127);
   const uint32_t ring_u32 = smem_u32(smem + off) + warp * (STAGES * kWideStage);
-  KDNN_TRACE(0);
 
   // even contiguous split of the row groups over the CTAs (quotient and remainder from the host)
   const int c0 = static_cast<int>(blockIdx.x) * p.gq + min(static_cast<int>(blockIdx.x), p.gr);
@@ -747,13 +730,10 @@ __global__ void __launch_bounds__(MAXW * 32, MAXW == 8 ? 2 : 1) gemv_q4k_wide_ke
   }
 #pragma unroll
   for (int s = 0; s < STAGES; ++s) issue(s);
-  KDNN_TRACE(1);
   pdl_launch_dependents();
   pdl_wait();
-  KDNN_TRACE(2);
   stage_activations_wide<XT>(static_cast<const XT*>(p.x), p.K, smem, blockIdx.x == 0 ? p.scratch : nullptr);
   __syncthreads();
-  KDNN_TRACE(3);
 
   float acc[RW] = {0.f, 0.f};   // per-lane sums of this unit: [0] as a row-0 lane, [1] as a row-1 lane
   YT* y = static_cast<YT*>(p.y);
@@ -771,7 +751,6 @@ __global__ void __launch_bounds__(MAXW * 32, MAXW == 8 ? 2 : 1) gemv_q4k_wide_ke
         ok = more = false;
         break;
       }
-      if (first_round) { if (s == 0) KDNN_TRACE(4); if (s == 1) KDNN_TRACE(5); } else if (s == 0 && phase == 1) KDNN_TRACE(7);
       const int lrow0 = m_row[s];
       const int nrow  = min(RW, p.rows - (c0 * RW + lrow0));
       const int sb0   = m_chunk[s] * p.csb;
@@ -800,7 +779,6 @@ __global__ void __launch_bounds__(MAXW * 32, MAXW == 8 ? 2 : 1) gemv_q4k_wide_ke
     phase ^= 1u;
   }
   if (!ok && lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
-  KDNN_TRACE(6);
   if (p.upg > 1) {
     __syncthreads();
     const int nloc = min((c1 - c0) * RW, p.rows - c0 * RW);
@@ -836,10 +814,8 @@ struct XregParams {
   int wpc;            // warps per chunk
   uint32_t nch_magic; // ceil(65536 / nchunks): warp / nchunks == (warp * magic) >> 16 for warp < 16
   int part_floats;
-  int ablate;         // debug: 1 = skip the dot products (stream only)
   int early;          // ring stages requested before the activation window is quantized
   int split_first;    // request only the first row of the first stage before the dependency
-  unsigned long long* trace;
 };
 
 // Half a super-block of one row: 128 weights against the lane's register window.
@@ -902,7 +878,6 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
   float* part = reinterpret_cast<float*>(smem + off);  // [local row][chunk]
   off += (static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127);
   const uint32_t ring_u32 = smem_u32(smem + off) + warp * (STAGES * kStage);
-  KDNN_TRACE(0);
 
   // even contiguous split of the row groups over the CTAs (quotient and remainder from the host)
   const int c0 = static_cast<int>(blockIdx.x) * p.gq + min(static_cast<int>(blockIdx.x), p.gr);
@@ -977,10 +952,8 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
     draw();
     advance();
   }
-  KDNN_TRACE(1);
   pdl_launch_dependents();
   pdl_wait();
-  KDNN_TRACE(2);
   // ring stages 1 .. early-1 are requested once the activation loads are in flight, the
   // rest after the quantized window has been written
   const bool first_live = m_group[0] >= 0;
@@ -990,7 +963,6 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
     for (int s = 1; s < STAGES; ++s)
       if (s < p.early) issue(s);
   });
-  KDNN_TRACE(7);
 #pragma unroll
   for (int s = 1; s < STAGES; ++s)
     if (s >= p.early) issue(s);
@@ -1009,7 +981,6 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
   const float4 dxv = make_float4(__int_as_float(dxi.x), __int_as_float(dxi.y), __int_as_float(dxi.z), __int_as_float(dxi.w));
   const float4 dsv = make_float4(__int_as_float(dsi.x), __int_as_float(dsi.y), __int_as_float(dsi.z), __int_as_float(dsi.w));
   const uint32_t lane_blk = sb * 144, qoff = 16 + 64 * half;
-  KDNN_TRACE(3);
 
   YT* y = static_cast<YT*>(p.y);
   uint32_t phase = 0;
@@ -1026,14 +997,13 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
         ok = more = false;
         break;
       }
-      if (first_round && s == 0) KDNN_TRACE(4);
       const int lrow0 = m_group[s] * RW;
       const int nrow  = min(RW, p.rows - (c0 * RW + lrow0));
       float acc[RW];
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
         acc[r] = 0.f;
-        if (r < nrow && !(p.ablate & 1)) {
+        if (r < nrow) {
           const float v = q4k_half_dot(ring_u32 + s * kStage + r * kWideRowPitch + lane_blk, qoff, half, xg, dxv, dsv);
           acc[r] = active ? v : 0.f;
         }
@@ -1052,7 +1022,6 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
     first_round = false;
   }
   if (!ok && lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
-  KDNN_TRACE(6);
   if (p.nchunks > 1) {
     __syncthreads();
     const int nloc = min(G * RW, p.rows - c0 * RW);
@@ -1084,7 +1053,6 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
   float* part = reinterpret_cast<float*>(smem + off);  // [local row][chunk]
   off += (static_cast<size_t>(p.part_floats) * 4 + 127) & ~size_t(127);
   const uint32_t ring_u32 = smem_u32(smem + off) + warp * (STAGES * kStage);
-  KDNN_TRACE(0);
 
   // even contiguous split of the row groups over the CTAs (quotient and remainder from the host)
   const int c0 = static_cast<int>(blockIdx.x) * p.gq + min(static_cast<int>(blockIdx.x), p.gr);
@@ -1154,10 +1122,8 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
     draw();
     advance();
   }
-  KDNN_TRACE(1);
   pdl_launch_dependents();
   pdl_wait();
-  KDNN_TRACE(2);
   // ring stages 1 .. early-1 are requested once the activation loads are in flight, the
   // rest after the quantized window has been written
   stage_activations<DT, XT>(static_cast<const XT*>(p.x), p.K, p.nitems, xg, hd, hs, blockIdx.x == 0 ? p.scratch : nullptr, [&]() {
@@ -1165,7 +1131,6 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
     for (int s = 1; s < STAGES; ++s)
       if (s < p.early) issue(s);
   });
-  KDNN_TRACE(7);
 #pragma unroll
   for (int s = 1; s < STAGES; ++s)
     if (s >= p.early) issue(s);
@@ -1180,7 +1145,6 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
   x.hd = hd[item];
   x.hs = make_int4(0, 0, 0, 0);
   if (DT == KDNN_GGML_Q6_K) x.hs = hs[item];
-  KDNN_TRACE(3);
 
   YT* y = static_cast<YT*>(p.y);
   uint32_t phase = 0;
@@ -1197,14 +1161,13 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
         ok = more = false;
         break;
       }
-      if (first_round && s == 0) KDNN_TRACE(4);
       const int lrow0 = m_group[s] * RW;
       const int nrow  = min(RW, p.rows - (c0 * RW + lrow0));
       float acc[RW];
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
         acc[r] = 0.f;
-        if (r < nrow && !(p.ablate & 1)) {
+        if (r < nrow) {
           if (active) acc[r] = item_dot<DT>(ring_u32 + s * kStage + r * kRowPitch, lane, x);
         }
       }
@@ -1222,7 +1185,6 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
     first_round = false;
   }
   if (!ok && lane == 0) atomicExch(&g_gemv_status, KDNN_ERR_DEVICE_WAIT);
-  KDNN_TRACE(6);
   if (p.nchunks > 1) {
     __syncthreads();
     const int nloc = min(G * RW, p.rows - c0 * RW);
@@ -1412,25 +1374,8 @@ static const DeviceInfo& device_info() {
   return d;
 }
 
-// KDNN_NO_PDL=1 launches without programmatic stream serialization (A/B aid).
-static bool use_pdl() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("KDNN_NO_PDL");
-    v             = (e && e[0] == '1') ? 0 : 1;
-  }
-  return v != 0;
-}
+static bool use_pdl() { return pdl_enabled() && t_lay.no_pdl == 0; }
 
-static int env_int(const char* name, int dflt) {
-  const char* e = getenv(name);
-  return (e && *e) ? atoi(e) : dflt;
-}
-
-// Debug aid: when set (kdnn_b200_debug_set_trace), every warp of the streaming kernel
-// writes kTraceSlots globaltimer stamps per launch into this device buffer.
-static unsigned long long* g_trace_buffer = nullptr;
-void gemv_set_trace(void* buf) { g_trace_buffer = static_cast<unsigned long long*>(buf); }
 
 static thread_local bool t_ring_does_not_fit = false;
 
@@ -1457,11 +1402,7 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
   p.gq = p.ngroups / grid;
   p.gr = p.ngroups % grid;
   GemvSplit sp = choose_split(p.ngroups, p.nchunks, grid);
-  if (const int w = env_int("KDNN_GEMV_WARPS", 0)) sp.warps = max(1, min(kGemvMaxWarps, w));
-  if (const int c = env_int("KDNN_GEMV_CPU", 0)) {
-    sp.cpu = max(1, min(p.nchunks, c));
-    sp.upg = (p.nchunks + sp.cpu - 1) / sp.cpu;
-  }
+  if (const int w = t_lay.warps) sp.warps = max(1, min(kGemvMaxWarps, w));
   const int gpc = (p.ngroups + grid - 1) / grid;
   if (sp.upg > 1 && static_cast<size_t>(gpc + 1) * RW * sp.upg * 4 > 48 * 1024) {   // partial sums would not fit
     sp.cpu = p.nchunks;
@@ -1479,14 +1420,9 @@ static cudaError_t launch_stream(const GemvParams& base, cudaStream_t stream) {
     t_ring_does_not_fit = true;   // the caller takes the plain-load kernel instead
     return cudaSuccess;
   }
-  p.trace = g_trace_buffer;
   auto kern = gemv_stream_kernel<DT, RW, XT, YT>;
-  static thread_local size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem);
-    if (e != cudaSuccess) return e;
-    configured = di.max_smem;
-  }
+  static SmemAttrOnce once;
+  if (const cudaError_t e = set_max_smem_once(once, kern, di.max_smem)) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(sp.warps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1526,7 +1462,7 @@ static bool launch_q4k_xreg(const GemvParams& base, cudaStream_t stream, cudaErr
     }
     p.wpc = best;
   }
-  if (const int w = env_int("KDNN_GEMV_WARPS", 0)) p.wpc = max(1, max(1, min(kXregMaxWarps, w)) / p.nchunks);
+  if (const int w = t_lay.warps) p.wpc = max(1, max(1, min(kXregMaxWarps, w)) / p.nchunks);
   const int warps = p.wpc * p.nchunks;
   p.gq = p.ngroups / grid;
   p.gr = p.ngroups % grid;
@@ -1539,27 +1475,22 @@ static bool launch_q4k_xreg(const GemvParams& base, cudaStream_t stream, cudaErr
   constexpr int kStage = RW * kWideRowPitch;
   auto smem_for = [&](int st) { return fixed + static_cast<size_t>(kXregMaxWarps) * st * 8 + static_cast<size_t>(warps) * st * kStage; };
   const int units_per_warp = (gpc + p.wpc - 1) / p.wpc;
-  int stages = env_int("KDNN_GEMV_STAGES", 0);
+  int stages = t_lay.stages;
   if (stages == 0) stages = 3;
   stages = max(2, min(4, min(stages, max(2, units_per_warp))));
   while (stages > 2 && smem_for(stages) > static_cast<size_t>(di.max_smem)) --stages;
   if (smem_for(stages) > static_cast<size_t>(di.max_smem)) return false;
   const size_t smem = smem_for(stages);
-  p.trace = g_trace_buffer;
-  p.ablate = env_int("KDNN_GEMV_ABLATE", 0);
-  p.early  = env_int("KDNN_GEMV_EARLY", 2);
+  p.early  = t_lay.early_stages > 0 ? t_lay.early_stages : 2;
   // When every warp has at most one unit the whole matrix would be requested before the dependency and
   // the activation loads would queue behind all of it: request half of it first, the rest behind those loads.
-  p.split_first = env_int("KDNN_GEMV_SPLIT", gpc <= p.wpc ? 1 : 0);
+  p.split_first = gpc <= p.wpc ? 1 : 0;
   using Kern = void (*)(const XregParams);
   const Kern kern = stages == 2 ? gemv_q4k_xreg_kernel<XT, YT, RW, 2>
                   : stages == 3 ? gemv_q4k_xreg_kernel<XT, YT, RW, 3> : gemv_q4k_xreg_kernel<XT, YT, RW, 4>;
-  static thread_local bool configured[5] = {};
-  if (!configured[stages]) {
-    err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem);
-    if (err != cudaSuccess) return true;
-    configured[stages] = true;
-  }
+  static SmemAttrOnce once[5];
+  err = set_max_smem_once(once[stages], kern, di.max_smem);
+  if (err != cudaSuccess) return true;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(warps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1595,24 +1526,19 @@ static bool launch_item_xreg(const GemvParams& base, cudaStream_t stream, cudaEr
   constexpr int kStage = RW * chunk_bytes_full<DT>();
   auto smem_for = [&](int st) { return fixed + static_cast<size_t>(kGemvMaxWarps) * st * (8 + kStage); };
   const int units_per_warp = (gpc + p.wpc - 1) / p.wpc;
-  int stages = env_int("KDNN_GEMV_STAGES", 0);
+  int stages = t_lay.stages;
   if (stages == 0) stages = 3;
   stages = max(2, min(4, min(stages, max(2, units_per_warp))));
   while (stages > 2 && smem_for(stages) > static_cast<size_t>(di.max_smem)) --stages;
   if (smem_for(stages) > static_cast<size_t>(di.max_smem)) return false;
   const size_t smem = smem_for(stages);
-  p.trace  = g_trace_buffer;
-  p.ablate = env_int("KDNN_GEMV_ABLATE", 0);
-  p.early  = env_int("KDNN_GEMV_EARLY", 2);
+  p.early  = t_lay.early_stages > 0 ? t_lay.early_stages : 2;
   using Kern = void (*)(const XregParams);
   const Kern kern = stages == 2 ? gemv_item_xreg_kernel<DT, XT, YT, RW, 2>
                   : stages == 3 ? gemv_item_xreg_kernel<DT, XT, YT, RW, 3> : gemv_item_xreg_kernel<DT, XT, YT, RW, 4>;
-  static thread_local bool configured[5] = {};
-  if (!configured[stages]) {
-    err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem);
-    if (err != cudaSuccess) return true;
-    configured[stages] = true;
-  }
+  static SmemAttrOnce once[5];
+  err = set_max_smem_once(once[stages], kern, di.max_smem);
+  if (err != cudaSuccess) return true;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(warps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1638,11 +1564,7 @@ static cudaError_t launch_q4k_wide(const GemvParams& base, cudaStream_t stream) 
   p.gq = p.ngroups / grid;
   p.gr = p.ngroups % grid;
   GemvSplit sp = choose_split(p.ngroups, p.nchunks, grid);
-  if (const int w = env_int("KDNN_GEMV_WARPS", 0)) sp.warps = max(1, min(kGemvMaxWarps, w));
-  if (const int c = env_int("KDNN_GEMV_CPU", 0)) {
-    sp.cpu = max(1, min(p.nchunks, c));
-    sp.upg = (p.nchunks + sp.cpu - 1) / sp.cpu;
-  }
+  if (const int w = t_lay.warps) sp.warps = max(1, min(kGemvMaxWarps, w));
   const int gpc = (p.ngroups + grid - 1) / grid;
   if (sp.upg > 1 && static_cast<size_t>(gpc + 1) * 2 * sp.upg * 4 > 32 * 1024) {
     sp.cpu = p.nchunks;
@@ -1660,7 +1582,7 @@ static cudaError_t launch_q4k_wide(const GemvParams& base, cudaStream_t stream) 
   auto smem_for = [&](int st) { return fixed + static_cast<size_t>(maxw) * st * (8 + kWideStage); };
   const size_t cap = maxw == 8 ? static_cast<size_t>(di.max_smem) / 2 - 1024 : static_cast<size_t>(di.max_smem);
   const int chunks_per_warp = (gpc * p.nchunks + sp.warps - 1) / sp.warps;
-  int stages = env_int("KDNN_GEMV_STAGES", 0);
+  int stages = t_lay.stages;
   if (stages == 0) stages = max(2, min(4, chunks_per_warp));
   stages = max(2, min(4, stages));
   while (stages > 2 && smem_for(stages) > cap) --stages;
@@ -1669,7 +1591,6 @@ static cudaError_t launch_q4k_wide(const GemvParams& base, cudaStream_t stream) 
     return cudaSuccess;
   }
   const size_t smem = smem_for(stages);
-  p.trace = g_trace_buffer;
   using Kern = void (*)(const WideParams);
   Kern kern;
   if (maxw == 8)
@@ -1678,12 +1599,8 @@ static cudaError_t launch_q4k_wide(const GemvParams& base, cudaStream_t stream) 
   else
     kern = stages == 2 ? gemv_q4k_wide_kernel<XT, YT, 16, 2> : stages == 3 ? gemv_q4k_wide_kernel<XT, YT, 16, 3>
                                                                              : gemv_q4k_wide_kernel<XT, YT, 16, 4>;
-  static thread_local bool configured[2][5] = {};
-  if (!configured[maxw == 8][stages]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(cap));
-    if (e != cudaSuccess) return e;
-    configured[maxw == 8][stages] = true;
-  }
+  static SmemAttrOnce once[2][5];
+  if (const cudaError_t e = set_max_smem_once(once[maxw == 8][stages], kern, static_cast<int>(cap))) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(sp.warps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1697,16 +1614,16 @@ template <uint32_t DT, class XT, class YT>
 static cudaError_t launch_stream_rw(const GemvParams& p, cudaStream_t stream) {
   // Rows per group: two rows share one load of the activation window and one pass of
   // the loop bookkeeping.
-  int rw = env_int("KDNN_GEMV_RW", 0);
-  if (DT == KDNN_GGML_Q4_K && !env_int("KDNN_GEMV_ITEM", 0)) {
-    const int mode = env_int("KDNN_GEMV_Q4K", 0);   // 0: register window, 1: shared-memory window
+  int rw = t_lay.rows_per_group;
+  const int kk = t_lay.kernel;   // 0 / 1: register window, 2: shared-memory window, 3: item mapping with the window in shared memory
+  if (DT == KDNN_GGML_Q4_K && kk != 3) {
     cudaError_t err = cudaSuccess;
-    if (mode == 0) {
+    if (kk != 2) {
       if (rw == 1 ? launch_q4k_xreg<XT, YT, 1>(p, stream, err) : launch_q4k_xreg<XT, YT, 2>(p, stream, err)) return err;
     }
     return launch_q4k_wide<XT, YT>(p, stream);
   }
-  if (DT != KDNN_GGML_Q4_K && !env_int("KDNN_GEMV_ITEM", 0)) {   // register-window kernel for Q6_K / Q8_0
+  if (DT != KDNN_GGML_Q4_K && kk != 2 && kk != 3) {   // register-window kernel for Q6_K / Q8_0
     cudaError_t err = cudaSuccess;
     if (rw == 1 ? launch_item_xreg<DT, XT, YT, 1>(p, stream, err) : launch_item_xreg<DT, XT, YT, 2>(p, stream, err)) return err;
   }
@@ -1741,9 +1658,12 @@ static cudaError_t launch_generic_dt(const uint8_t* w, size_t rb, int rows, int 
   return cudaGetLastError();
 }
 
-// Entry used by the C ABI. `force_generic` != 0 selects the plain-load kernels.
+// Entry used by the C ABI. `layout` (may be null) carries the caller's tuning; kernel 4 selects the
+// plain-load kernels.
 cudaError_t gemv_launch(uint32_t dt, const void* w, size_t rows, size_t cols, const void* x, int xs,
-                        void* y, int ys, void* scratch, int force_generic, cudaStream_t stream) {
+                        void* y, int ys, void* scratch, const kdnn_b200_gemv_layout* layout, cudaStream_t stream) {
+  t_lay = layout != nullptr ? *layout : kdnn_b200_gemv_layout{};
+  const bool force_generic = t_lay.kernel == 4;
   const size_t rb = row_bytes_of(dt, cols);
   const bool w16  = (reinterpret_cast<uintptr_t>(w) & 15u) == 0;
   // bulk copies need 16-byte aligned row segments: every row start and every
@@ -1850,9 +1770,9 @@ static cudaError_t noalloc_staging_address(uint8_t** out) {
 
 }  // namespace kdnn
 
-extern "C" int kdnn_b200_quant_gemv_noalloc(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
-                                            const void* x, int x_scalar, void* y, int y_scalar,
-                                            void* stream) {
+extern "C" int kdnn_b200_quant_gemv_noalloc_ex(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                                               const void* x, int x_scalar, void* y, int y_scalar,
+                                               const kdnn_b200_gemv_layout* layout, void* stream) {
   using namespace kdnn;
   if ((x_scalar != KDNN_F32 && x_scalar != KDNN_BF16) || (y_scalar != KDNN_F32 && y_scalar != KDNN_BF16)) {
     set_last_error("quant_gemv_noalloc: scalar must be KDNN_F32 or KDNN_BF16");
@@ -1874,11 +1794,17 @@ extern "C" int kdnn_b200_quant_gemv_noalloc(uint32_t ggml_type, const void* w, s
   uint8_t* staging = nullptr;
   cudaError_t e = noalloc_staging_address(&staging);
   if (e == cudaSuccess)
-    e = gemv_launch(ggml_type, w, rows, cols, x, x_scalar, y, y_scalar, staging, 0,
+    e = gemv_launch(ggml_type, w, rows, cols, x, x_scalar, y, y_scalar, staging, layout,
                     static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) {
     set_last_error((std::string("quant_gemv_noalloc: ") + cudaGetErrorString(e)).c_str());
     return KDNN_ERR_CUDA;
   }
   return KDNN_OK;
+}
+
+extern "C" int kdnn_b200_quant_gemv_noalloc(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                                            const void* x, int x_scalar, void* y, int y_scalar,
+                                            void* stream) {
+  return kdnn_b200_quant_gemv_noalloc_ex(ggml_type, w, rows, cols, x, x_scalar, y, y_scalar, nullptr, stream);
 }

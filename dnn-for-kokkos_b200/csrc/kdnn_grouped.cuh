@@ -156,12 +156,9 @@ template <uint32_t DT, int MODE, class XT, class YT>
 static cudaError_t launch_grouped(const GroupedParams& p, int groups, cudaStream_t st) {
   const size_t smem = sizeof(ActItem) * kMT * kKChunk;  // 48 KB
   auto kern = grouped_gemm_kernel<DT, MODE, XT, YT>;
-  static thread_local bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static SmemAttrOnce once;
+  const cudaError_t e = set_max_smem_once(once, kern, (int)smem);
+  if (e != cudaSuccess) return e;
   dim3 grid((p.N + kRowsCta - 1) / kRowsCta, groups);
   kern<<<grid, kRowsCta, smem, st>>>(p);
   return cudaGetLastError();

@@ -11,6 +11,8 @@
 // lives there, which is what a rescale every 32 elements wants.
 #pragma once
 
+#include <atomic>
+
 #include "kdnn_tile.cuh"
 
 namespace kdnn {
@@ -34,7 +36,6 @@ struct MmaParams {
   size_t q_pitch;        //         here instead of floats to dst
   int* status;
   int passes_z;          // CTAs along z that share a group's 32-row passes (0 = 1)
-  int ablate;            // debug: 1 skip the MMA loop, 2 skip the scale table, 4 skip activation staging
   int early;             // launch as a programmatic dependent (only worth it behind a tiny kernel, see launch_chained_if)
 };
 
@@ -396,14 +397,14 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
     for (int c = 0; c < nchunk; ++c) {
       cp_async_wait_but_one();
       __syncthreads();   // chunk c has landed for everybody; everybody is done with chunk c - 1
-      if (c + 1 < nchunk && !(p.ablate & 4)) stage_chunk(c + 1); else cp_async_commit();
+      if (c + 1 < nchunk) stage_chunk(c + 1); else cp_async_commit();
       const uint32_t xb = xq_u32 + (c & 1) * (kM2NT * kM2XPitch);
       const uint32_t sbuf = xs_u32 + (c & 1) * ((kM2KC / 32) * kM2NT * 4);
       const uint32_t pbuf = xp_u32 + (c & 1) * ((kM2KC / 256) * 3 * kM2NT * 16);
       const int sb_first = c * (kM2KC / 256), sb_last = min(nsb, sb_first + kM2KC / 256);
       for (int sb = sb_first; sb < sb_last; ++sb) {
         const uint32_t st = ring_u32 + (sb % kM2Stages) * kM2StageBytes;
-        if (!(p.ablate & 2)) {  // expand the 6-bit scales: lane = (row, half) -> {sw0, mw0, sw1, mw1} pairs of its four sub-blocks
+        {  // expand the 6-bit scales: lane = (row, half) -> {sw0, mw0, sw1, mw1} pairs of its four sub-blocks
           const int r = lane >> 1, half = lane & 1;
           const int4 h = lds128_g(st + r * kM2WPitch);
           const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
@@ -428,7 +429,7 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
         }
         __syncwarp();
         const int blk0 = (sb - sb_first) * 8;   // first 32-block of this super-block inside the chunk
-        if (!(p.ablate & 1)) switch (ntiles) {
+        switch (ntiles) {
           case 1: m2_superblock<1>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 4), pbuf + (sb - sb_first) * (3 * kM2NT * 16), gid, tig); break;
           case 2: m2_superblock<2>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 4), pbuf + (sb - sb_first) * (3 * kM2NT * 16), gid, tig); break;
           case 3: m2_superblock<3>(acc, st, tab_u32, xb + blk0 * 32, sbuf + blk0 * (kM2NT * 4), pbuf + (sb - sb_first) * (3 * kM2NT * 16), gid, tig); break;
@@ -517,17 +518,11 @@ template <int MODE, class YT>
 static cudaError_t launch_grouped_mma(const MmaParams& p, int groups, cudaStream_t st) {
   using L = M2Layout<MODE>;
   auto kern = grouped_mma2_q4k_kernel<MODE, YT>;
-  static thread_local bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::total);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static SmemAttrOnce once;
+  const cudaError_t e = set_max_smem_once(once, kern, (int)L::total);
+  if (e != cudaSuccess) return e;
   dim3 grid((p.N + L::kRowsPerCta - 1) / L::kRowsPerCta, groups, p.passes_z > 0 ? p.passes_z : 1);
-  MmaParams q = p;
-  static const int ablate = [] { const char* e = getenv("KDNN_TILE_ABLATE"); return e ? atoi(e) : 0; }();
-  q.ablate = ablate;
-  return launch_chained_if(p.early != 0, kern, grid, dim3(kM2Warps * 32), L::total, st, q);
+  return launch_chained_if(p.early != 0, kern, grid, dim3(kM2Warps * 32), L::total, st, p);
 }
 
 // Batched form of the reference's stage-1 quantizer: row r of `src` (pitch ld

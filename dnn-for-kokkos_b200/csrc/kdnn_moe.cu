@@ -14,19 +14,80 @@
 // Workspace (caller-owned): offsets, slot list, slot positions, int8 items, act, out.
 #include "kdnn_grouped.cuh"
 #include "kdnn_mma.cuh"
-#include "kdnn_umma.cuh"
+#include "kdnn_tc.cuh"
 
 #include <limits.h>
 #include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
 
 namespace kdnn {
 
 __device__ int g_moe_status = 0;
-int* moe_status_ptr() {
-  int* p = nullptr;
-  cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_moe_status);
-  return p;
+// Device address of the status word, looked up once per device (outside any stream capture when the first
+// call on a device is) and cached; a failed lookup is reported to the caller instead of handing the kernels
+// a null pointer.
+cudaError_t moe_status_ptr(int** out) {
+  constexpr int kMaxDevices = 64;
+  static int* cache[kMaxDevices] = {};
+  static std::atomic<bool> ready[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_moe_status);
+    if (e != cudaSuccess) return e;
+    cache[dev] = static_cast<int*>(p);
+    ready[dev].store(true, std::memory_order_release);
+  }
+  *out = cache[dev];
+  return cudaSuccess;
 }
+
+int device_sm_count() {
+  static std::atomic<int> cache[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int v = cache[dev & 63].load(std::memory_order_relaxed);
+  if (v == 0) {
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    cache[dev & 63].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+TcEncodeFn tc_encode_fn() {
+  static std::atomic<TcEncodeFn> fn{nullptr};
+  TcEncodeFn f = fn.load(std::memory_order_acquire);
+  if (f == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
+        qr != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    f = reinterpret_cast<TcEncodeFn>(p);
+    fn.store(f, std::memory_order_release);
+  }
+  return f;
+}
+
+cudaError_t tc_encode_matrix_host(void* out128, const void* w, size_t rows, size_t row_bytes) {
+  CUtensorMap m;
+  const cudaError_t e = tc_encode_matrix(&m, w, rows, row_bytes);
+  if (e == cudaSuccess) memcpy(out128, &m, 128);
+  return e;
+}
+
+// Which Q4_K tile kernel the batched calls use: 2 = tcgen05 + TMEM (default), 1 = mma.sync,
+// 0 = the CUDA-core dp4a kernel (which also serves every other format). Process-wide, read per call.
+static std::atomic<int> g_tile_kind{2};
+int tile_kind() { return g_tile_kind.load(std::memory_order_relaxed); }
+int set_tile_kind(int k) { return k >= 0 && k <= 2 ? g_tile_kind.exchange(k) : g_tile_kind.load(); }
 
 // ---- router ----------------------------------------------------------------------
 // One warp per token; the E scores live in shared memory (src/KokkosDNN_MoE.hpp:
@@ -203,6 +264,166 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_slots, in
   }
 }
 
+
+// ---- prep: slot sort + activation quantizer in ONE launch ------------------------------------
+// CTA 0 groups the routed slots by expert (same outputs as moe_sort_kernel plus the tile kernels' group
+// list), every other CTA quantizes activation rows. The sort is a counting sort over a bit matrix in shared
+// memory: bit t of mask[e][t / 32] says token t routed a slot to local expert e, so a slot's position inside
+// its expert's run is a prefix popcount -- every slot is placed independently, in token order, by its own
+// thread (no sweep per expert). A token that names the same expert twice (callers may pass any idx) is
+// detected by the atomicOr that sets the bit; the kernel then places sequentially per expert instead.
+//   groups[g] = {table index of the expert, first position, rows (<= 32), 0}: one entry per 32 rows of an
+//   expert's run, experts without rows have none.
+struct PrepParams {
+  const int32_t* idx;
+  int n_slots, S, e_first, e_count, words;   // words = ceil(T / 32)
+  int* offs; int* list; int* pos; int4* groups; int* n_groups;
+  const void* X; size_t ldx; int T, H; uint8_t* xrows; size_t x_pitch;   // X == nullptr: no rows to quantize
+};
+
+__device__ void moe_sort_block(const PrepParams& p, uint32_t* sm) {
+  const int tid = threadIdx.x, nt = blockDim.x, E = p.e_count, W = p.words;
+  uint32_t* mask = sm;
+  uint32_t* wpre = mask + E * W;
+  int* counts = reinterpret_cast<int*>(wpre + E * W);
+  int* starts = counts + E;
+  int* gst    = starts + E + 1;
+  int* dup    = gst + E + 1;
+  for (int i = tid; i < E * W; i += nt) mask[i] = 0u;
+  if (tid == 0) *dup = 0;
+  __syncthreads();
+  for (int i = tid; i < p.n_slots; i += nt) {
+    const int e = p.idx[i] - p.e_first;
+    if (e >= 0 && e < E) {
+      const int t = i / p.S;
+      const uint32_t bit = 1u << (t & 31);
+      const uint32_t old = atomicOr(&mask[e * W + (t >> 5)], bit);
+      if (old & bit) *dup = 1;
+    }
+  }
+  __syncthreads();
+  const bool has_dup = *dup != 0;
+  for (int e = tid; e < E; e += nt) {
+    int run = 0;
+    if (!has_dup) {
+      for (int w = 0; w < W; ++w) {
+        wpre[e * W + w] = run;
+        run += __popc(mask[e * W + w]);
+      }
+    } else {
+      for (int i = 0; i < p.n_slots; ++i) run += (p.idx[i] - p.e_first == e);
+    }
+    counts[e] = run;
+  }
+  __syncthreads();
+  if (tid < 32) {   // exclusive prefix sums of the row counts and of the group counts, 32 experts per step
+    int run = 0, grun = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + tid;
+      const int c = e < E ? counts[e] : 0;
+      const int gc = (c + kTcNT - 1) / kTcNT;
+      int incl = c, gincl = gc;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, o), gv = __shfl_up_sync(0xFFFFFFFFu, gincl, o);
+        if (tid >= o) { incl += v; gincl += gv; }
+      }
+      if (e < E) { starts[e] = run + incl - c; gst[e] = grun + gincl - gc; }
+      run += __shfl_sync(0xFFFFFFFFu, incl, 31);
+      grun += __shfl_sync(0xFFFFFFFFu, gincl, 31);
+    }
+    if (tid == 0) {
+      starts[E] = run;
+      p.offs[E] = run;
+      *p.n_groups = grun;
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += nt) {
+    p.offs[e] = starts[e];
+    const int c = counts[e];
+    for (int q = 0; q * kTcNT < c; ++q)
+      p.groups[gst[e] + q] = make_int4(p.e_first + e, starts[e] + q * kTcNT, min(kTcNT, c - q * kTcNT), 0);
+    if (has_dup) {   // sequential, stable placement of this expert's slots
+      int c2 = starts[e];
+      for (int i = 0; i < p.n_slots; ++i)
+        if (p.idx[i] - p.e_first == e) { p.list[c2] = i; p.pos[i] = c2; ++c2; }
+    }
+  }
+  for (int i = tid; i < p.n_slots; i += nt) {
+    const int e = p.idx[i] - p.e_first;
+    if (e < 0 || e >= E) {
+      p.pos[i] = -1;
+    } else if (!has_dup) {
+      const int t = i / p.S, w = t >> 5;
+      const uint32_t bit = 1u << (t & 31);
+      const int ps = starts[e] + static_cast<int>(wpre[e * W + w]) + __popc(mask[e * W + w] & (bit - 1u));
+      p.list[ps] = i;
+      p.pos[i]   = ps;
+    }
+  }
+}
+inline size_t moe_sort_smem(size_t e_count, size_t T) {
+  return (2 * e_count * ((T + 31) / 32) + 3 * e_count + 8) * sizeof(int);
+}
+
+// One warp-iteration = eight 32-blocks of one row (four lanes per block), as quantize_rows_kernel.
+template <class SRC>
+__device__ void quantize_rows_part(const SRC* __restrict__ src, size_t ld, int nrows, int K, uint8_t* __restrict__ dst,
+                                   size_t pitch_bytes, int gwarp, int nwarp) {
+  const int nblk = K / 32, per_row = (nblk + 7) / 8;
+  const int lane = threadIdx.x & 31, l4 = lane & 3;
+  for (int it = gwarp; it < nrows * per_row; it += nwarp) {
+    const int row = it / per_row, b = (it - row * per_row) * 8 + (lane >> 2);
+    const SRC* x = src + static_cast<size_t>(row) * ld;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    uint8_t* out = dst + static_cast<size_t>(row) * pitch_bytes;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    if (b < nblk) load8<SRC>(x, static_cast<size_t>(b) * 32 + l4 * 8, vec_ok, v);
+    float d;
+    int part, total;
+    const uint2 packed = quantize_block_lane8(v, d, part, total);
+    if (b >= nblk) continue;
+    reinterpret_cast<uint2*>(out + static_cast<size_t>(b) * 32)[l4] = packed;
+    if (l4 == 0) {
+      reinterpret_cast<ActHdr*>(out + act_hdr_offset(K))[b] = ActHdr{d, part, total - part, 0};
+      const float ds = __fmul_rn(static_cast<float>(total), d);
+      reinterpret_cast<float2*>(out + act_bytes(K))[b] = make_float2(d, ds);
+      store_sum_parts(out, act_parts_offset(static_cast<size_t>(K)), b, ds);
+    }
+  }
+}
+
+template <class SRC>
+__global__ void __launch_bounds__(1024, 1) moe_prep_kernel(const PrepParams p) {
+  pdl_chain_entry();
+  extern __shared__ uint32_t prep_smem[];
+  if (blockIdx.x == 0) {
+    moe_sort_block(p, prep_smem);
+  } else if (p.X != nullptr) {
+    quantize_rows_part<SRC>(static_cast<const SRC*>(p.X), p.ldx, p.T, p.H, p.xrows, p.x_pitch,
+                            (blockIdx.x - 1) * (blockDim.x >> 5) + (threadIdx.x >> 5), (gridDim.x - 1) * (blockDim.x >> 5));
+  }
+}
+
+static cudaError_t moe_prep_launch(const PrepParams& p, int xs, cudaStream_t st) {
+  const size_t smem = moe_sort_smem(p.e_count, p.T);
+  int qctas = 0;
+  if (p.X != nullptr) {
+    const int items = p.T * ((p.H / 32 + 7) / 8);
+    qctas = max(1, min(4 * device_sm_count(), (items + 31) / 32));
+  }
+  auto kern = xs == KDNN_F32 ? moe_prep_kernel<float> : moe_prep_kernel<__nv_bfloat16>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  return launch_chained(kern, dim3(1 + qctas), dim3(1024), smem, st, p);
+}
+constexpr size_t kPrepSmemLimit = 160 * 1024;
+
 // Y[t, d] = Scalar(sum_s w[t,s] * out[pos(t,s), d]), slots ascending, fp32
 // (src/KokkosDNN_MoE.hpp:326-331; zero-weight and unrouted slots skipped,
 // src/KokkosDNN_GGUF.hpp:2205-2207).
@@ -256,20 +477,9 @@ __global__ void moe_combine4_kernel(const float* __restrict__ out, const int* __
 
 // ---- workspace layout -------------------------------------------------------------------
 struct MoeWs {
-  size_t offs, list, pos, xq, act, actq, out, total;
+  size_t offs, list, pos, groups, ngroups, xq, act, actq, out, total;
 };
 static size_t max_sz(size_t a, size_t b) { return a > b ? a : b; }
-// KDNN_TILE selects the Q4_K tile kernel: "mma" (mma.sync, default), "umma" (tcgen05 + TMEM),
-// "dp4a" (CUDA-core grouped kernel, which also serves every other format).
-int tile_kind() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("KDNN_TILE");
-    v             = !e ? 1 : (e[0] == 'd' ? 0 : (e[0] == 'u' ? 2 : 1));
-  }
-  return v;
-}
-bool tile_mma_enabled() { return tile_kind() != 0; }
 static MoeWs moe_ws_layout(size_t T, size_t S, size_t H, size_t F, size_t n_experts) {
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
   MoeWs w{};
@@ -277,6 +487,8 @@ static MoeWs moe_ws_layout(size_t T, size_t S, size_t H, size_t F, size_t n_expe
   w.offs = o; o += up((n_experts + 1) * sizeof(int));
   w.list = o; o += up(T * S * sizeof(int));
   w.pos  = o; o += up(T * S * sizeof(int));
+  w.groups = o; o += up((n_experts + T * S / kTcNT + 1) * sizeof(int4));
+  w.ngroups = o; o += 256;
   w.xq   = o; o += up(T * max_sz((H / 64) * sizeof(ActItem), act_row_pitch(H)));
   w.act  = o; o += up(T * S * F * sizeof(float));
   w.actq = o; o += up(T * S * max_sz((F / 64) * sizeof(ActItem), act_row_pitch(F)));
@@ -286,6 +498,90 @@ static MoeWs moe_ws_layout(size_t T, size_t S, size_t H, size_t F, size_t n_expe
 }
 size_t moe_workspace_bytes(size_t T, size_t S, size_t H, size_t F, size_t n_experts) {
   return moe_ws_layout(T, S, H, F, n_experts).total;
+}
+
+// The expert feed-forward between the slot sort and the combine, Q4_K on the tensor cores:
+// gate/up + SwiGLU (+ per-32 quantization of the result) and the down projection, two launches.
+// `kind` 2 = tcgen05 kernel (needs the tables' TMA descriptors), 1 = mma.sync kernel.
+static cudaError_t moe_tiles_q4k(int kind, const kdnn_b200_weight_table* gate, const kdnn_b200_weight_table* up,
+                                 const kdnn_b200_weight_table* down, size_t T, size_t S, int xs, size_t e_first,
+                                 size_t e_count, uint8_t* b, const MoeWs& L, cudaStream_t st) {
+  const size_t H = gate->cols, F = gate->rows;
+  const int n_slots = static_cast<int>(T * S);
+  int* offs = reinterpret_cast<int*>(b + L.offs);
+  int* list = reinterpret_cast<int*>(b + L.list);
+  float* act = reinterpret_cast<float*>(b + L.act);
+  float* out = reinterpret_cast<float*>(b + L.out);
+  uint8_t* xrows = b + L.xq;
+  uint8_t* arows = b + L.actq;
+  int* status = nullptr;
+  cudaError_t err = moe_status_ptr(&status);
+  if (err != cudaSuccess) return err;
+  if (kind == 2) {
+    const int max_groups = static_cast<int>(e_count) + n_slots / kTcNT;
+    TcParams g{};
+    g.maps0 = static_cast<const CUtensorMap*>(gate->tma); g.maps1 = static_cast<const CUtensorMap*>(up->tma);
+    g.N = (int)F; g.K = (int)H; g.tile_rows = 64; g.row_tiles = (int)((F + 63) / 64);
+    g.groups = reinterpret_cast<const int4*>(b + L.groups); g.n_groups = reinterpret_cast<const int*>(b + L.ngroups);
+    g.list = list; g.S = (int)S; g.xrows = xrows; g.x_pitch = act_row_pitch(H);
+    g.dst = act; g.ld_dst = F; g.round_bf16 = xs == KDNN_BF16; g.qdst = arows; g.q_pitch = act_row_pitch(F);
+    g.status = status;
+    err = launch_grouped_tc<1, float>(g, max_groups * g.row_tiles, st);
+    if (err != cudaSuccess) return err;
+    TcParams d{};
+    d.maps0 = static_cast<const CUtensorMap*>(down->tma);
+    d.N = (int)H; d.K = (int)F; d.tile_rows = 128; d.row_tiles = (int)((H + 127) / 128);
+    d.groups = g.groups; d.n_groups = g.n_groups; d.list = list; d.S = (int)S;
+    d.xrows = arows; d.x_pitch = act_row_pitch(F); d.dst = out; d.ld_dst = H; d.status = status;
+    return launch_grouped_tc<0, float>(d, max_groups * d.row_tiles, st);
+  }
+  MmaParams g{};
+  g.w0 = gate->base; g.w1 = up->base; g.row_bytes = (int)gate->row_bytes;
+  g.N = (int)F; g.K = (int)H; g.offs = offs; g.list = list; g.S = (int)S; g.g_first = (int)e_first;
+  g.xrows = xrows; g.x_pitch = act_row_pitch(H); g.dst = act; g.ld_dst = F;
+  g.round_bf16 = xs == KDNN_BF16; g.status = status;
+  // A group has n_slots / n_experts rows on average; routing is never uniform, so give every group one
+  // CTA more along z than the mean needs (CTAs without a pass return at once).
+  const int mean_rows = static_cast<int>((static_cast<size_t>(n_slots) + gate->n_experts - 1) / gate->n_experts);
+  const int passes_z  = max(1, min(4, 1 + (2 * mean_rows) / 32));
+  g.passes_z = passes_z;
+  g.early = T <= 8;   // one-token decode: the kernel in front of it is a handful of CTAs
+  const bool fused_q = F % 64 == 0;   // the epilogue quantizes whole 32-blocks of the result
+  if (fused_q) {
+    g.qdst    = arows;
+    g.q_pitch = act_row_pitch(F);
+  }
+  err = launch_grouped_mma<1, float>(g, (int)e_count, st);
+  if (err != cudaSuccess) return err;
+  if (!fused_q) {
+    err = launch_quantize_rows<float>(act, F, n_slots, (int)F, offs + e_count, arows, act_row_pitch(F), st);
+    if (err != cudaSuccess) return err;
+  }
+  MmaParams d{};
+  d.w0 = down->base; d.w1 = nullptr; d.row_bytes = (int)down->row_bytes;
+  d.N = (int)H; d.K = (int)F; d.offs = offs; d.list = list; d.S = (int)S; d.g_first = (int)e_first;
+  d.xrows = arows; d.x_pitch = act_row_pitch(F); d.dst = out; d.ld_dst = H; d.status = status;
+  d.passes_z = passes_z;
+  return launch_grouped_mma<0, float>(d, (int)e_count, st);
+}
+
+// Whether the tcgen05 kernel covers this call (otherwise the mma.sync kernel runs it).
+static bool tc_covers(const kdnn_b200_weight_table* gate, const kdnn_b200_weight_table* up,
+                      const kdnn_b200_weight_table* down) {
+  const size_t H = gate->cols, F = gate->rows;
+  return gate->tma != nullptr && up->tma != nullptr && down->tma != nullptr && F % 64 == 0 && H >= 512 && F >= 256;
+}
+
+template <class YT>
+static cudaError_t moe_combine_launch(const float* out, const int* pos, const float* wts, size_t T, size_t S, size_t H,
+                                      void* Y, size_t ldy, cudaStream_t st) {
+  const size_t ybytes = sizeof(YT);
+  const bool vec4 = H % 4 == 0 && (reinterpret_cast<uintptr_t>(Y) % (4 * ybytes)) == 0 && (ldy * ybytes) % (4 * ybytes) == 0;
+  if (vec4)
+    return launch_chained(moe_combine4_kernel<YT>, dim3((unsigned)((H / 4 + 127) / 128), (unsigned)T), dim3(128), 0, st,
+                          out, pos, wts, (int)T, (int)S, (int)H, static_cast<YT*>(Y), ldy);
+  return launch_chained(moe_combine_kernel<YT>, dim3((unsigned)((H + 255) / 256), (unsigned)T), dim3(256), 0, st, out,
+                        pos, wts, (int)T, (int)S, (int)H, static_cast<YT*>(Y), ldy);
 }
 
 cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
@@ -305,96 +601,67 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
   ActItem* actq = reinterpret_cast<ActItem*>(b + L.actq);
   float* out = reinterpret_cast<float*>(b + L.out);
   const int n_slots = static_cast<int>(T * S);
-  const int sort_ctas = static_cast<int>(e_count < 4 ? 1 : (e_count + 3) / 4 > 64 ? 64 : (e_count + 3) / 4);
-  const int cache_slots = n_slots <= 8192;   // the sweeps then read shared memory instead of global memory
-  cudaError_t err = launch_chained(moe_sort_kernel, dim3(sort_ctas), dim3(128),
-                                   (2 * (e_count + 1) + (cache_slots ? n_slots : 0)) * sizeof(int), st, idx, n_slots,
-                                   (int)e_first, (int)e_count, offs, list, pos, cache_slots);
-  if (err != cudaSuccess) return err;
   const bool all_q4k = gate->ggml_type == KDNN_GGML_Q4_K && down->ggml_type == KDNN_GGML_Q4_K &&
                        (reinterpret_cast<uintptr_t>(ws) & 15u) == 0;
-  if (e_count > 0 && all_q4k && tile_mma_enabled()) {
-    // tensor-core tile path: quantized rows in the reference staging layout
-    uint8_t* xrows = b + L.xq;
-    uint8_t* arows = b + L.actq;
-    err = xs == KDNN_F32
-              ? launch_quantize_rows<float>(static_cast<const float*>(X), ldx, (int)T, (int)H, nullptr, xrows, act_row_pitch(H), st)
-              : launch_quantize_rows<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(X), ldx, (int)T, (int)H, nullptr, xrows, act_row_pitch(H), st);
+  const int kind = !all_q4k ? 0 : (tile_kind() == 2 && !tc_covers(gate, up, down)) ? 1 : tile_kind();
+  cudaError_t err;
+  if (kind != 0 && moe_sort_smem(e_count, T) <= kPrepSmemLimit) {
+    // one launch: slot sort (CTA 0) + row quantizer (the other CTAs)
+    PrepParams pp{};
+    pp.idx = idx; pp.n_slots = n_slots; pp.S = (int)S; pp.e_first = (int)e_first; pp.e_count = (int)e_count;
+    pp.words = (int)((T + 31) / 32);
+    pp.offs = offs; pp.list = list; pp.pos = pos;
+    pp.groups = reinterpret_cast<int4*>(b + L.groups); pp.n_groups = reinterpret_cast<int*>(b + L.ngroups);
+    pp.X = e_count > 0 ? X : nullptr; pp.ldx = ldx; pp.T = (int)T; pp.H = (int)H;
+    pp.xrows = b + L.xq; pp.x_pitch = act_row_pitch(H);
+    err = moe_prep_launch(pp, xs, st);
     if (err != cudaSuccess) return err;
-    MmaParams g{};
-    g.w0 = gate->base; g.w1 = up->base; g.row_bytes = (int)gate->row_bytes;
-    g.N = (int)F; g.K = (int)H; g.offs = offs; g.list = list; g.S = (int)S; g.g_first = (int)e_first;
-    g.xrows = xrows; g.x_pitch = act_row_pitch(H); g.dst = act; g.ld_dst = F;
-    g.round_bf16 = xs == KDNN_BF16; g.status = moe_status_ptr();
-    // The mma.sync kernel quantizes its SwiGLU output in the epilogue (a CTA owns whole 32-blocks);
-    // the tcgen05 kernel writes floats and the row quantizer follows.
-    // A group has n_slots / n_experts rows on average; routing is never uniform, so give every group one
-    // CTA more along z than the mean needs (CTAs without a pass return at once).
-    const int mean_rows = static_cast<int>((static_cast<size_t>(n_slots) + gate->n_experts - 1) / gate->n_experts);
-    const int passes_z  = max(1, min(4, 1 + (2 * mean_rows) / 32));
-    g.passes_z = passes_z;
-    g.early = T <= 8;   // one-token decode: the row quantizer in front of it is a handful of CTAs
-    const bool fused_q = tile_kind() != 2 && F % 64 == 0;
-    if (fused_q) {
-      g.qdst    = arows;
-      g.q_pitch = act_row_pitch(F);
-    }
-    err = tile_kind() == 2 ? launch_grouped_umma<1, float>(g, (int)e_count, st)
-                           : launch_grouped_mma<1, float>(g, (int)e_count, st);
-    if (err != cudaSuccess) return err;
-    if (!fused_q) {
-      err = launch_quantize_rows<float>(act, F, n_slots, (int)F, offs + e_count, arows, act_row_pitch(F), st);
+    if (e_count > 0) {
+      err = moe_tiles_q4k(kind, gate, up, down, T, S, xs, e_first, e_count, b, L, st);
       if (err != cudaSuccess) return err;
     }
-    MmaParams d{};
-    d.w0 = down->base; d.w1 = nullptr; d.row_bytes = (int)down->row_bytes;
-    d.N = (int)H; d.K = (int)F; d.offs = offs; d.list = list; d.S = (int)S; d.g_first = (int)e_first;
-    d.xrows = arows; d.x_pitch = act_row_pitch(F); d.dst = out; d.ld_dst = H; d.status = moe_status_ptr();
-    d.passes_z = passes_z;
-    err = tile_kind() == 2 ? launch_grouped_umma<0, float>(d, (int)e_count, st)
-                           : launch_grouped_mma<0, float>(d, (int)e_count, st);
+  } else {
+    const int sort_ctas = static_cast<int>(e_count < 4 ? 1 : (e_count + 3) / 4 > 64 ? 64 : (e_count + 3) / 4);
+    const int cache_slots = n_slots <= 8192;   // the sweeps then read shared memory instead of global memory
+    err = launch_chained(moe_sort_kernel, dim3(sort_ctas), dim3(128),
+                         (2 * (e_count + 1) + (cache_slots ? n_slots : 0)) * sizeof(int), st, idx, n_slots,
+                         (int)e_first, (int)e_count, offs, list, pos, cache_slots);
     if (err != cudaSuccess) return err;
-  } else if (e_count > 0) {
-    err = xs == KDNN_F32
-              ? launch_quantize_items<float>(gate->ggml_type, static_cast<const float*>(X), ldx, (int)T, (int)H, nullptr, xq, st)
-              : launch_quantize_items<__nv_bfloat16>(gate->ggml_type, static_cast<const __nv_bfloat16*>(X), ldx, (int)T, (int)H, nullptr, xq, st);
-    if (err != cudaSuccess) return err;
-    GroupedParams g{};
-    g.w0 = gate->base; g.w1 = up->base;
-    g.row_bytes0 = (int)gate->row_bytes; g.row_bytes1 = (int)up->row_bytes;
-    g.N = (int)F; g.K = (int)H;
-    g.offs = offs; g.list = list; g.S = (int)S; g.g_first = (int)e_first;
-    g.src = xq; g.dst = act; g.ld_dst = F; g.round_bf16 = xs == KDNN_BF16;
-    err = xs == KDNN_F32 ? launch_grouped_dt<1, float, float>(gate->ggml_type, g, (int)e_count, st)
-                         : launch_grouped_dt<1, __nv_bfloat16, float>(gate->ggml_type, g, (int)e_count, st);
-    if (err != cudaSuccess) return err;
-    err = launch_quantize_items<float>(down->ggml_type, act, F, n_slots, (int)F, offs + e_count, actq, st);
-    if (err != cudaSuccess) return err;
-    GroupedParams d{};
-    d.w0 = down->base; d.w1 = nullptr;
-    d.row_bytes0 = (int)down->row_bytes;
-    d.N = (int)H; d.K = (int)F;
-    d.offs = offs; d.list = list; d.S = (int)S; d.g_first = (int)e_first;
-    d.src = actq; d.dst = out; d.ld_dst = H;
-    err = launch_grouped_dt<0, float, float>(down->ggml_type, d, (int)e_count, st);
-    if (err != cudaSuccess) return err;
+    if (e_count > 0 && kind != 0) {   // slot matrix too large for the one-CTA sort: mma.sync kernel behind the plain sort
+      err = xs == KDNN_F32
+                ? launch_quantize_rows<float>(static_cast<const float*>(X), ldx, (int)T, (int)H, nullptr, b + L.xq, act_row_pitch(H), st)
+                : launch_quantize_rows<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(X), ldx, (int)T, (int)H, nullptr, b + L.xq, act_row_pitch(H), st);
+      if (err != cudaSuccess) return err;
+      err = moe_tiles_q4k(1, gate, up, down, T, S, xs, e_first, e_count, b, L, st);
+      if (err != cudaSuccess) return err;
+    } else if (e_count > 0) {
+      err = xs == KDNN_F32
+                ? launch_quantize_items<float>(gate->ggml_type, static_cast<const float*>(X), ldx, (int)T, (int)H, nullptr, xq, st)
+                : launch_quantize_items<__nv_bfloat16>(gate->ggml_type, static_cast<const __nv_bfloat16*>(X), ldx, (int)T, (int)H, nullptr, xq, st);
+      if (err != cudaSuccess) return err;
+      GroupedParams g{};
+      g.w0 = gate->base; g.w1 = up->base;
+      g.row_bytes0 = (int)gate->row_bytes; g.row_bytes1 = (int)up->row_bytes;
+      g.N = (int)F; g.K = (int)H;
+      g.offs = offs; g.list = list; g.S = (int)S; g.g_first = (int)e_first;
+      g.src = xq; g.dst = act; g.ld_dst = F; g.round_bf16 = xs == KDNN_BF16;
+      err = xs == KDNN_F32 ? launch_grouped_dt<1, float, float>(gate->ggml_type, g, (int)e_count, st)
+                           : launch_grouped_dt<1, __nv_bfloat16, float>(gate->ggml_type, g, (int)e_count, st);
+      if (err != cudaSuccess) return err;
+      err = launch_quantize_items<float>(down->ggml_type, act, F, n_slots, (int)F, offs + e_count, actq, st);
+      if (err != cudaSuccess) return err;
+      GroupedParams d{};
+      d.w0 = down->base; d.w1 = nullptr;
+      d.row_bytes0 = (int)down->row_bytes;
+      d.N = (int)H; d.K = (int)F;
+      d.offs = offs; d.list = list; d.S = (int)S; d.g_first = (int)e_first;
+      d.src = actq; d.dst = out; d.ld_dst = H;
+      err = launch_grouped_dt<0, float, float>(down->ggml_type, d, (int)e_count, st);
+      if (err != cudaSuccess) return err;
+    }
   }
-  const size_t ybytes = ys == KDNN_F32 ? 4 : 2;
-  const bool vec4 = H % 4 == 0 && (reinterpret_cast<uintptr_t>(Y) % (4 * ybytes)) == 0 && (ldy * ybytes) % (4 * ybytes) == 0;
-  if (vec4) {
-    dim3 cgrid((unsigned)((H / 4 + 127) / 128), (unsigned)T);
-    if (ys == KDNN_F32)
-      return launch_chained(moe_combine4_kernel<float>, cgrid, dim3(128), 0, st, out, pos, wts, (int)T, (int)S, (int)H,
-                            static_cast<float*>(Y), ldy);
-    return launch_chained(moe_combine4_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, st, out, pos, wts, (int)T, (int)S,
-                          (int)H, static_cast<__nv_bfloat16*>(Y), ldy);
-  }
-  dim3 cgrid((unsigned)((H + 255) / 256), (unsigned)T);
-  if (ys == KDNN_F32)
-    return launch_chained(moe_combine_kernel<float>, cgrid, dim3(256), 0, st, out, pos, wts, (int)T, (int)S, (int)H,
-                          static_cast<float*>(Y), ldy);
-  return launch_chained(moe_combine_kernel<__nv_bfloat16>, cgrid, dim3(256), 0, st, out, pos, wts, (int)T, (int)S,
-                        (int)H, static_cast<__nv_bfloat16*>(Y), ldy);
+  return ys == KDNN_F32 ? moe_combine_launch<float>(out, pos, wts, T, S, H, Y, ldy, st)
+                        : moe_combine_launch<__nv_bfloat16>(out, pos, wts, T, S, H, Y, ldy, st);
 }
 
 // out[t,:] = Scalar(r / sqrt(mean(r^2) + eps)) with r = Scalar(float(h[t,:]) + y[t,:]): the residual

@@ -205,6 +205,7 @@ kdnn_b200_weight_table table_of(const Table& t) {
   c.cols      = t.cols;
   c.row_bytes = t.row_bytes;
   c.n_experts = t.size();
+  c.tma       = nullptr;
   return c;
 }
 

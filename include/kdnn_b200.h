@@ -56,12 +56,6 @@ const char* kdnn_b200_last_error(void);
  * Synchronizes the device. */
 int kdnn_b200_device_status(void);
 
-/* Debug aid: with a device buffer of 2 * SMs * 8 warps * 8 uint64 set, every warp of the
- * streaming GEMV kernel records eight globaltimer stamps (entry, prefetch issued,
- * dependency resolved, activations staged, first stage landed, first refill, -, exit)
- * of the most recent launch. NULL switches it off. No counterpart in the reference. */
-void kdnn_b200_debug_set_trace(void* device_buffer);
-
 /* ---- GEMV -------------------------------------------------------------- */
 
 /* Bytes of activation staging for a K-element row; 0 when K % 32 != 0.
@@ -90,6 +84,27 @@ int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t 
                          const void* x, int x_scalar, void* y, int y_scalar,
                          void* act_scratch, size_t act_scratch_bytes, void* stream);
 
+/* Optional tuning of one GEMV call; all zero = the library's own choice. Stands in for
+ * Impl::GgufMvq::Int8Layout, src/KokkosDNN_GGUFGemvInt8.hpp:604-608 (rows_per_group keeps its meaning:
+ * weight rows that share one pass over the activation window; the other fields name this library's
+ * kernels instead of the reference's threads_per_row / groups). Results do not depend on it beyond
+ * fp32 summation order. */
+typedef struct {
+  int kernel;         /* 0 auto; 1 activation window in registers; 2 window in shared memory;
+                         3 item mapping with the window in shared memory; 4 plain loads (any alignment) */
+  int rows_per_group; /* 0 auto; 1 or 2 */
+  int stages;         /* 0 auto; 2..4 ring stages per warp */
+  int early_stages;   /* 0 auto; ring stages requested before the activation row is quantized */
+  int warps;          /* 0 auto; warps per CTA */
+  int no_pdl;         /* 1: launch without programmatic stream serialization */
+} kdnn_b200_gemv_layout;
+
+/* kdnn_b200_quant_gemv with a tuning struct (NULL = defaults). */
+int kdnn_b200_quant_gemv_ex(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                            const void* x, int x_scalar, void* y, int y_scalar,
+                            void* act_scratch, size_t act_scratch_bytes,
+                            const kdnn_b200_gemv_layout* layout, void* stream);
+
 /* The same GEMV for callers that have no scratch buffer to give and may not create one: a
  * host runtime that reserved the whole device up front and forbids cudaMalloc in its
  * plug-ins, or a decode loop that is not allowed to touch the allocator because an
@@ -108,6 +123,11 @@ int kdnn_b200_quant_gemv(uint32_t ggml_type, const void* w, size_t rows, size_t 
  * caller's act_scratch view. */
 int kdnn_b200_quant_gemv_noalloc(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
                                  const void* x, int x_scalar, void* y, int y_scalar, void* stream);
+/* The same entry point with the tuning struct of kdnn_b200_quant_gemv_ex (NULL = defaults); x and y must
+ * have unit stride, as everywhere. No counterpart in the reference either. */
+int kdnn_b200_quant_gemv_noalloc_ex(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
+                                    const void* x, int x_scalar, void* y, int y_scalar,
+                                    const kdnn_b200_gemv_layout* layout, void* stream);
 
 /* kdnn_b200_quant_gemv for a host that keeps activations and results in its own (ideally page-locked)
  * memory: one call enqueues the copy of x_host[cols] to x_dev, the GEMV, and the copy of y_dev[rows] to
@@ -151,6 +171,22 @@ int kdnn_b200_quant_gemm(uint32_t ggml_type, const void* w, size_t N, size_t K,
                          void* Y, size_t ldy, int y_scalar,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* Parity probe of the batched path: kdnn_b200_quant_gemm on the tcgen05 tile kernel that additionally
+ * stores the raw int32 sub-block dots the tensor cores produced, dots[m][n][K/32] (Q4_K: the integer
+ * sum over 32 elements of nibble * xq, the factor the reference multiplies by d*sc*dx,
+ * src/KokkosDNN_GGUFGemvInt8.hpp:359-388). KDNN_DECLINED when the tcgen05 kernel does not serve the call. */
+int kdnn_b200_quant_gemm_dots(uint32_t ggml_type, const void* w, size_t N, size_t K,
+                              const void* X, size_t ldx, size_t M, int x_scalar,
+                              void* Y, size_t ldy, int y_scalar, int32_t* dots,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* Which tile kernel the batched Q4_K calls (quant_gemm, moe_ffn, moe_block) use from now on, process-wide:
+ * 2 = tcgen05.mma + TMEM, fed by tensor-map TMA (the default), 1 = mma.sync m16n8k32, 0 = the CUDA-core
+ * dp4a kernel that serves every other format. Returns the previous kind; kind < 0 only queries.
+ * A tuning knob in the sense of Int8Layout (src/KokkosDNN_GGUFGemvInt8.hpp:604-608); results agree
+ * within fp32 summation order. */
+int kdnn_b200_tile_kind(int kind);
+
 /* ---- MoE ------------------------------------------------------------------ */
 
 /* Per-token top-k expert selection and combination weights.
@@ -172,7 +208,22 @@ typedef struct {
   uint32_t ggml_type;
   size_t rows, cols, row_bytes;
   size_t n_experts;
+  const void* tma;       /* device array [n_experts] of 128-byte TMA descriptors written by
+                            kdnn_b200_weight_table_tma_encode, or NULL (the tcgen05 tile kernel then
+                            leaves the call to the mma.sync kernel) */
 } kdnn_b200_weight_table;
+
+/* Bytes of the descriptor array of a table with n_experts entries (128 each). */
+size_t kdnn_b200_weight_table_tma_bytes(size_t n_experts);
+
+/* Fills host_out[n_experts * 128] with one TMA descriptor per expert matrix (host_base: the payload
+ * addresses on the HOST, i.e. what make_quant_weight_table copies to the device,
+ * src/KokkosDNN_GGUF.hpp:2031-2053). The caller copies host_out to 128-byte aligned device memory and
+ * points `tma` at it; payloads must not move afterwards (they never do after load,
+ * models/lfm2_5/KokkosDNN_LFM25Model.hpp:557-560). Only Q4_K tables have a tensor-core kernel:
+ * KDNN_DECLINED for other types (leave `tma` NULL). Pure host work, no launch, no allocation. */
+int kdnn_b200_weight_table_tma_encode(const uintptr_t* host_base, uint32_t ggml_type, size_t rows, size_t cols,
+                                      size_t n_experts, void* host_out);
 
 /* Workspace bytes for kdnn_b200_moe_ffn with T tokens, S slots per token. */
 size_t kdnn_b200_moe_workspace_bytes(size_t T, size_t S, size_t H, size_t F, size_t n_experts);

@@ -18,26 +18,26 @@ DTYPES = [O.Q4_K, O.Q6_K, O.Q8_0]
 DTYPES_RANDOM = DTYPES + [O.Q5_K]   # Q5_K has no encoder here: random payloads only
 
 
-def _run(kd, dtype, packed, rows, K, x_t, y_dtype):
+def _run(kd, dtype, packed, rows, K, x_t, y_dtype, layout=None):
     dev = torch.device("cuda:0")
     w = kd.QuantWeight.from_numpy(packed, dtype, rows, K, dev)
     y = torch.full((rows,), float("nan"), dtype=y_dtype, device=dev)
     scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
-    kd.quant_gemv(x_t.to(dev), w, y, scratch)
+    kd.quant_gemv(x_t.to(dev), w, y, scratch, layout)
     torch.cuda.synchronize()
     assert kd.device_status() == 0
     return w, y, scratch
 
 
 def _check(kd, port, dtype, rows, K, seed, payload, x_dtype=torch.float32, y_dtype=torch.float32,
-           probe=True):
+           probe=True, layout=None):
     if payload == "random":
         packed = kd.ggml_pack.random_payload(dtype, rows, K, seed)
     else:
         packed = kd.ggml_pack.synth_weight(dtype, rows, K, seed)
     g = torch.Generator().manual_seed(seed + 1)
     x_t = torch.randn(K, generator=g).to(x_dtype)
-    w, y, scratch = _run(kd, dtype, packed, rows, K, x_t, y_dtype)
+    w, y, scratch = _run(kd, dtype, packed, rows, K, x_t, y_dtype, layout)
     host = O.aligned_copy(packed)
     xf = x_t.float().numpy()
     y_ref, staging = port.gemv_int8(dtype, host, rows, K, xf)
@@ -221,18 +221,16 @@ def test_graph_replays_recompute_every_row(kd, port, dtype):
     assert kd.device_status() == 0
 
 
-@pytest.mark.parametrize("env", [{"KDNN_GEMV_Q4K": "1"}, {"KDNN_GEMV_ITEM": "1"}, {"KDNN_GEMV_ITEM": "1", "KDNN_GEMV_RW": "1"},
-                                 {"KDNN_GEMV_STAGES": "2"}, {"KDNN_GEMV_STAGES": "4", "KDNN_GEMV_EARLY": "1"}])
+@pytest.mark.parametrize("layout", [{"kernel": 2}, {"kernel": 3}, {"kernel": 3, "rows_per_group": 1}, {"kernel": 4},
+                                    {"stages": 2}, {"stages": 4, "early_stages": 1}, {"rows_per_group": 1, "no_pdl": 1}])
 @pytest.mark.parametrize("dtype", DTYPES_RANDOM)
-def test_alternate_streaming_kernels(kd, port, dtype, env, monkeypatch):
+def test_alternate_streaming_kernels(kd, port, dtype, layout):
     """The kernels that take over for very long rows (activation window in shared memory, item
-    mapping) and the other ring depths are selected per launch by environment switches; they must
-    give the same results as the default ones."""
-    for k, v in env.items():
-        monkeypatch.setenv(k, v)
-    _check(kd, port, dtype, 37, 4096, 91, "random")
-    _check(kd, port, dtype, 5000, 2048, 92, "random", probe=False)
-    _check(kd, port, dtype, 300, 6144 if dtype != O.Q4_K else 6656, 93, "random", probe=False)
+    mapping), the plain-load kernels and the other ring depths can be selected per call through the
+    layout struct (the counterpart of Int8Layout); they must give the same results as the defaults."""
+    _check(kd, port, dtype, 37, 4096, 91, "random", layout=layout)
+    _check(kd, port, dtype, 5000, 2048, 92, "random", probe=False, layout=layout)
+    _check(kd, port, dtype, 300, 6144 if dtype != O.Q4_K else 6656, 93, "random", probe=False, layout=layout)
 
 
 def test_q5k_lm_head_like_shape(kd, port):

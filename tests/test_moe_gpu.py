@@ -13,6 +13,23 @@ from oracle import oracle as O
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 DEV = "cuda:0"
+TILE_KINDS = [2, 1, 0]        # tcgen05 + TMEM (default), mma.sync, CUDA-core dp4a
+TILE_NAMES = {2: "tcgen05", 1: "mma.sync", 0: "dp4a"}
+
+
+@pytest.fixture(params=TILE_KINDS, ids=lambda k: TILE_NAMES[k])
+def tile(kd, request):
+    """Runs the test once per Q4_K tile kernel (explicit selection through the C ABI, restored afterwards)."""
+    prev = kd.tile_kind(request.param)
+    yield request.param
+    kd.tile_kind(prev)
+
+
+@pytest.fixture(params=[2, 1], ids=lambda k: TILE_NAMES[k])
+def tensor_tile(kd, request):
+    prev = kd.tile_kind(request.param)
+    yield request.param
+    kd.tile_kind(prev)
 
 
 def _route(kd, lg_t, bias_t, k, norm, scale, sig):
@@ -90,7 +107,9 @@ def _ffn(kd, X_t, tabs, idx, wts, y_dtype, e_first=0, e_count=None):
 @pytest.mark.parametrize("dtypes", [(O.Q4_K, O.Q4_K, O.Q4_K), (O.Q4_K, O.Q4_K, O.Q6_K), (O.Q8_0, O.Q8_0, O.Q8_0),
                                     (O.Q6_K, O.Q6_K, O.Q4_K)])
 @pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
-def test_moe_ffn_small(kd, port, dtypes, x_dtype):
+def test_moe_ffn_small(kd, port, dtypes, x_dtype, tile):
+    if dtypes != (O.Q4_K, O.Q4_K, O.Q4_K) and tile != 2:
+        pytest.skip("the tile kind only matters for all-Q4_K experts")
     E, H, F, T, S = 6, 512, 256, 21, 3
     gate, up, down = _experts(kd, E, H, F, 40, dtypes)
     tabs = _tables(kd, gate, up, down, dtypes, H, F)
@@ -162,8 +181,10 @@ def test_moe_ffn_q5k_experts(kd, port, dtypes):
 
 
 @pytest.mark.parametrize("dtype,N,K", [(O.Q4_K, 300, 1024), (O.Q6_K, 130, 2048), (O.Q8_0, 257, 512), (O.Q5_K, 200, 1024)])
-@pytest.mark.parametrize("M", [1, 2, 3, 5, 16, 17, 32])
-def test_quant_gemm_rows_equal_gemv(kd, port, dtype, N, K, M):
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 16, 17, 32, 33, 70])
+def test_quant_gemm_rows_equal_gemv(kd, port, dtype, N, K, M, tile):
+    if dtype != O.Q4_K and tile != 2:
+        pytest.skip("the tile kind only matters for Q4_K")
     packed = kd.ggml_pack.random_payload(dtype, N, K, N + K)
     w = kd.QuantWeight.from_numpy(packed, dtype, N, K, DEV)
     X = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16)
@@ -198,12 +219,78 @@ def _full_layer(kd, port, E, k, H, F, T, seed):
     assert np.abs(got - ref).max() <= 1e-3 * np.abs(ref).max()
 
 
-def test_fine_grained_layer_full_size(kd, port):
+def test_fine_grained_layer_full_size(kd, port, tensor_tile):
     """One layer of the 128-expert / top-8 / hidden 2048 / FFN 768 / 256-token configuration."""
     _full_layer(kd, port, 128, 8, 2048, 768, 256, 77)
 
 
-def test_mixtral_style_layer_reduced_tokens(kd, port):
-    """8 experts / top-2 / hidden 4096 / FFN 14336 at the full weight shapes, 16 tokens (the checker's cost
-    grows with tokens; the 64-token case is covered by the routing and tile-tail cases above)."""
-    _full_layer(kd, port, 8, 2, 4096, 14336, 16, 78)
+def test_mixtral_style_layer_full_size(kd, port, tensor_tile):
+    """8 experts / top-2 / hidden 4096 / FFN 14336 / 64 tokens: the coarse MoE configuration at its full
+    shapes (792.7 MB of packed expert bytes)."""
+    _full_layer(kd, port, 8, 2, 4096, 14336, 64, 78)
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 32])
+def test_batched_sweep_at_the_llama_ffn_shape(kd, port, M, tensor_tile):
+    """Q4_K 14336 x 4096 with 1..32 activation rows: every output row equals the int8 GEMV of its
+    activation row (the reference has no batched int8 kernel: src/KokkosDNN_GGUF.hpp:2564-2593 is fp)."""
+    N, K = 14336, 4096
+    packed = kd.ggml_pack.random_payload(O.Q4_K, N, K, 4242)
+    w = kd.QuantWeight.from_numpy(packed, O.Q4_K, N, K, DEV)
+    X = torch.randn(M, K, generator=torch.Generator().manual_seed(100 + M)).to(torch.bfloat16)
+    Y = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ws = torch.zeros(kd.quant_gemm_workspace_bytes(M, K), dtype=torch.uint8, device=DEV)
+    kd.quant_gemm(X.to(DEV), w, Y, ws)
+    torch.cuda.synchronize()
+    assert kd.device_status() == 0
+    host = O.aligned_copy(packed)
+    got = Y.cpu().numpy()
+    for m in range(M):
+        ref, _ = port.gemv_int8(O.Q4_K, host, N, K, X[m].float().numpy())
+        assert np.abs(got[m] - ref).max() <= 1e-3 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("N,K,M", [(128, 256, 1), (300, 1024, 5), (257, 2048, 32), (130, 512, 45)])
+def test_tcgen05_sub_block_dots_bit_exact(kd, port, N, K, M):
+    """The int32 sub-block dots the PRODUCTION tile kernel's tensor-core instructions leave in tensor memory,
+    dumped by the kernel itself, equal the reference's unit integers summed per 32-element sub-block
+    (src/KokkosDNN_GGUFGemvInt8.hpp:359-388: dotA / dotB of the two half units of a sub-block)."""
+    prev = kd.tile_kind(2)
+    try:
+        packed = kd.ggml_pack.random_payload(O.Q4_K, N, K, N * 7 + K)
+        w = kd.QuantWeight.from_numpy(packed, O.Q4_K, N, K, DEV)
+        X = torch.randn(M, K, generator=torch.Generator().manual_seed(M + K))
+        Y = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+        ws = torch.zeros(kd.quant_gemm_workspace_bytes(M, K), dtype=torch.uint8, device=DEV)
+        dots = kd.quant_gemm_dots(X.to(DEV), w, Y, ws).cpu().numpy()
+        torch.cuda.synchronize()
+        assert kd.device_status() == 0
+    finally:
+        kd.tile_kind(prev)
+    host = O.aligned_copy(packed)
+    for m in range(M):
+        ref, staging = port.gemv_int8(O.Q4_K, host, N, K, X[m].numpy())
+        ints, _ = port.unit_table(O.Q4_K, host, N, K, staging)      # [N, K/32 units, {dotA, dotB}]
+        u = ints.reshape(N, K // 256, 4, 2, 2)                      # [row, block, iter, half, A/B]
+        want = u.sum(axis=3).reshape(N, K // 32)                    # sub-block 2*iter = A, 2*iter+1 = B
+        assert np.array_equal(dots[m], want), m
+        assert np.abs(Y[m].cpu().numpy() - ref).max() <= 1e-3 * np.abs(ref).max()
+
+
+def test_duplicate_expert_in_one_token(kd, port, tensor_tile):
+    """idx may name the same expert twice for one token (the reference treats every slot on its own,
+    src/KokkosDNN_GGUF.hpp:2106-2110): both slots count."""
+    E, H, F, T, S = 4, 512, 256, 9, 3
+    dt3 = (O.Q4_K,) * 3
+    gate, up, down = _experts(kd, E, H, F, 90, dt3)
+    tabs = _tables(kd, gate, up, down, dt3, H, F)
+    rng = np.random.default_rng(12)
+    X = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32))
+    idx = np.stack([rng.permutation(E)[:S] for _ in range(T)]).astype(np.int32)
+    idx[2, 1] = idx[2, 0]
+    idx[5, :] = 3
+    wts = rng.random((T, S)).astype(np.float32)
+    al = lambda lst: [O.aligned_copy(a) for a in lst]
+    ref = port.moe_ffn_int8(X.numpy(), al(gate), al(up), al(down), idx, wts, F, dt3, bf16=False)
+    got = _ffn(kd, X, tabs, idx, wts, torch.float32)
+    assert np.abs(got - ref).max() <= 1e-3 * np.abs(ref).max()
