@@ -64,7 +64,7 @@ class GemvLayoutC(C.Structure):
 
 
 KERNEL_AUTO, KERNEL_XREG, KERNEL_SMEM_WINDOW, KERNEL_ITEM_STREAM, KERNEL_PLAIN_LOADS = 0, 1, 2, 3, 4
-TILE_DP4A, TILE_MMA_SYNC, TILE_TCGEN05 = 0, 1, 2
+TILE_DP4A, TILE_MMA_SYNC, TILE_TCGEN05, TILE_AUTO = 0, 1, 2, 3
 
 
 def _load() -> C.CDLL:
@@ -222,8 +222,8 @@ def quant_gemv_int8_supported(dtype: int, K: int, scalar: torch.dtype = torch.fl
 
 
 def tile_kind(kind: int = -1) -> int:
-    """Selects the tile kernel of the batched Q4_K calls (TILE_TCGEN05 default, TILE_MMA_SYNC, TILE_DP4A);
-    returns the previous selection. A negative kind only queries."""
+    """Selects the kernel of the batched Q4_K calls (TILE_AUTO default = by measured crossover, TILE_TCGEN05,
+    TILE_MMA_SYNC, TILE_DP4A); returns the previous selection. A negative kind only queries."""
     return int(lib.kdnn_b200_tile_kind(kind))
 
 

@@ -42,7 +42,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     env.pop("CC", None)   # the image's CC/CXX point at a compiler front-end nvcc cannot drive
     env.pop("CXX", None)
     nvcc = _nvcc()
-    flags = [f for f in NVCC_FLAGS if f != "-shared"]
+    flags = [f for f in NVCC_FLAGS if f != "-shared"] + os.environ.get("KDNN_NVCC_EXTRA", "").split()
     with tempfile.TemporaryDirectory(prefix="kdnn_build_") as tmp:
         def compile_one(src: str):
             obj = os.path.join(tmp, src.replace(".cu", ".o"))

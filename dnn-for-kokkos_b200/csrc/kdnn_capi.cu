@@ -257,7 +257,7 @@ int kdnn_b200_quant_gemm_dots(uint32_t ggml_type, const void* w, size_t N, size_
     return KDNN_DECLINED;
   if ((ggml_type == KDNN_GGML_Q4_K || ggml_type == KDNN_GGML_Q5_K) && (reinterpret_cast<uintptr_t>(w) & 15u) != 0u)
     return KDNN_DECLINED;   // 16-byte loads of the super-blocks, src/KokkosDNN_GGUFGemvInt8.hpp:741-743
-  if (dots != nullptr && (ggml_type != KDNN_GGML_Q4_K || kdnn::tile_kind() != 2)) return KDNN_DECLINED;
+  if (dots != nullptr && (ggml_type != KDNN_GGML_Q4_K || kdnn::tile_kind() < 2)) return KDNN_DECLINED;
   return cuda_result(kdnn::gemm_launch(ggml_type, w, N, K, X, ldx, M, x_scalar, Y, ldy, y_scalar,
                                        workspace, dots, static_cast<cudaStream_t>(stream)),
                      "quant_gemm");

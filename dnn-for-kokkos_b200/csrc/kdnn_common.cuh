@@ -248,6 +248,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same probe with a suspend-time hint (ns): a thread whose phase is not complete is parked by the
+// hardware for up to that long (it resumes at once when the phase completes) instead of coming back to
+// spin -- a CTA with many waiting warps otherwise spends its issue slots on their polling loops.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: gives up after `limit` probes (each probe itself blocks for a
 // hardware-defined slice), so a copy that never lands cannot hang the GPU.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,

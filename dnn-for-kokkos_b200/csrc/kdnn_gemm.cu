@@ -9,6 +9,8 @@ namespace kdnn {
 
 int tile_kind();
 cudaError_t moe_status_ptr(int** out);
+cudaError_t gemv_launch(uint32_t dt, const void* w, size_t rows, size_t cols, const void* x, int xs,
+                        void* y, int ys, void* scratch, const kdnn_b200_gemv_layout* layout, cudaStream_t stream);
 
 // workspace: [offs: 2 ints, group count | pad to 256][wptr: 1 address | pad to 256][list: M ints][groups][items: M x K/64]
 static size_t gemm_groups_offset(size_t M) { return 512 + ((M * sizeof(int) + 255) & ~size_t(255)); }
@@ -49,6 +51,26 @@ static int gemm_tile_rows(size_t N, size_t groups) {
 cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const void* X, size_t ldx,
                         size_t M, int xs, void* Y, size_t ldy, int ys, void* ws, int32_t* dots, cudaStream_t st) {
   uint8_t* b      = static_cast<uint8_t*>(ws);
+  // Crossover measured on a 14336 x 4096 Q4_K matrix: one GEMV kernel per activation row (6.9 us each) beats
+  // the tile kernels (24 us and up) for up to three rows; the tcgen05 kernel is the faster tile kernel up
+  // to eight rows (24-27 us against 30-31 us), the mma.sync kernel beyond (28 / 37 us against 31 / 42 us
+  // at 16 / 32 rows).
+  int kind = tile_kind();
+  if (kind == 3 && dots == nullptr) {
+    if (M <= 3) {
+      uint8_t* scratch = b + gemm_items_offset(M);   // room for one staged row: the workspace holds M of them
+      const size_t xb = xs == KDNN_F32 ? 4 : 2, yb = ys == KDNN_F32 ? 4 : 2;
+      for (size_t m = 0; m < M; ++m) {
+        const cudaError_t e = gemv_launch(dt, w, N, K, static_cast<const uint8_t*>(X) + m * ldx * xb, xs,
+                                          static_cast<uint8_t*>(Y) + m * ldy * yb, ys, scratch, nullptr, st);
+        if (e != cudaSuccess) return e;
+      }
+      return cudaSuccess;
+    }
+    kind = M <= 8 ? 2 : 1;
+  } else if (kind == 3) {
+    kind = 2;
+  }
   int* offs       = reinterpret_cast<int*>(b);
   uintptr_t* wptr = reinterpret_cast<uintptr_t*>(b + 256);
   int* list       = reinterpret_cast<int*>(b + 512);
@@ -56,7 +78,7 @@ cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const vo
   cudaError_t err = launch_chained(gemm_setup_kernel, dim3((unsigned)((M + 255) / 256)), dim3(256), 0, st, (int)M,
                                    reinterpret_cast<uintptr_t>(w), offs, wptr, list, groups);
   if (err != cudaSuccess) return err;
-  if (dt == KDNN_GGML_Q4_K && tile_kind() != 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0) {
+  if (dt == KDNN_GGML_Q4_K && kind != 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0) {
     uint8_t* xrows = b + gemm_items_offset(M);
     int* status = nullptr;
     err = moe_status_ptr(&status);
@@ -65,7 +87,7 @@ cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const vo
               ? launch_quantize_rows<float>(static_cast<const float*>(X), ldx, (int)M, (int)K, nullptr, xrows, act_row_pitch(K), st)
               : launch_quantize_rows<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(X), ldx, (int)M, (int)K, nullptr, xrows, act_row_pitch(K), st);
     if (err != cudaSuccess) return err;
-    if (tile_kind() == 2) {
+    if (kind == 2) {
       TcParams t{};
       err = tc_encode_matrix(&t.one, w, N, row_bytes_of(dt, K));
       if (err == cudaSuccess) {

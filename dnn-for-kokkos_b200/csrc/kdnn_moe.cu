@@ -83,11 +83,13 @@ cudaError_t tc_encode_matrix_host(void* out128, const void* w, size_t rows, size
   return e;
 }
 
-// Which Q4_K tile kernel the batched calls use: 2 = tcgen05 + TMEM (default), 1 = mma.sync,
-// 0 = the CUDA-core dp4a kernel (which also serves every other format). Process-wide, read per call.
-static std::atomic<int> g_tile_kind{2};
+// Which Q4_K tile kernel the batched calls use: 3 = by measured crossover (default: the GEMV kernel per row
+// up to 3 activation rows, the tcgen05 kernel up to 8, the mma.sync kernel beyond and for the MoE
+// feed-forward), 2 = tcgen05 + TMEM everywhere it applies, 1 = mma.sync, 0 = the CUDA-core dp4a kernel
+// (which also serves every other format). Process-wide, read per call.
+static std::atomic<int> g_tile_kind{3};
 int tile_kind() { return g_tile_kind.load(std::memory_order_relaxed); }
-int set_tile_kind(int k) { return k >= 0 && k <= 2 ? g_tile_kind.exchange(k) : g_tile_kind.load(); }
+int set_tile_kind(int k) { return k >= 0 && k <= 3 ? g_tile_kind.exchange(k) : g_tile_kind.load(); }
 
 // ---- router ----------------------------------------------------------------------
 // One warp per token; the E scores live in shared memory (src/KokkosDNN_MoE.hpp:
@@ -603,7 +605,8 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
   const int n_slots = static_cast<int>(T * S);
   const bool all_q4k = gate->ggml_type == KDNN_GGML_Q4_K && down->ggml_type == KDNN_GGML_Q4_K &&
                        (reinterpret_cast<uintptr_t>(ws) & 15u) == 0;
-  const int kind = !all_q4k ? 0 : (tile_kind() == 2 && !tc_covers(gate, up, down)) ? 1 : tile_kind();
+  const int want = tile_kind() == 3 ? 1 : tile_kind();   // measured: the mma.sync kernel is the faster one here
+  const int kind = !all_q4k ? 0 : (want == 2 && !tc_covers(gate, up, down)) ? 1 : want;
   cudaError_t err;
   if (kind != 0 && moe_sort_smem(e_count, T) <= kPrepSmemLimit) {
     // one launch: slot sort (CTA 0) + row quantizer (the other CTAs)

@@ -5,19 +5,21 @@
 // pipeline between tiles, so the next tile's packed rows are already in flight
 // while the current tile is being folded.
 //
-//   warp 12      producer: per 256-element super-block of K one stage of the ring =
+//   warp 24      producer: per 256-element super-block of K one stage of the ring =
 //                128 packed rows x 144 bytes by tensor-map TMA (cp.async.bulk.tensor.2d,
-//                32-row boxes, this GPU's memory only, no multicast) + the group's
-//                quantized activation bytes and block scales by 1-D bulk copies
-//   warps 8-11   unpack: thread = weight row; nibbles -> int8 in the K-major core-matrix
+//                32-row boxes, this GPU's memory only, no multicast)
+//   warps 16-23  unpack: thread = (weight row, half of its sub-blocks); nibbles -> int8 in the K-major core-matrix
 //                layout the MMA reads (eight 128 x 32 A tiles per stage), the 6-bit scales
-//                and mins -> fp32 tables, activations -> eight 32 x 32 B tiles
-//   warp 13      one thread issues eight tcgen05.mma per stage (one per 32-element
+//                and mins -> fp32 tables; the group's quantized activations (a few KB per stage,
+//                L2 hits) come by plain loads one stage ahead -> eight 32 x 32 B tiles
+//   warp 25      one thread issues eight tcgen05.mma per stage (one per 32-element
 //                sub-block, each into its own 32-column TMEM slot: every sub-block has its
 //                own scale on both sides, so nothing accumulates across them in TMEM) and
 //                commits them to an mbarrier; two slot groups (2 x 256 columns) rotate
-//   warps 0-7    drain: thread = (weight row, half of the activation rows); tcgen05.ld of
-//                its TMEM lane, fold  acc += (d*sc) * dx * dot - (dmin*mn) * dx * sum  in
+//   warps 0-15   drain: thread = (weight row, half of the activation rows, half of the sub-blocks) --
+//                four warps per TMEM lane quadrant, because the fold is a chain of dependent FP32
+//                instructions that needs several warps per scheduler to issue at rate; tcgen05.ld
+//                of its TMEM lane, fold  acc += (d*sc) * dx * dot - (dmin*mn) * dx * sum  in
 //                fp32 registers while the other slot group is being filled, then the
 //                epilogue (SwiGLU + per-32 int8 quantization of the result for the
 //                gate/up call; plain stores otherwise)
@@ -39,12 +41,10 @@ namespace kdnn {
 constexpr int kTcNT       = 32;                 // activation rows per group (MMA N)
 constexpr int kTcBoxRows  = 32;                 // rows of one TMA box
 constexpr int kTcWStage   = 128 * 144;          // packed rows of one stage
-constexpr int kTcXq       = kTcNT * 256;        // int8 activations of one stage
-constexpr int kTcXs       = kTcNT * 64;         // {d, d * sum} of the stage's eight 32-blocks per row
-constexpr int kTcXStage   = kTcXq + kTcXs;
 constexpr int kTcATile    = 128 * 32;
 constexpr int kTcBTile    = kTcNT * 32;
-constexpr int kTcThreads  = 14 * 32;
+constexpr int kTcThreads  = 26 * 32;
+constexpr int kTcDrainWarps = 16, kTcUnpackWarp0 = 16, kTcWarpProducer = 24, kTcWarpMma = 25;
 constexpr uint32_t kTcCols = 512;               // TMEM columns: 2 slot groups x 8 slots x 32
 
 struct alignas(64) TcParams {
@@ -69,17 +69,18 @@ struct alignas(64) TcParams {
   int32_t* dots;              // debug/parity: when set, raw int32 sub-block dots [pos][N][K/32] are stored too
 };
 
+
 template <int MODE>
 struct TcLayout {
-  static constexpr int kStages = MODE == 1 ? 3 : 4;
+  static constexpr int kStages = MODE == 1 ? 5 : 6;   // as many as fit next to the other buffers
   static constexpr uint32_t w    = 0;
-  static constexpr uint32_t x    = w + kStages * kTcWStage;
-  static constexpr uint32_t a    = x + kStages * kTcXStage;
+  static constexpr uint32_t a    = w + kStages * kTcWStage;
   static constexpr uint32_t b    = a + 2 * 8 * kTcATile;
-  static constexpr uint32_t ws   = b + 2 * 8 * kTcBTile;          // [2][16][128] float: d*sc of 8 sub-blocks, dmin*mn of 8
-  static constexpr uint32_t dx   = ws + 2 * 16 * 128 * 4;         // [2][16][32] float: dx of 8 blocks, dx*sum of 8
-  static constexpr uint32_t ex   = dx + 2 * 16 * kTcNT * 4;       // MODE 1: [2][2 halves][2 warps][16][32] float
-  static constexpr uint32_t bar  = ex + (MODE == 1 ? 2 * 2048 * 4 : 0);
+  static constexpr uint32_t ws   = b + 2 * 8 * kTcBTile;          // [2][2 sub-block halves][sw, mw][128 rows][4] float: d*sc, dmin*mn
+  static constexpr uint32_t dx   = ws + 2 * 2 * 2 * 128 * 16;     // [2][16][32] float: dx of 8 blocks, dx*sum of 8
+  static constexpr uint32_t red  = dx + 2 * 16 * kTcNT * 4;       // [4 quadrants][2 column halves][16][32] float: partial sums of sub-blocks 4-7
+  static constexpr uint32_t ex   = red + 4 * 2 * 16 * 32 * 4;     // MODE 1: [2 column halves][2 warps][16][32] float: the up rows' sums
+  static constexpr uint32_t bar  = ex + (MODE == 1 ? 2048 * 4 : 0);
   static constexpr uint32_t total = bar + 256 + 128;              // + slack for the 128-byte alignment of the base
 };
 
@@ -115,10 +116,9 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint6
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_ld8(uint32_t taddr, int (&v)[16], int o) {
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, int (&v)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(v[o + 0]), "=r"(v[o + 1]), "=r"(v[o + 2]), "=r"(v[o + 3]), "=r"(v[o + 4]), "=r"(v[o + 5]),
-                 "=r"(v[o + 6]), "=r"(v[o + 7])
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                : "r"(taddr));
 }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, int (&v)[16]) {
@@ -148,6 +148,73 @@ __device__ __forceinline__ float4 lds128f(uint32_t a) {
   return v;
 }
 
+// One sub-block of one TMEM lane, already in registers, folded into the thread's accumulators:
+//   acc[c] += sw * (float(D[c]) * dx[c]) - mw * dxs[c],  c < 8 * NC8.
+template <int NC8>
+__device__ __forceinline__ void tc_fold(float (&acc)[16], const int (&d)[8 * NC8], float sw, float mw, uint32_t dxs) {
+  // all of the sub-block's activation scales first (one shared-memory round trip, not one per use)
+  float4 a[2 * NC8], m[2 * NC8];
+#pragma unroll
+  for (int v = 0; v < 2 * NC8; ++v) {
+    a[v] = lds128f(dxs + 16 * v);
+    m[v] = lds128f(dxs + 8 * kTcNT * 4 + 16 * v);
+  }
+  const float2 sw2 = make_float2(sw, sw), nmw2 = make_float2(-mw, -mw);
+  const float2 nmagic = make_float2(-kM2MagicF, -kM2MagicF);
+#pragma unroll
+  for (int v = 0; v < 2 * NC8; ++v) {
+    // int -> float on the integer and FP32 pipes (no conversion instruction): for |i| < 2^22 the bits of
+    // i + 0x4B400000 are the float 12582912 + i, one exact subtraction gives float(i); a sub-block dot is
+    // at most 32 * 15 * 127 in magnitude. (Presetting the TMEM slots to that constant and letting the MMA
+    // accumulate onto it saves the integer add but costs a tcgen05.st per slot and use: measured slower.)
+    const float2 f0 = fadd2(make_float2(__int_as_float(d[4 * v] + kM2MagicI), __int_as_float(d[4 * v + 1] + kM2MagicI)), nmagic);
+    const float2 f1 = fadd2(make_float2(__int_as_float(d[4 * v + 2] + kM2MagicI), __int_as_float(d[4 * v + 3] + kM2MagicI)), nmagic);
+    const float2 p0 = fmul2(f0, make_float2(a[v].x, a[v].y));
+    const float2 p1 = fmul2(f1, make_float2(a[v].z, a[v].w));
+    float2 r = ffma2(sw2, p0, make_float2(acc[4 * v], acc[4 * v + 1]));
+    r = ffma2(nmw2, make_float2(m[v].x, m[v].y), r);
+    acc[4 * v] = r.x; acc[4 * v + 1] = r.y;
+    r = ffma2(sw2, p1, make_float2(acc[4 * v + 2], acc[4 * v + 3]));
+    r = ffma2(nmw2, make_float2(m[v].z, m[v].w), r);
+    acc[4 * v + 2] = r.x; acc[4 * v + 3] = r.y;
+  }
+}
+
+// Four sub-block slots of one TMEM lane: the loads come first and the slot group is handed back to the MMA
+// warp (`t_empty_bar`) as soon as the values are in registers -- the arithmetic then overlaps the next MMAs
+// into the same slots. Eight columns per thread: all four slots at once (32 registers); sixteen: two and two.
+// `taddr` / `dxb` already point at the first of the four sub-blocks.
+template <int NC8>
+__device__ __forceinline__ void tc_drain_half(float (&acc)[16], uint32_t taddr, const float (&sws)[4], const float (&mws)[4],
+                                              uint32_t dxb, uint32_t t_empty_bar, int lane) {
+  if (NC8 == 1) {
+    int d[4][8];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) tc_ld8(taddr + g * kTcNT, d[g]);
+    tc_wait_ld();
+    tc_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(t_empty_bar);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) tc_fold<1>(acc, d[g], sws[g], mws[g], dxb + g * kTcNT * 4);
+  } else {
+    int d[2][16];
+    tc_ld16(taddr, d[0]);
+    tc_ld16(taddr + kTcNT, d[1]);
+    tc_wait_ld();
+    tc_fold<2>(acc, d[0], sws[0], mws[0], dxb);
+    tc_fold<2>(acc, d[1], sws[1], mws[1], dxb + kTcNT * 4);
+    tc_ld16(taddr + 2 * kTcNT, d[0]);
+    tc_ld16(taddr + 3 * kTcNT, d[1]);
+    tc_wait_ld();
+    tc_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(t_empty_bar);
+    tc_fold<2>(acc, d[0], sws[2], mws[2], dxb + 2 * kTcNT * 4);
+    tc_fold<2>(acc, d[1], sws[3], mws[3], dxb + 3 * kTcNT * 4);
+  }
+}
+
 // MODE 0: dst[pos, j]  = W0[j,:] . q(x[pos,:])                        (down projection)
 // MODE 1: act[pos, j]  = Scalar(silu(W0 . q(x)) * (W1 . q(x)))        (gate / up + SwiGLU; quantized when qdst is set)
 // MODE 2: dst[row, j]  = YT(W0[j,:] . q(x[row,:]))                    (plain batched GEMM)
@@ -160,34 +227,41 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
   uint8_t* smem = tc_smem_raw + (base - smem_u32(tc_smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // barriers: w_full[4], w_empty[4], a_full[2], mma_done[2], t_empty[2], ex_full[2]
+  // barriers: w_full[8], w_empty[8], a_full[2], mma_done[2], t_empty[2], red_full, red_empty, ex_full, ex_empty, s_free[2]
   const uint32_t bars = base + L::bar;
   auto w_full   = [&](int s) { return bars + 8u * s; };
-  auto w_empty  = [&](int s) { return bars + 32u + 8u * s; };
-  auto a_full   = [&](int b) { return bars + 64u + 8u * b; };
-  auto mma_done = [&](int b) { return bars + 80u + 8u * b; };
-  auto t_empty  = [&](int b) { return bars + 96u + 8u * b; };
-  auto ex_full  = [&](int b) { return bars + 112u + 8u * b; };
-  uint32_t* tmem_slot      = reinterpret_cast<uint32_t*>(smem + L::bar + 128);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::bar + 132);
+  auto w_empty  = [&](int s) { return bars + 64u + 8u * s; };
+  auto a_full   = [&](int b) { return bars + 128u + 8u * b; };
+  auto mma_done = [&](int b) { return bars + 144u + 8u * b; };
+  auto t_empty  = [&](int b) { return bars + 160u + 8u * b; };
+  const uint32_t red_full = bars + 176u, red_empty = bars + 184u, ex_full = bars + 192u, ex_empty = bars + 200u;
+  auto s_free   = [&](int b) { return bars + 208u + 8u * b; };
+  uint32_t* tmem_slot      = reinterpret_cast<uint32_t*>(smem + L::bar + 224);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::bar + 228);
 
-  if (warp == 13) {
+  if (warp == kTcWarpMma) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"(kTcCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 4; ++s) {
+    // one arrival per WARP on the barriers several warps feed (lane 0, after __syncwarp): hundreds of
+    // per-thread arrivals on one shared-memory word serialise
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(w_full(s), 1);
-      mbar_init(w_empty(s), 128);
+      mbar_init(w_empty(s), 8);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(a_full(b), 128);
+      mbar_init(a_full(b), 8);
       mbar_init(mma_done(b), 1);
-      mbar_init(t_empty(b), 256);
-      mbar_init(ex_full(b), 128);
+      mbar_init(t_empty(b), kTcDrainWarps);
+      mbar_init(s_free(b), kTcDrainWarps);
     }
+    mbar_init(red_full, 8);
+    mbar_init(red_empty, 8);
+    mbar_init(ex_full, 4);
+    mbar_init(ex_empty, 4);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -203,7 +277,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
   // another role of this CTA has already given up.
   auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
     for (uint32_t i = 0; i < (1u << 21); ++i) {
-      if (mbar_try_wait(bar, parity)) return true;
+      if (mbar_try_wait(bar, parity)) {
+        return true;
+      }
       if ((i & 31u) == 31u && *abort_flag) return false;
     }
     *abort_flag = 1;
@@ -215,34 +291,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
   const int nks         = p.K / 256;
   bool ok = true;
 
-  if (warp == 12) {
-    // ------------------------------------------------------------------ producer
-    const size_t scale_off = act_bytes(static_cast<size_t>(p.K));
-    uint32_t seq = 0;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const int g = t / p.row_tiles, rb = t - g * p.row_tiles;
-      const int4 gi = __ldg(p.groups + g);
-      const CUtensorMap* m0 = p.maps0 ? p.maps0 + gi.x : &p.one;
-      const CUtensorMap* m1 = MODE == 1 ? p.maps1 + gi.x : m0;
-      if (lane == 0 && p.maps0) {
-        tensormap_acquire(m0);
-        if (MODE == 1) tensormap_acquire(m1);
-      }
-      const int r0 = rb * p.tile_rows;
-      const int nbox = MODE == 1 ? 4 : (min(p.tile_rows, p.N - r0) + kTcBoxRows - 1) / kTcBoxRows;
-      const uint8_t* xrow = nullptr;
-      if (lane < gi.z) {
-        const int srow = MODE == 0 ? gi.y + lane : __ldg(p.list + gi.y + lane) / p.S;
-        xrow = p.xrows + static_cast<size_t>(srow) * p.x_pitch;
-      }
-      for (int ks = 0; ks < nks; ++ks, ++seq) {
-        const int s = static_cast<int>(seq % kStages);
-        const uint32_t use = seq / kStages;
-        if (!wait(w_empty(s), (use & 1u) ^ 1u)) { ok = false; break; }
-        const uint32_t bar = w_full(s);
-        const uint32_t wdst = base + L::w + s * kTcWStage, xdst = base + L::x + s * kTcXStage;
-        if (lane == 0) {
-          mbar_expect_tx(bar, static_cast<uint32_t>(nbox) * (kTcBoxRows * 144) + static_cast<uint32_t>(gi.z) * 320u);
+  if (warp == kTcWarpProducer) {
+    // ------------------------------------------------------------------ producer (one thread)
+    if (lane == 0) {
+      uint32_t seq = 0;
+      int e_next = blockIdx.x < total_tiles ? __ldg(p.groups + blockIdx.x / p.row_tiles).x : 0;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int g = t / p.row_tiles, rb = t - g * p.row_tiles;
+        const int e = e_next;   // requested a tile ago
+        if (t + static_cast<int>(gridDim.x) < total_tiles) e_next = __ldg(p.groups + (t + gridDim.x) / p.row_tiles).x;
+        const CUtensorMap* m0 = p.maps0 ? p.maps0 + e : &p.one;
+        const CUtensorMap* m1 = MODE == 1 ? p.maps1 + e : m0;
+        if (p.maps0) {
+          tensormap_acquire(m0);
+          if (MODE == 1) tensormap_acquire(m1);
+        }
+        const int r0 = rb * p.tile_rows;
+        const int nbox = MODE == 1 ? 4 : (min(p.tile_rows, p.N - r0) + kTcBoxRows - 1) / kTcBoxRows;
+        for (int ks = 0; ks < nks; ++ks, ++seq) {
+          const int s = static_cast<int>(seq % kStages);
+          const uint32_t use = seq / kStages;
+          if (!wait(w_empty(s), (use & 1u) ^ 1u)) { ok = false; break; }
+          const uint32_t bar = w_full(s);
+          const uint32_t wdst = base + L::w + s * kTcWStage;
+          mbar_expect_tx(bar, static_cast<uint32_t>(nbox) * (kTcBoxRows * 144));
           if (MODE == 1) {
             tma_load_2d(wdst, m0, ks * 144, r0, bar);
             tma_load_2d(wdst + 4608, m0, ks * 144, r0 + 32, bar);
@@ -252,87 +324,144 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
             for (int bx = 0; bx < nbox; ++bx) tma_load_2d(wdst + bx * 4608, m0, ks * 144, r0 + bx * kTcBoxRows, bar);
           }
         }
-        __syncwarp();
-        if (xrow) {
-          bulk_g2s(xdst + lane * 256, xrow + static_cast<size_t>(ks) * 256, 256, bar);
-          bulk_g2s(xdst + kTcXq + lane * 64, xrow + scale_off + static_cast<size_t>(ks) * 64, 64, bar);
-        }
+      }
+      if (!ok || *abort_flag) {
+        // copies of the last stages may still be in flight: give them time to land before the CTA's
+        // shared memory is handed to somebody else (bounded, the result of the launch is void anyway)
+        for (int s = 0; s < kStages; ++s)
+          for (uint32_t i = 0; i < (1u << 16); ++i)
+            if (mbar_try_wait(w_full(s), 0u) || mbar_try_wait(w_full(s), 1u)) break;
       }
     }
-    if (!ok || *abort_flag) {
-      // copies of the last stages may still be in flight: give them time to land before the CTA's
-      // shared memory is handed to somebody else (bounded, the result of the launch is void anyway)
-      for (int s = 0; s < kStages; ++s)
-        for (uint32_t i = 0; i < (1u << 16); ++i)
-          if (mbar_try_wait(w_full(s), 0u) || mbar_try_wait(w_full(s), 1u)) break;
-    }
-  } else if (warp >= 8 && warp < 12) {
+  } else if (warp >= kTcUnpackWarp0 && warp < kTcUnpackWarp0 + 8) {
     // ------------------------------------------------------------------ unpack
-    const int u = threadIdx.x - 256;
-    uint32_t seq = 0;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const int g = t / p.row_tiles;
-      const int ntok = __ldg(p.groups + g).z;
-      for (int ks = 0; ks < nks; ++ks, ++seq) {
-        const int s = static_cast<int>(seq % kStages);
-        const uint32_t use = seq / kStages;
-        const int b = seq & 1u;
-        const uint32_t j = seq >> 1;
-        if (!wait(w_full(s), use & 1u) || !wait(mma_done(b), (j & 1u) ^ 1u) || !wait(t_empty(b), (j & 1u) ^ 1u)) {
-          ok = false;
-          break;
-        }
-        const uint32_t mine = base + L::w + s * kTcWStage + u * 144;
-        const int4 hdr = lds128_g(mine);
+    // thread = (weight row u of the tile, half uh of its nibble groups) for the weights; for the group's
+    // activations it owns two 16-byte pieces (rows ut / 16 and ut / 16 + 16, piece ut % 16 of the stage's
+    // 256 bytes) and one {d, d * sum} pair (row ut / 8, block ut % 8), fetched from global memory (L2) with
+    // plain loads ONE STAGE AHEAD into registers: bulk copies of a few hundred bytes cost the copy engine
+    // about as much as a 4 KB box each.
+    const int ut = threadIdx.x - kTcUnpackWarp0 * 32;
+    const int u = ut & 127, uh = ut >> 7;
+    const size_t scale_off = act_bytes(static_cast<size_t>(p.K));
+    // Metadata runs two tiles ahead so that no load waits for another load on the way: the group record of
+    // tile i + 2 is requested when tile i is entered, the row ids of tile i + 1 (which need its group record,
+    // here since a tile ago) at the same moment, and the pieces of stage s + 1 while stage s is unpacked.
+    struct Rows { const uint8_t* r0; const uint8_t* r1; const uint8_t* rs; };   // null past the group's rows
+    const int xn = ((ut >> 7) << 3) | (ut & 7), xc16 = (ut >> 3) & 15;   // this thread's pieces: rows xn, xn + 16, 16-byte piece xc16
+    auto group_of = [&](int t) { return t < total_tiles ? __ldg(p.groups + t / p.row_tiles) : make_int4(0, 0, 0, 0); };
+    auto rows_of = [&](const int4& gi) {
+      auto row_of = [&](int n) -> const uint8_t* {
+        if (n >= gi.z) return nullptr;
+        const int srow = MODE == 0 ? gi.y + n : __ldg(p.list + gi.y + n) / p.S;
+        return p.xrows + static_cast<size_t>(srow) * p.x_pitch;
+      };
+      return Rows{row_of(xn), row_of(xn + 16), row_of(ut & 31)};
+    };
+    // (piece mapping chosen for the STORES: eight consecutive lanes fill one 128-byte core matrix of a
+    // B tile, 32 consecutive lanes fill 32 consecutive scale words -- no bank conflicts)
+    struct Pieces { int4 x0, x1; uint2 sv; };
+    int f_t = blockIdx.x, f_ks = 0;                 // fetch cursor: the stage whose pieces are requested next
+    int4 gi2 = group_of(f_t + 2 * gridDim.x);
+    Rows rows0 = rows_of(group_of(f_t)), rows1 = rows_of(group_of(f_t + gridDim.x));
+    auto fetch = [&](Pieces& f) {
+      f.x0 = f.x1 = make_int4(0, 0, 0, 0);
+      f.sv = make_uint2(0u, 0u);
+      if (f_t < total_tiles) {
+        const size_t ko = static_cast<size_t>(f_ks) * 256 + xc16 * 16;
+        if (rows0.r0) f.x0 = ldg128(rows0.r0 + ko);
+        if (rows0.r1) f.x1 = ldg128(rows0.r1 + ko);
+        if (rows0.rs) f.sv = __ldg(reinterpret_cast<const uint2*>(rows0.rs + scale_off + static_cast<size_t>(f_ks) * 64 + (ut >> 5) * 8));
+      }
+      if (++f_ks == nks) {   // the cursor enters the next tile
+        f_ks = 0;
+        f_t += gridDim.x;
+        rows0 = rows1;
+        rows1 = rows_of(gi2);
+        gi2 = group_of(f_t + 2 * gridDim.x);
+      }
+    };
+    auto stage = [&](uint32_t seq, const Pieces& have) -> bool {
+      const int s = static_cast<int>(seq % kStages);
+      const uint32_t use = seq / kStages;
+      const int b = seq & 1u;
+      const uint32_t j = seq >> 1;
+      bool okw = wait(w_full(s), use & 1u);
+      okw = okw && wait(mma_done(b), (j & 1u) ^ 1u);
+      if (!okw) return false;
+      const uint32_t mine = base + L::w + s * kTcWStage + u * 144;
+      const int4 hdr = lds128_g(mine);
+      int4 qa[2], qb[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        qa[i] = lds128_g(mine + 16 + (2 * uh + i) * 32);
+        qb[i] = lds128_g(mine + 32 + (2 * uh + i) * 32);
+      }
+      const uint32_t abase = base + L::a + b * (8 * kTcATile) + (u >> 3) * 256 + (u & 7) * 16;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int it = 2 * uh + i;
+        // sub-block 2*it: low nibbles, 2*it+1: high nibbles; K bytes 0-15 then 16-31
+        const int4 a4 = qa[i], b4 = qb[i];
+        const int4 lo0 = make_int4(a4.x & 0x0F0F0F0F, a4.y & 0x0F0F0F0F, a4.z & 0x0F0F0F0F, a4.w & 0x0F0F0F0F);
+        const int4 lo1 = make_int4(b4.x & 0x0F0F0F0F, b4.y & 0x0F0F0F0F, b4.z & 0x0F0F0F0F, b4.w & 0x0F0F0F0F);
+        const int4 hi0 = make_int4((a4.x >> 4) & 0x0F0F0F0F, (a4.y >> 4) & 0x0F0F0F0F, (a4.z >> 4) & 0x0F0F0F0F,
+                                   (a4.w >> 4) & 0x0F0F0F0F);
+        const int4 hi1 = make_int4((b4.x >> 4) & 0x0F0F0F0F, (b4.y >> 4) & 0x0F0F0F0F, (b4.z >> 4) & 0x0F0F0F0F,
+                                   (b4.w >> 4) & 0x0F0F0F0F);
+        sts128(abase + (2 * it) * kTcATile, lo0);
+        sts128(abase + (2 * it) * kTcATile + 128, lo1);
+        sts128(abase + (2 * it + 1) * kTcATile, hi0);
+        sts128(abase + (2 * it + 1) * kTcATile + 128, hi1);
+      }
+      // activations of the group (rows past its end are zeros): two pieces -> the B tile of their sub-block
+      const uint32_t bdst = base + L::b + b * (8 * kTcBTile) + (xc16 >> 1) * kTcBTile + (xc16 & 1) * 128;
+      sts128(bdst + (xn >> 3) * 256 + (xn & 7) * 16, have.x0);
+      sts128(bdst + ((xn + 16) >> 3) * 256 + (xn & 7) * 16, have.x1);
+      // the scale tables of this buffer are free once the drain warps are through with stage seq - 2
+      if (!wait(s_free(b), (j & 1u) ^ 1u)) return false;
+      {  // d * sc and dmin * mn of this thread's four sub-blocks (6-bit integers -> float through the mantissa
+         // of 8388608.0f, no conversion instruction), 16 bytes per row and kind: conflict-free both ways
         const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));
-        const uint32_t wsb = base + L::ws + b * (16 * 128 * 4) + u * 4;
-        const uint32_t abase = base + L::a + b * (8 * kTcATile) + (u >> 3) * 256 + (u & 7) * 16;
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          uint32_t scp, mnp;
-          q4k_scale_pair(hdr.y, hdr.z, hdr.w, it, scp, mnp);
-          sts32f(wsb + (2 * it) * 512, dd.x * static_cast<float>(scp & 0xFF));
-          sts32f(wsb + (2 * it + 1) * 512, dd.x * static_cast<float>(scp >> 8));
-          sts32f(wsb + (8 + 2 * it) * 512, dd.y * static_cast<float>(mnp & 0xFF));
-          sts32f(wsb + (9 + 2 * it) * 512, dd.y * static_cast<float>(mnp >> 8));
-          const int4 qa = lds128_g(mine + 16 + it * 32), qb = lds128_g(mine + 32 + it * 32);
-          // sub-block 2*it: low nibbles, 2*it+1: high nibbles; K bytes 0-15 then 16-31
-          const int4 lo0 = make_int4(qa.x & 0x0F0F0F0F, qa.y & 0x0F0F0F0F, qa.z & 0x0F0F0F0F, qa.w & 0x0F0F0F0F);
-          const int4 lo1 = make_int4(qb.x & 0x0F0F0F0F, qb.y & 0x0F0F0F0F, qb.z & 0x0F0F0F0F, qb.w & 0x0F0F0F0F);
-          const int4 hi0 = make_int4((qa.x >> 4) & 0x0F0F0F0F, (qa.y >> 4) & 0x0F0F0F0F, (qa.z >> 4) & 0x0F0F0F0F,
-                                     (qa.w >> 4) & 0x0F0F0F0F);
-          const int4 hi1 = make_int4((qb.x >> 4) & 0x0F0F0F0F, (qb.y >> 4) & 0x0F0F0F0F, (qb.z >> 4) & 0x0F0F0F0F,
-                                     (qb.w >> 4) & 0x0F0F0F0F);
-          sts128(abase + (2 * it) * kTcATile, lo0);
-          sts128(abase + (2 * it) * kTcATile + 128, lo1);
-          sts128(abase + (2 * it + 1) * kTcATile, hi0);
-          sts128(abase + (2 * it + 1) * kTcATile + 128, hi1);
-        }
-        // activations of the group: 32 rows x 16 pieces of 16 bytes -> eight B tiles
-        const uint32_t xsrc = base + L::x + s * kTcXStage;
-        const uint32_t bdst = base + L::b + b * (8 * kTcBTile);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int pc = u + 128 * i, n = pc >> 4, c16 = pc & 15;
-          int4 v = make_int4(0, 0, 0, 0);
-          if (n < ntok) v = lds128_g(xsrc + n * 256 + c16 * 16);
-          sts128(bdst + (c16 >> 1) * kTcBTile + (n >> 3) * 256 + (c16 & 1) * 128 + (n & 7) * 16, v);
-        }
-        const uint32_t dxb = base + L::dx + b * (16 * kTcNT * 4);
+        float sw[4], mw[4];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-          const int f = u + 128 * i, n = f >> 3, jj = f & 7;
-          uint2 v = make_uint2(0u, 0u);
-          if (n < ntok) v = lds64_g(xsrc + kTcXq + n * 64 + jj * 8);
-          sts32f(dxb + (jj * kTcNT + n) * 4, __uint_as_float(v.x));
-          sts32f(dxb + ((8 + jj) * kTcNT + n) * 4, __uint_as_float(v.y));
+          uint32_t scp, mnp;
+          q4k_scale_pair(hdr.y, hdr.z, hdr.w, 2 * uh + i, scp, mnp);
+          sw[2 * i]     = dd.x * (__uint_as_float(0x4B000000u | (scp & 0xFFu)) - 8388608.0f);
+          sw[2 * i + 1] = dd.x * (__uint_as_float(0x4B000000u | (scp >> 8)) - 8388608.0f);
+          mw[2 * i]     = dd.y * (__uint_as_float(0x4B000000u | (mnp & 0xFFu)) - 8388608.0f);
+          mw[2 * i + 1] = dd.y * (__uint_as_float(0x4B000000u | (mnp >> 8)) - 8388608.0f);
         }
-        fence_proxy_async();   // generic-proxy writes (A, B tiles) -> async-proxy reads by the MMA
+        const uint32_t wsb = base + L::ws + ((b * 2 + uh) * 2 * 128 + u) * 16;
+        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(wsb), "f"(sw[0]), "f"(sw[1]), "f"(sw[2]), "f"(sw[3]) : "memory");
+        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(wsb + 128 * 16), "f"(mw[0]), "f"(mw[1]), "f"(mw[2]), "f"(mw[3]) : "memory");
+      }
+      const uint32_t dxb = base + L::dx + b * (16 * kTcNT * 4);
+      sts32f(dxb + ((ut >> 5) * kTcNT + (ut & 31)) * 4, __uint_as_float(have.sv.x));
+      sts32f(dxb + ((8 + (ut >> 5)) * kTcNT + (ut & 31)) * 4, __uint_as_float(have.sv.y));
+      fence_proxy_async();   // generic-proxy writes (A, B tiles) -> async-proxy reads by the MMA
+      __syncwarp();
+      if (lane == 0) {
         mbar_arrive(a_full(b));
         mbar_arrive(w_empty(s));
       }
+      return true;
+    };
+    const int my_tiles = blockIdx.x < total_tiles ? (total_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+    const uint32_t nstages = static_cast<uint32_t>(my_tiles) * nks;
+    // two stages per trip with the piece registers swapping roles, so that a stage's loads land in the
+    // registers they are used from (no register move has to wait for a load in flight)
+    Pieces pa, pb;
+    fetch(pa);
+    for (uint32_t seq = 0; seq < nstages && ok; seq += 2) {
+      fetch(pb);
+      ok = stage(seq, pa);
+      if (ok && seq + 1 < nstages) {
+        fetch(pa);
+        ok = stage(seq + 1, pb);
+      }
     }
-  } else if (warp == 13) {
+  } else if (warp == kTcWarpMma) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       uint32_t seq = 0;
@@ -340,7 +469,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
         for (int ks = 0; ks < nks; ++ks, ++seq) {
           const int b = seq & 1u;
           const uint32_t j = seq >> 1;
-          if (!wait(a_full(b), j & 1u)) { ok = false; break; }
+          if (!wait(a_full(b), j & 1u) || !wait(t_empty(b), (j & 1u) ^ 1u)) { ok = false; break; }
           tc_after();
           const uint32_t a0 = base + L::a + b * (8 * kTcATile), b0 = base + L::b + b * (8 * kTcBTile);
 #pragma unroll
@@ -352,14 +481,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
     }
   } else {
     // ------------------------------------------------------------------ drain + epilogue
-    const int q = warp & 3, hf = warp >> 2;
+    const int q = warp & 3, hf = (warp >> 2) & 1, sh = warp >> 3;   // lane quadrant, column half, sub-block half
     const int row = q * 32 + lane;
-    const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hf * 16;
+    const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + sh * (4 * kTcNT);
     uint32_t seq = 0, tile_no = 0;
+    int4 gi_next = blockIdx.x < total_tiles ? __ldg(p.groups + blockIdx.x / p.row_tiles) : make_int4(0, 0, 0, 0);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
       const int g = t / p.row_tiles, rb = t - g * p.row_tiles;
-      const int4 gi = __ldg(p.groups + g);
-      const int ncol = max(0, min(16, gi.z - 16 * hf));
+      const int4 gi = gi_next;   // requested a tile ago
+      if (t + static_cast<int>(gridDim.x) < total_tiles) gi_next = __ldg(p.groups + (t + gridDim.x) / p.row_tiles);
+      // the group's activation rows are split between the warps that share a TMEM lane quadrant:
+      // columns [0, h0) and [h0, n), h0 a multiple of 8
+      const int h0 = min(gi.z, (((gi.z + 1) >> 1) + 7) & ~7);
+      const int c0 = hf ? h0 : 0;
+      const int ncol = hf ? gi.z - h0 : h0;
       const int n8 = (ncol + 7) >> 3;
       const int r0 = rb * p.tile_rows;
       float acc[16];
@@ -368,72 +503,85 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
       for (int ks = 0; ks < nks; ++ks, ++seq) {
         const int b = seq & 1u;
         const uint32_t j = seq >> 1;
+        const int s = static_cast<int>(seq % kStages);
         if (!wait(a_full(b), j & 1u) || !wait(mma_done(b), j & 1u)) { ok = false; break; }
         tc_after();
-        if (n8 > 0) {
-          const uint32_t wsb = base + L::ws + b * (16 * 128 * 4) + row * 4;
-          const uint32_t dxb = base + L::dx + b * (16 * kTcNT * 4) + hf * 64;
-#pragma unroll
-          for (int s8 = 0; s8 < 8; ++s8) {
+        if (p.dots != nullptr && n8 > 0) {   // parity probe: the exact integer sub-block dots of the production MMAs, read before the slots are preset again
+          const int jrow = MODE == 1 ? (row < 64 ? r0 + row : -1) : (row < p.tile_rows ? r0 + row : -1);
+          for (int s4 = 0; s4 < 4; ++s4) {
             int d[16];
-            if (n8 == 2) tc_ld16(taddr0 + b * 256 + s8 * kTcNT, d);
-            else tc_ld8(taddr0 + b * 256 + s8 * kTcNT, d, 0);
+            tc_ld16(taddr0 + b * 256 + c0 + s4 * kTcNT, d);   // columns past the group's rows are read but not stored
             tc_wait_ld();
-            const float sw = lds32f(wsb + s8 * 512), mw = lds32f(wsb + (8 + s8) * 512);
-            if (p.dots != nullptr) {   // parity probe: the exact integer sub-block dots of the production MMAs
-              const int jrow = MODE == 1 ? (row < 64 ? r0 + row : -1) : (row < p.tile_rows ? r0 + row : -1);
-              if (jrow >= 0 && jrow < p.N) {
+            if (jrow >= 0 && jrow < p.N) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c)
-                  if (c < ncol)
-                    p.dots[(static_cast<size_t>(gi.y + 16 * hf + c) * p.N + jrow) * (p.K / 32) + ks * 8 + s8] = d[c];
-              }
-            }
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (v < 2 * n8) {
-                const float4 a = lds128f(dxb + (s8 * kTcNT + 4 * v) * 4);
-                const float4 m = lds128f(dxb + ((8 + s8) * kTcNT + 4 * v) * 4);
-                const float2 sw2 = make_float2(sw, sw), nmw2 = make_float2(-mw, -mw);
-                const float2 p0 = fmul2(make_float2(static_cast<float>(d[4 * v]), static_cast<float>(d[4 * v + 1])),
-                                        make_float2(a.x, a.y));
-                const float2 p1 = fmul2(make_float2(static_cast<float>(d[4 * v + 2]), static_cast<float>(d[4 * v + 3])),
-                                        make_float2(a.z, a.w));
-                float2 r = ffma2(sw2, p0, make_float2(acc[4 * v], acc[4 * v + 1]));
-                r = ffma2(nmw2, make_float2(m.x, m.y), r);
-                acc[4 * v] = r.x; acc[4 * v + 1] = r.y;
-                r = ffma2(sw2, p1, make_float2(acc[4 * v + 2], acc[4 * v + 3]));
-                r = ffma2(nmw2, make_float2(m.z, m.w), r);
-                acc[4 * v + 2] = r.x; acc[4 * v + 3] = r.y;
-              }
+              for (int c = 0; c < 16; ++c)
+                if (c < ncol)
+                  p.dots[(static_cast<size_t>(gi.y + c0 + c) * p.N + jrow) * (p.K / 32) + ks * 8 + sh * 4 + s4] = d[c];
             }
           }
         }
-        tc_before();
-        mbar_arrive(t_empty(b));
+        const uint32_t wsb = base + L::ws + ((b * 2 + sh) * 2 * 128 + row) * 16;
+        const float4 swv = lds128f(wsb), mwv = lds128f(wsb + 128 * 16);
+        const float sws[4] = {swv.x, swv.y, swv.z, swv.w}, mws[4] = {mwv.x, mwv.y, mwv.z, mwv.w};
+        const uint32_t slot0 = taddr0 + b * 256;
+        const uint32_t taddr = slot0 + c0;
+        const uint32_t dxb = base + L::dx + b * (16 * kTcNT * 4) + (sh * 4 * kTcNT + c0) * 4;
+        if (n8 == 1) {
+          tc_drain_half<1>(acc, taddr, sws, mws, dxb, t_empty(b), lane);
+        } else if (n8 == 2) {
+          tc_drain_half<2>(acc, taddr, sws, mws, dxb, t_empty(b), lane);
+        } else {
+          tc_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(t_empty(b));
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free(b));   // done with this stage's scale tables
       }
       if (!ok) break;
-      // ---- epilogue of the tile ----
+      // ---- the two sub-block halves meet: warps of half 1 hand their sums to the warps of half 0 ----
+      {
+        const uint32_t rb_ = base + L::red + ((q * 2 + hf) * 16 * 32 + lane) * 4;
+        if (sh == 1) {
+          if (!wait(red_empty, (tile_no & 1u) ^ 1u)) { ok = false; break; }
+#pragma unroll
+          for (int c = 0; c < 16; ++c) sts32f(rb_ + c * 128, acc[c]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(red_full);
+          continue;
+        }
+        if (!wait(red_full, tile_no & 1u)) { ok = false; break; }
+#pragma unroll
+        for (int c = 0; c < 16; ++c) acc[c] += lds32f(rb_ + c * 128);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(red_empty);
+      }
+      // ---- epilogue of the tile (warps of sub-block half 0) ----
       if (MODE == 1) {
-        const int tp = tile_no & 1u;
-        const uint32_t exb = base + L::ex + tp * 8192 + ((hf * 2 + (q & 1)) * 16 * 32 + lane) * 4;
+        const uint32_t exb = base + L::ex + ((hf * 2 + (q & 1)) * 16 * 32 + lane) * 4;
         if (q >= 2) {
+          if (!wait(ex_empty, (tile_no & 1u) ^ 1u)) { ok = false; break; }
 #pragma unroll
           for (int c = 0; c < 16; ++c) sts32f(exb + c * 128, acc[c]);
-          mbar_arrive(ex_full(tp));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(ex_full);
         } else {
-          if (!wait(ex_full(tp), (tile_no >> 1) & 1u)) { ok = false; break; }
+          if (!wait(ex_full, tile_no & 1u)) { ok = false; break; }
+          float upv[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) upv[c] = lds32f(exb + c * 128);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(ex_empty);
           const int jcol = r0 + row;          // row < 64: this thread's gate row
           const int blk = jcol >> 5;          // 32-block of the act row this warp's lanes form
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
             if (c < ncol) {                   // uniform across the warp
-              const float up = lds32f(exb + c * 128);
               float v = acc[c];
-              v = (v / (1.0f + expf(-v))) * up;
+              v = (v / (1.0f + expf(-v))) * upv[c];
               if (p.round_bf16) v = __bfloat162float(__float2bfloat16_rn(v));
               if (jcol >= p.N) v = 0.f;
-              const size_t ps = static_cast<size_t>(gi.y + 16 * hf + c);
+              const size_t ps = static_cast<size_t>(gi.y + c0 + c);
               if (p.qdst != nullptr) {
                 // the reference's stage-1 quantizer on the 32 values the warp holds (one whole block)
                 float amax = fabsf(v);
@@ -471,7 +619,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
             if (c < ncol) {
-              const int ps = gi.y + 16 * hf + c;
+              const int ps = gi.y + c0 + c;
               if (MODE == 2) {
                 const int srow = __ldg(p.list + ps) / p.S;
                 store_scalar(static_cast<YT*>(p.dst) + static_cast<size_t>(srow) * p.ld_dst + jrow, acc[c]);
@@ -487,7 +635,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
   if (!ok && lane == 0) atomicExch(p.status, KDNN_ERR_DEVICE_WAIT);
   tc_before();
   __syncthreads();
-  if (warp == 13)
+  if (warp == kTcWarpMma)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTcCols) : "memory");
 }
 

@@ -180,9 +180,11 @@ int kdnn_b200_quant_gemm_dots(uint32_t ggml_type, const void* w, size_t N, size_
                               void* Y, size_t ldy, int y_scalar, int32_t* dots,
                               void* workspace, size_t workspace_bytes, void* stream);
 
-/* Which tile kernel the batched Q4_K calls (quant_gemm, moe_ffn, moe_block) use from now on, process-wide:
- * 2 = tcgen05.mma + TMEM, fed by tensor-map TMA (the default), 1 = mma.sync m16n8k32, 0 = the CUDA-core
- * dp4a kernel that serves every other format. Returns the previous kind; kind < 0 only queries.
+/* Which kernel the batched Q4_K calls (quant_gemm, moe_ffn, moe_block) use from now on, process-wide:
+ * 3 = by measured crossover (the default: quant_gemm runs the GEMV kernel per row up to 3 activation rows,
+ * the tcgen05 kernel up to 8, the mma.sync kernel beyond; the MoE feed-forward runs the mma.sync kernel),
+ * 2 = tcgen05.mma + TMEM fed by tensor-map TMA wherever it applies, 1 = mma.sync m16n8k32, 0 = the
+ * CUDA-core dp4a kernel that serves every other format. Returns the previous kind; kind < 0 only queries.
  * A tuning knob in the sense of Int8Layout (src/KokkosDNN_GGUFGemvInt8.hpp:604-608); results agree
  * within fp32 summation order. */
 int kdnn_b200_tile_kind(int kind);

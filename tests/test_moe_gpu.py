@@ -13,8 +13,8 @@ from oracle import oracle as O
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 DEV = "cuda:0"
-TILE_KINDS = [2, 1, 0]        # tcgen05 + TMEM (default), mma.sync, CUDA-core dp4a
-TILE_NAMES = {2: "tcgen05", 1: "mma.sync", 0: "dp4a"}
+TILE_KINDS = [3, 2, 1, 0]     # by measured crossover (default), tcgen05 + TMEM, mma.sync, CUDA-core dp4a
+TILE_NAMES = {3: "auto", 2: "tcgen05", 1: "mma.sync", 0: "dp4a"}
 
 
 @pytest.fixture(params=TILE_KINDS, ids=lambda k: TILE_NAMES[k])
@@ -25,7 +25,7 @@ def tile(kd, request):
     kd.tile_kind(prev)
 
 
-@pytest.fixture(params=[2, 1], ids=lambda k: TILE_NAMES[k])
+@pytest.fixture(params=[3, 2, 1], ids=lambda k: TILE_NAMES[k])
 def tensor_tile(kd, request):
     prev = kd.tile_kind(request.param)
     yield request.param
@@ -108,7 +108,7 @@ def _ffn(kd, X_t, tabs, idx, wts, y_dtype, e_first=0, e_count=None):
                                     (O.Q6_K, O.Q6_K, O.Q4_K)])
 @pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
 def test_moe_ffn_small(kd, port, dtypes, x_dtype, tile):
-    if dtypes != (O.Q4_K, O.Q4_K, O.Q4_K) and tile != 2:
+    if dtypes != (O.Q4_K, O.Q4_K, O.Q4_K) and tile != 3:
         pytest.skip("the tile kind only matters for all-Q4_K experts")
     E, H, F, T, S = 6, 512, 256, 21, 3
     gate, up, down = _experts(kd, E, H, F, 40, dtypes)
@@ -183,7 +183,7 @@ def test_moe_ffn_q5k_experts(kd, port, dtypes):
 @pytest.mark.parametrize("dtype,N,K", [(O.Q4_K, 300, 1024), (O.Q6_K, 130, 2048), (O.Q8_0, 257, 512), (O.Q5_K, 200, 1024)])
 @pytest.mark.parametrize("M", [1, 2, 3, 5, 16, 17, 32, 33, 70])
 def test_quant_gemm_rows_equal_gemv(kd, port, dtype, N, K, M, tile):
-    if dtype != O.Q4_K and tile != 2:
+    if dtype != O.Q4_K and tile not in (3, 0):
         pytest.skip("the tile kind only matters for Q4_K")
     packed = kd.ggml_pack.random_payload(dtype, N, K, N + K)
     w = kd.QuantWeight.from_numpy(packed, dtype, N, K, DEV)
