@@ -39,6 +39,10 @@ EXPORTS = [
     "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quant_gemv_ex", "kdnn_b200_quant_gemv_noalloc",
     "kdnn_b200_quant_gemv_noalloc_ex", "kdnn_b200_quantize_act_q8", "kdnn_b200_quant_gemm_dots", "kdnn_b200_tile_kind",
     "kdnn_b200_weight_table_tma_bytes", "kdnn_b200_weight_table_tma_encode",
+    "kdnn_b200_moe_exchange_bytes", "kdnn_b200_moe_block_workspace_bytes", "kdnn_b200_moe_block",
+    "kdnn_b200_moe_block_routing", "kdnn_b200_peer_alloc", "kdnn_b200_peer_open", "kdnn_b200_peer_close",
+    "kdnn_b200_peer_free", "kdnn_b200_swiglu", "kdnn_b200_moe_expert_weighted_sum", "kdnn_b200_moe_gather_rows",
+    "kdnn_b200_moe_scatter_add_weighted", "kdnn_b200_read_probe",
     "kdnn_b200_unit_dots", "kdnn_b200_gemm_workspace_bytes", "kdnn_b200_quant_gemm",
     "kdnn_b200_moe_route", "kdnn_b200_moe_workspace_bytes", "kdnn_b200_moe_ffn",
     "kdnn_b200_residual_rmsnorm", "kdnn_b200_dequant_to_dense", "kdnn_b200_quant_gemv_fp",
@@ -61,6 +65,11 @@ class GemvLayoutC(C.Structure):
     """kdnn_b200_gemv_layout: optional tuning of one GEMV call (all zero = defaults)."""
     _fields_ = [("kernel", C.c_int), ("rows_per_group", C.c_int), ("stages", C.c_int),
                 ("early_stages", C.c_int), ("warps", C.c_int), ("no_pdl", C.c_int)]
+
+
+class MoeExchangeC(C.Structure):
+    _fields_ = [("rank", C.c_int), ("world", C.c_int), ("regions", C.POINTER(C.c_void_p)),
+                ("wait_ns", C.c_ulonglong)]
 
 
 KERNEL_AUTO, KERNEL_XREG, KERNEL_SMEM_WINDOW, KERNEL_ITEM_STREAM, KERNEL_PLAIN_LOADS = 0, 1, 2, 3, 4
@@ -120,6 +129,31 @@ def _load() -> C.CDLL:
                                             C.c_void_p, C.c_int, C.c_void_p]
     lib.kdnn_b200_dequant_to_dense.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                                C.c_size_t, C.c_int, C.c_void_p]
+    lib.kdnn_b200_moe_exchange_bytes.restype = C.c_size_t
+    lib.kdnn_b200_moe_exchange_bytes.argtypes = [C.c_size_t] * 4
+    lib.kdnn_b200_moe_block_workspace_bytes.restype = C.c_size_t
+    lib.kdnn_b200_moe_block_workspace_bytes.argtypes = [C.c_size_t] * 6 + [C.c_int]
+    lib.kdnn_b200_moe_block.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p,
+                                        C.c_int, C.c_int, C.c_float, C.c_int, C.POINTER(WeightTableC),
+                                        C.POINTER(WeightTableC), C.POINTER(WeightTableC), C.c_size_t, C.c_size_t,
+                                        C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t,
+                                        C.c_void_p, C.c_size_t, C.c_float, C.POINTER(MoeExchangeC), C.c_void_p,
+                                        C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_moe_block_routing.argtypes = [C.POINTER(MoeExchangeC), C.c_void_p] + [C.c_size_t] * 6 + \
+        [C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.kdnn_b200_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
+    lib.kdnn_b200_peer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    lib.kdnn_b200_peer_close.argtypes = [C.c_void_p]
+    lib.kdnn_b200_peer_free.argtypes = [C.c_void_p]
+    lib.kdnn_b200_swiglu.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t,
+                                     C.c_size_t, C.c_int, C.c_void_p]
+    lib.kdnn_b200_moe_expert_weighted_sum.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t,
+                                                      C.c_size_t, C.c_size_t, C.c_int, C.c_void_p]
+    lib.kdnn_b200_moe_gather_rows.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t,
+                                              C.c_size_t, C.c_size_t, C.c_int, C.c_void_p]
+    lib.kdnn_b200_moe_scatter_add_weighted.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                       C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_void_p]
+    lib.kdnn_b200_read_probe.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
     lib.kdnn_b200_residual_rmsnorm.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p,
                                                C.c_size_t, C.c_size_t, C.c_size_t, C.c_float, C.c_int, C.c_void_p]
     return lib
@@ -512,3 +546,146 @@ def residual_rmsnorm(h: torch.Tensor, y: torch.Tensor, out: torch.Tensor, eps: f
     rc = lib.kdnn_b200_residual_rmsnorm(h.data_ptr(), h.stride(0), y.data_ptr(), y.stride(0), out.data_ptr(),
                                         out.stride(0), T, H, float(eps), _scalar(h), _stream())
     _check(rc, "residual_rmsnorm")
+
+
+# ---------------------------------------------------------------------------
+# the reference's small MoE operators (src/KokkosDNN_SwiGLU.hpp, src/KokkosDNN_MoE.hpp:313-381)
+def swiglu(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = Scalar(silu(gate) * up) (KokkosDNN::swiglu, src/KokkosDNN_SwiGLU.hpp:24-38)."""
+    T, F = gate.shape
+    if tuple(up.shape) != (T, F) or tuple(out.shape) != (T, F) or up.dtype != gate.dtype or out.dtype != gate.dtype:
+        raise ValueError("swiglu: dimension mismatch")
+    rc = lib.kdnn_b200_swiglu(gate.data_ptr(), gate.stride(0), up.data_ptr(), up.stride(0), out.data_ptr(),
+                              out.stride(0), T, F, _scalar(gate), _stream())
+    _check(rc, "swiglu")
+
+
+def moe_expert_weighted_sum(expert_out: torch.Tensor, top_w: torch.Tensor, y: torch.Tensor) -> None:
+    """y[t,d] = sum_k top_w[t,k] * expert_out[t,k,d] (KokkosDNN::moe_expert_weighted_sum, src/KokkosDNN_MoE.hpp:313-332)."""
+    T, D = y.shape
+    K = top_w.shape[1]
+    if tuple(expert_out.shape) != (T, K, D) or top_w.shape[0] != T:
+        raise ValueError("moe_expert_weighted_sum: dimension mismatch")
+    if not expert_out.is_contiguous() or not top_w.is_contiguous() or top_w.dtype != torch.float32:
+        raise ValueError("moe_expert_weighted_sum: expert_out / top_w must be contiguous, top_w float32")
+    rc = lib.kdnn_b200_moe_expert_weighted_sum(expert_out.data_ptr(), top_w.data_ptr(), y.data_ptr(), y.stride(0), T, K,
+                                               D, _scalar(y), _stream())
+    _check(rc, "moe_expert_weighted_sum")
+
+
+def moe_gather_rows(src: torch.Tensor, rows: torch.Tensor, dst: torch.Tensor) -> None:
+    """dst[n,:] = src[rows[n],:] (KokkosDNN::moe_gather_rows, src/KokkosDNN_MoE.hpp:337-351)."""
+    N = rows.shape[0]
+    D = src.shape[1]
+    if dst.shape[0] != N or (N > 0 and dst.shape[1] != D):
+        raise ValueError("moe_gather_rows: dimension mismatch")
+    if rows.dtype != torch.int32 or dst.dtype != src.dtype:
+        raise ValueError("moe_gather_rows: rows must be int32, src and dst one Scalar")
+    rc = lib.kdnn_b200_moe_gather_rows(src.data_ptr(), src.stride(0), src.shape[0], rows.data_ptr(), dst.data_ptr(),
+                                       dst.stride(0) if N else D, N, D, _scalar(src), _stream())
+    _check(rc, "moe_gather_rows")
+
+
+def moe_scatter_add_weighted(src: torch.Tensor, rows: torch.Tensor, weights: torch.Tensor, dst: torch.Tensor) -> None:
+    """dst[rows[n],:] += weights[n] * src[n,:], rows unique (KokkosDNN::moe_scatter_add_weighted, src/KokkosDNN_MoE.hpp:360-381)."""
+    N = rows.shape[0]
+    C_, D = dst.shape
+    if src.shape[0] != N or weights.shape[0] != N or (N > 0 and src.shape[1] != D):
+        raise ValueError("moe_scatter_add_weighted: dimension mismatch")
+    if rows.dtype != torch.int32 or weights.dtype != torch.float32 or dst.dtype != src.dtype:
+        raise ValueError("moe_scatter_add_weighted: rows int32, weights float32, src and dst one Scalar")
+    rc = lib.kdnn_b200_moe_scatter_add_weighted(src.data_ptr(), src.stride(0) if N else D, rows.data_ptr(),
+                                                weights.data_ptr(), dst.data_ptr(), dst.stride(0), C_, N, D,
+                                                _scalar(dst), _stream())
+    _check(rc, "moe_scatter_add_weighted")
+
+
+# ---------------------------------------------------------------------------
+# the MoE block in four launches, single GPU or expert-parallel over peer memory
+class MoeExchange:
+    """Exchange regions of an expert-parallel group: this rank's region (peer-visible device memory) and the
+    peers' regions opened through IPC handles. ``handles`` is the list of every rank's 64-byte handle in rank
+    order (what ``all_gather`` of ``local_handle`` gives); the single-process form (``MoeExchange.local``) maps
+    plain device buffers and is what the tests use to stand in for peers that never answer."""
+
+    def __init__(self, rank: int, world: int, regions: Sequence[int], wait_ns: int = 0, owner=None):
+        self.rank, self.world, self.regions, self.wait_ns, self._owner = rank, world, list(regions), wait_ns, owner
+        self._arr = (C.c_void_p * world)(*self.regions)
+        self.c = MoeExchangeC(rank, world, self._arr, wait_ns)
+
+    @staticmethod
+    def region_bytes(tokens_local: int, world: int, top_k: int, H: int) -> int:
+        return int(lib.kdnn_b200_moe_exchange_bytes(tokens_local, world, top_k, H))
+
+    @staticmethod
+    def alloc(nbytes: int):
+        """(device pointer, 64-byte IPC handle) of a zeroed peer-visible allocation."""
+        ptr, handle = C.c_void_p(), (C.c_ubyte * 64)()
+        _check(lib.kdnn_b200_peer_alloc(nbytes, C.byref(ptr), handle), "peer_alloc")
+        return int(ptr.value), bytes(handle)
+
+    @staticmethod
+    def open(handle: bytes) -> int:
+        ptr, buf = C.c_void_p(), (C.c_ubyte * 64).from_buffer_copy(handle)
+        _check(lib.kdnn_b200_peer_open(buf, C.byref(ptr)), "peer_open")
+        return int(ptr.value)
+
+    @staticmethod
+    def local(rank: int, world: int, buffers: Sequence[torch.Tensor], wait_ns: int = 0) -> "MoeExchange":
+        return MoeExchange(rank, world, [b.data_ptr() for b in buffers], wait_ns, owner=tuple(buffers))
+
+
+def moe_block_workspace_bytes(tokens_local: int, world: int, top_k: int, H: int, F: int, n_experts: int,
+                              with_region: bool) -> int:
+    return int(lib.kdnn_b200_moe_block_workspace_bytes(tokens_local, world, top_k, H, F, n_experts, int(with_region)))
+
+
+def moe_block(x: torch.Tensor, router_w: torch.Tensor, router_bias: Optional[torch.Tensor], top_k: int, norm_topk: bool,
+              routed_scale: float, gate: QuantWeightTable, up: QuantWeightTable, down: QuantWeightTable,
+              workspace: torch.Tensor, y: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
+              h_out: Optional[torch.Tensor] = None, xn_out: Optional[torch.Tensor] = None, eps: float = 1e-6,
+              sigmoid: bool = False, expert_first: int = 0, expert_count: Optional[int] = None,
+              exchange: Optional[MoeExchange] = None) -> None:
+    """One MoE block for this rank's tokens (see kdnn_b200_moe_block): router logits, routing, expert
+    feed-forward on the local experts, combine on the token owner, optional residual add + un-scaled RMS norm."""
+    Tl, H = x.shape
+    E = gate.size()
+    if tuple(router_w.shape) != (E, H) or router_w.dtype != x.dtype:
+        raise ValueError("moe_block: router_w must be [E, H] in the Scalar of x")
+    have_bias = router_bias is not None and router_bias.numel() != 0
+    if have_bias and (router_bias.numel() != E or router_bias.dtype != x.dtype):
+        raise ValueError("moe_block: expert_bias extent must be E")
+    for t, n in ((y, "y"), (resid, "resid"), (h_out, "h_out"), (xn_out, "xn_out")):
+        if t is not None and tuple(t.shape) != (Tl, H):
+            raise ValueError(f"moe_block: {n} must be [tokens_local, H]")
+    if y is not None and y.dtype != torch.float32:
+        raise ValueError("moe_block: y is float32")
+    g, u, d = gate.c_struct(), up.c_struct(), down.c_struct()
+    n = E if expert_count is None else expert_count
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    ld = lambda t: t.stride(0) if t is not None else 0
+    rc = lib.kdnn_b200_moe_block(x.data_ptr(), x.stride(0), Tl, _scalar(x), router_w.data_ptr(), router_w.stride(0),
+                                 router_bias.data_ptr() if have_bias else None, top_k, int(norm_topk),
+                                 float(routed_scale), int(sigmoid), C.byref(g), C.byref(u), C.byref(d), expert_first, n,
+                                 ptr(y), ld(y), ptr(resid), ld(resid), ptr(h_out), ld(h_out), ptr(xn_out), ld(xn_out),
+                                 float(eps), C.byref(exchange.c) if exchange is not None else None,
+                                 workspace.data_ptr(), workspace.numel(), _stream())
+    _check(rc, "moe_block")
+
+
+def moe_block_routing(workspace: torch.Tensor, tokens_local: int, world: int, top_k: int, H: int, F: int, n_experts: int,
+                      exchange: Optional[MoeExchange] = None):
+    """(idx, wts) of ALL tokens from the last moe_block call, as device tensors [T, top_k]."""
+    T = tokens_local * world
+    idx = torch.empty((T, top_k), dtype=torch.int32, device=workspace.device)
+    wts = torch.empty((T, top_k), dtype=torch.float32, device=workspace.device)
+    _check(lib.kdnn_b200_moe_block_routing(C.byref(exchange.c) if exchange is not None else None, workspace.data_ptr(),
+                                           tokens_local, world, top_k, H, F, n_experts, idx.data_ptr(), wts.data_ptr(),
+                                           _stream()), "moe_block_routing")
+    return idx, wts
+
+
+def read_probe(buf: torch.Tensor, sink: torch.Tensor) -> None:
+    """Streams `buf` once with read-only 128-bit loads (kdnn_b200_read_probe): the read-only bandwidth ceiling."""
+    _check(lib.kdnn_b200_read_probe(buf.data_ptr(), buf.numel() * buf.element_size(), sink.data_ptr(), _stream()),
+           "read_probe")

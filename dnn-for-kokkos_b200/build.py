@@ -8,7 +8,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["kdnn_gemv.cu", "kdnn_gemm.cu", "kdnn_moe.cu", "kdnn_dequant.cu", "kdnn_capi.cu"]
+SOURCES = ["kdnn_gemv.cu", "kdnn_gemm.cu", "kdnn_moe.cu", "kdnn_dequant.cu", "kdnn_elementwise.cu", "kdnn_capi.cu"]
 HEADERS = ["kdnn_common.cuh", "kdnn_tile.cuh", "kdnn_grouped.cuh", "kdnn_mma.cuh", "kdnn_tc.cuh", os.path.join("..", "..", "include", "kdnn_b200.h")]
 LIB = os.path.join(HERE, "libkdnn_b200.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -21,6 +21,22 @@ cudaError_t gemm_launch(uint32_t dt, const void* w, size_t N, size_t K, const vo
                         size_t M, int xs, void* Y, size_t ldy, int ys, void* ws, int32_t* dots, cudaStream_t st);
 int tile_kind();
 int set_tile_kind(int k);
+int device_sm_count();
+cudaError_t read_probe_launch(const void* src, size_t bytes, uint32_t* sink, int ctas, cudaStream_t st);
+cudaError_t swiglu_launch(const void* gate, size_t ldg, const void* up, size_t ldu, void* out, size_t ldo, size_t T,
+                          size_t F, int scalar, cudaStream_t st);
+cudaError_t weighted_sum_launch(const void* eo, const float* w, void* y, size_t ldy, size_t T, size_t K, size_t D,
+                                int scalar, cudaStream_t st);
+cudaError_t gather_rows_launch(const void* src, size_t lds, const int* rows, void* dst, size_t ldd, size_t N, size_t D,
+                               int scalar, cudaStream_t st);
+cudaError_t scatter_add_launch(const void* src, size_t lds, const int* rows, const float* w, void* dst, size_t ldd,
+                               size_t N, size_t D, int scalar, cudaStream_t st);
+size_t moe_exchange_bytes(size_t tokens_local, size_t world, size_t S, size_t H);
+size_t moe_block_workspace_bytes(size_t tokens_local, size_t world, size_t S, size_t H, size_t F, size_t n_experts,
+                                 int with_region);
+cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st);
+void moe_block_routing(void* const* regions, int rank, void* ws, size_t Tl, size_t world, size_t S, size_t H, size_t F,
+                       size_t E, const int32_t** idx, const float** wts);
 cudaError_t tc_encode_matrix_host(void* out128, const void* w, size_t rows, size_t row_bytes);
 
 cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, int scalar,
@@ -66,7 +82,7 @@ bool tile_type(uint32_t t) { return int8_type(t); }
 // pointer instead of by the copy engine: on a stream that alternates small copies and short kernels the
 // engine hand-offs cost more than the kernels. Chained like every other kernel of the library, so the GEMV
 // that follows a pull prefetches its weights while the pull is in flight.
-__global__ void copy_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, size_t bytes) {
+__global__ void copy_bytes_kernel(const uint8_t* src, uint8_t* dst, size_t bytes) {
   kdnn::pdl_chain_entry();
   const size_t n16 = bytes / 16;
   const size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -322,6 +338,95 @@ int kdnn_b200_moe_ffn(const void* X, size_t ldx, size_t T, int x_scalar,
                      "moe_ffn");
 }
 
+size_t kdnn_b200_moe_exchange_bytes(size_t tokens_local, size_t world, size_t top_k, size_t H) {
+  return kdnn::moe_exchange_bytes(tokens_local, world, top_k, H);
+}
+size_t kdnn_b200_moe_block_workspace_bytes(size_t tokens_local, size_t world, size_t top_k, size_t H, size_t F,
+                                           size_t n_experts, int with_region) {
+  return kdnn::moe_block_workspace_bytes(tokens_local, world, top_k, H, F, n_experts, with_region);
+}
+
+int kdnn_b200_moe_block(const void* x, size_t ldx, size_t tokens_local, int scalar, const void* router_w, size_t ldr,
+                        const void* router_bias, int top_k, int norm_topk, float routed_scale, int sigmoid,
+                        const kdnn_b200_weight_table* gate, const kdnn_b200_weight_table* up,
+                        const kdnn_b200_weight_table* down, size_t expert_first, size_t expert_count, float* y,
+                        size_t ldy, const void* resid, size_t ldres, void* h_out, size_t ldh, void* xn_out,
+                        size_t ldxn, float eps, const kdnn_b200_moe_exchange* ex, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  if (!scalar_ok(scalar)) return fail(KDNN_ERR_INVALID, "moe_block: scalar must be KDNN_F32 or KDNN_BF16");
+  if (!gate || !up || !down) return fail(KDNN_ERR_INVALID, "moe_block: null weight table");
+  const size_t H = gate->cols, F = gate->rows, E = gate->n_experts;
+  if (up->cols != H || up->rows != F || down->rows != H || down->cols != F)
+    return fail(KDNN_ERR_INVALID, "moe_block: dimension mismatch");
+  if (E == 0 || E != up->n_experts || E != down->n_experts)
+    return fail(KDNN_ERR_INVALID, "moe_block: expert table mismatch");
+  if (tokens_local == 0) return KDNN_OK;
+  if (top_k <= 0 || static_cast<size_t>(top_k) > E) return fail(KDNN_ERR_INVALID, "moe_block: need 1 <= top_k <= E");
+  const int world = ex ? ex->world : 1, rank = ex ? ex->rank : 0;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || (ex && !ex->regions))
+    return fail(KDNN_ERR_INVALID, "moe_block: bad exchange descriptor");
+  if (gate->ggml_type != KDNN_GGML_Q4_K || up->ggml_type != KDNN_GGML_Q4_K || down->ggml_type != KDNN_GGML_Q4_K)
+    return KDNN_DECLINED;
+  if (H % 256 != 0 || F % 256 != 0 || F % 64 != 0) return fail(KDNN_ERR_INVALID, "moe_block: K-quant rows must be a multiple of 256 elements");
+  if (!x || !router_w || !workspace || !gate->base || !up->base || !down->base || ldx < H || ldr < H)
+    return fail(KDNN_ERR_INVALID, "moe_block: null argument or short row");
+  const size_t sb = scalar == KDNN_F32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(router_w) & 15u) || (ldr * sb) % 16 != 0) return KDNN_DECLINED;
+  if (y && ((reinterpret_cast<uintptr_t>(y) & 15u) || ldy % 4 != 0 || ldy < H)) return KDNN_DECLINED;
+  if ((resid && ldres < H) || (h_out && ldh < H) || (xn_out && ldxn < H) || ((h_out || xn_out) && !resid))
+    return fail(KDNN_ERR_INVALID, "moe_block: residual outputs need resid and rows of at least H");
+  if (expert_first + expert_count > E) return fail(KDNN_ERR_INVALID, "moe_block: expert range outside the table");
+  if (world > 1 && expert_count == 0) return fail(KDNN_ERR_INVALID, "moe_block: every rank needs at least one expert");
+  const size_t T = tokens_local * static_cast<size_t>(world);
+  if (T * static_cast<size_t>(top_k) > static_cast<size_t>(INT_MAX) / 4) return fail(KDNN_ERR_INVALID, "moe_block: T*S too large");
+  if ((T + 31) / 32 * E * 8 + 16 * E > 160 * 1024) return KDNN_DECLINED;   // slot matrix beyond the one-CTA sort
+  if (workspace_bytes < kdnn::moe_block_workspace_bytes(tokens_local, world, top_k, H, F, E, ex == nullptr) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return fail(KDNN_ERR_INVALID, "moe_block: workspace too small or not 256-byte aligned");
+  kdnn::BlockArgs a{};
+  a.x = x; a.ldx = ldx; a.Tl = tokens_local; a.scalar = scalar; a.rw = router_w; a.ldr = ldr; a.bias = router_bias;
+  a.top_k = top_k; a.norm_topk = norm_topk; a.sigmoid = sigmoid; a.routed_scale = routed_scale;
+  a.gate = gate; a.up = up; a.down = down; a.e_first = expert_first; a.e_count = expert_count;
+  a.resid = resid; a.ldres = ldres; a.h_out = h_out; a.ldh = ldh; a.xn_out = xn_out; a.ldxn = ldxn; a.eps = eps;
+  a.y = y; a.ldy = ldy; a.world = world; a.rank = rank; a.regions = ex ? ex->regions : nullptr;
+  a.wait_ns = ex && ex->wait_ns ? ex->wait_ns : 2000000000ull; a.ws = workspace;
+  return cuda_result(kdnn::moe_block_launch(a, static_cast<cudaStream_t>(stream)), "moe_block");
+}
+
+int kdnn_b200_moe_block_routing(const kdnn_b200_moe_exchange* ex, void* workspace, size_t tokens_local, size_t world,
+                                size_t top_k, size_t H, size_t F, size_t n_experts, int32_t* idx_out, float* wts_out,
+                                void* stream) {
+  if (!workspace || !idx_out || !wts_out) return fail(KDNN_ERR_INVALID, "moe_block_routing: null argument");
+  const int32_t* idx = nullptr;
+  const float* wts = nullptr;
+  kdnn::moe_block_routing(ex ? ex->regions : nullptr, ex ? ex->rank : 0, workspace, tokens_local, world, top_k, H, F,
+                          n_experts, &idx, &wts);
+  const size_t n = tokens_local * world * top_k;
+  cudaError_t e = cudaMemcpyAsync(idx_out, idx, n * sizeof(int32_t), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(wts_out, wts, n * sizeof(float), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+  return cuda_result(e, "moe_block_routing");
+}
+
+int kdnn_b200_peer_alloc(size_t bytes, void** ptr, void* handle64) {
+  if (!ptr || !handle64 || bytes == 0) return fail(KDNN_ERR_INVALID, "peer_alloc: bad argument");
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e == cudaSuccess) e = cudaMemset(*ptr, 0, bytes);
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, *ptr);
+  if (e == cudaSuccess) memcpy(handle64, &h, sizeof(h));
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are 64 bytes");
+  return cuda_result(e, "peer_alloc");
+}
+int kdnn_b200_peer_open(const void* handle64, void** ptr) {
+  if (!ptr || !handle64) return fail(KDNN_ERR_INVALID, "peer_open: bad argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return cuda_result(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess), "peer_open");
+}
+int kdnn_b200_peer_close(void* ptr) { return cuda_result(cudaIpcCloseMemHandle(ptr), "peer_close"); }
+int kdnn_b200_peer_free(void* ptr) { return cuda_result(cudaFree(ptr), "peer_free"); }
+
 int kdnn_b200_residual_rmsnorm(const void* h, size_t ldh, const float* y, size_t ldy, void* out, size_t ldo,
                                size_t T, size_t H, float eps, int scalar, void* stream) {
   if (!scalar_ok(scalar)) return fail(KDNN_ERR_INVALID, "residual_rmsnorm: bad scalar");
@@ -331,6 +436,52 @@ int kdnn_b200_residual_rmsnorm(const void* h, size_t ldh, const float* y, size_t
   return cuda_result(kdnn::residual_rmsnorm_launch(h, ldh, y, ldy, out, ldo, T, H, eps, scalar,
                                                    static_cast<cudaStream_t>(stream)),
                      "residual_rmsnorm");
+}
+
+int kdnn_b200_swiglu(const void* gate, size_t ldg, const void* up, size_t ldu, void* out, size_t ldo, size_t T, size_t F,
+                     int scalar, void* stream) {
+  if (!scalar_ok(scalar)) return fail(KDNN_ERR_INVALID, "swiglu: bad scalar");
+  if (T == 0 || F == 0) return KDNN_OK;
+  if (!gate || !up || !out || ldg < F || ldu < F || ldo < F || T > 65535 || F > INT_MAX)
+    return fail(KDNN_ERR_INVALID, "swiglu: dimension mismatch");
+  return cuda_result(kdnn::swiglu_launch(gate, ldg, up, ldu, out, ldo, T, F, scalar, static_cast<cudaStream_t>(stream)), "swiglu");
+}
+
+int kdnn_b200_moe_expert_weighted_sum(const void* expert_out, const float* top_w, void* y, size_t ldy, size_t T, size_t K,
+                                      size_t D, int scalar, void* stream) {
+  if (!scalar_ok(scalar)) return fail(KDNN_ERR_INVALID, "moe_expert_weighted_sum: bad scalar");
+  if (T == 0 || D == 0 || K == 0) return KDNN_OK;   // src/KokkosDNN_MoE.hpp:323
+  if (!expert_out || !top_w || !y || ldy < D || T > 65535 || D > INT_MAX || K > INT_MAX)
+    return fail(KDNN_ERR_INVALID, "moe_expert_weighted_sum: dimension mismatch");
+  return cuda_result(kdnn::weighted_sum_launch(expert_out, top_w, y, ldy, T, K, D, scalar, static_cast<cudaStream_t>(stream)),
+                     "moe_expert_weighted_sum");
+}
+
+int kdnn_b200_moe_gather_rows(const void* src, size_t lds, size_t C, const int32_t* rows, void* dst, size_t ldd, size_t N,
+                              size_t D, int scalar, void* stream) {
+  if (!scalar_ok(scalar)) return fail(KDNN_ERR_INVALID, "moe_gather_rows: bad scalar");
+  if (N == 0 || D == 0) return KDNN_OK;   // :347
+  if (!src || !rows || !dst || lds < D || ldd < D || C == 0 || N > 65535 || D > INT_MAX)
+    return fail(KDNN_ERR_INVALID, "moe_gather_rows: dimension mismatch");
+  return cuda_result(kdnn::gather_rows_launch(src, lds, rows, dst, ldd, N, D, scalar, static_cast<cudaStream_t>(stream)),
+                     "moe_gather_rows");
+}
+
+int kdnn_b200_moe_scatter_add_weighted(const void* src, size_t lds, const int32_t* rows, const float* weights, void* dst,
+                                       size_t ldd, size_t C, size_t N, size_t D, int scalar, void* stream) {
+  if (!scalar_ok(scalar)) return fail(KDNN_ERR_INVALID, "moe_scatter_add_weighted: bad scalar");
+  if (N == 0 || D == 0 || C == 0) return KDNN_OK;   // :372
+  if (!src || !rows || !weights || !dst || lds < D || ldd < D || N > 65535 || D > INT_MAX)
+    return fail(KDNN_ERR_INVALID, "moe_scatter_add_weighted: dimension mismatch");
+  return cuda_result(kdnn::scatter_add_launch(src, lds, rows, weights, dst, ldd, N, D, scalar, static_cast<cudaStream_t>(stream)),
+                     "moe_scatter_add_weighted");
+}
+
+int kdnn_b200_read_probe(const void* src, size_t bytes, void* sink, void* stream) {
+  if (!src || !sink || (reinterpret_cast<uintptr_t>(src) & 15u)) return fail(KDNN_ERR_INVALID, "read_probe: bad argument");
+  if (bytes < 16) return KDNN_OK;
+  return cuda_result(kdnn::read_probe_launch(src, bytes, static_cast<uint32_t*>(sink), 4 * kdnn::device_sm_count(),
+                                             static_cast<cudaStream_t>(stream)), "read_probe");
 }
 
 int kdnn_b200_dequant_to_dense(uint32_t ggml_type, const void* w, size_t rows, size_t cols, void* y, size_t ldy,

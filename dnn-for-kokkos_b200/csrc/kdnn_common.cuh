@@ -323,6 +323,79 @@ inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block,
 }
 
 
+// ---- expert-parallel exchange over peer memory ---------------------------------------------------
+// Every rank owns one exchange region that its peers can write (plain stores over NVLink into the
+// CONSUMER's memory; consumers only ever read their own memory). Flags are 32-bit epochs that only grow:
+// a producer writes its data, then the epoch with release semantics at system scope; a consumer polls
+// with acquire loads until the flag has reached the epoch it expects. Every poll loop is bounded by the
+// global timer: a wait that runs out records KDNN_ERR_DEVICE_WAIT and the kernel carries on to its exit.
+constexpr int kMaxRanks = 8;
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// true when *flag reached `epoch` within `limit_ns`
+__device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch, unsigned long long limit_ns) {
+  if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
+  const unsigned long long t0 = global_timer_ns();
+  while (global_timer_ns() - t0 < limit_ns) {
+    if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    __nanosleep(64);
+  }
+  return false;
+}
+// What the down-projection kernels need to hand their rows to the token owners and to tell them.
+struct PeerOut {
+  float* out[kMaxRanks];        // every rank's slot-indexed output rows [tokens_local * S][N]; null = plain position-indexed dst
+  uint32_t* oflag[kMaxRanks];   // every rank's "outputs of rank r are complete" flags [world]
+  int world, rank, tokens_local;
+  int* ticket;                  // grid-completion counter (this GPU), null when world == 1
+  const uint32_t* epoch;        // this GPU's current epoch
+};
+// Called by every CTA of a down-projection kernel on its way out (all threads): the last CTA to arrive
+// publishes this rank's epoch to every rank's flag array.
+__device__ __forceinline__ void peer_out_finish(const PeerOut& po, unsigned total_ctas) {
+  if (po.ticket == nullptr) return;
+  __threadfence();   // device scope by everybody, system scope by the one thread that takes the ticket
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(po.ticket, 1) == static_cast<int>(total_ctas) - 1) {
+      *po.ticket = 0;
+      __threadfence_system();
+      const uint32_t e = *po.epoch;
+      for (int r = 0; r < po.world; ++r) st_release_sys(po.oflag[r] + po.rank, e);
+    }
+  }
+}
+// Destination of the output row of slot `slot` (token-major slot id over ALL tokens): the owner's buffer.
+__device__ __forceinline__ float* peer_out_row(const PeerOut& po, int slot, int S, int N) {
+  const int t = slot / S, owner = t / po.tokens_local;
+  return po.out[owner] + (static_cast<size_t>(t - owner * po.tokens_local) * S + (slot - t * S)) * N;
+}
+
+// Arguments of one MoE block call (kdnn_capi.cu validates and fills them, kdnn_moe.cu launches).
+struct BlockArgs {
+  const void* x; size_t ldx; size_t Tl; int scalar;
+  const void* rw; size_t ldr; const void* bias; int top_k, norm_topk, sigmoid; float routed_scale;
+  const kdnn_b200_weight_table *gate, *up, *down;
+  size_t e_first, e_count;
+  const void* resid; size_t ldres; void* h_out; size_t ldh; void* xn_out; size_t ldxn; float eps;
+  float* y; size_t ldy;
+  int world, rank; void* const* regions;   // host array [world] of exchange regions (null: single GPU, region in the workspace)
+  unsigned long long wait_ns;
+  void* ws;
+};
+
 // cudaFuncAttributeMaxDynamicSharedMemorySize belongs to the (kernel, device) pair, so a host thread that
 // moves to another device must set it there too: one bit per device, set on the first launch there.
 struct SmemAttrOnce {

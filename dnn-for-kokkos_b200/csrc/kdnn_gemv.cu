@@ -63,7 +63,7 @@ struct NoHook { __device__ void operator()() const {} };
 // `after_loads` runs once, after this thread's first batch of global loads has been issued
 // and before their values are used: work that needs no activation bytes goes there.
 template <uint32_t DT, class XT, class Hook = NoHook>
-__device__ __forceinline__ void stage_activations(const XT* __restrict__ x, int K, int nitems,
+__device__ __forceinline__ void stage_activations(const XT* x, int K, int nitems,
                                                   int4* xg, float4* hd, int4* hs,
                                                   uint8_t* gscratch, Hook after_loads = Hook()) {
   const int nblk     = K / 32;
@@ -542,7 +542,7 @@ constexpr int kWideRowPitch = kWideSb * 144;
 constexpr int kWideStage   = 2 * kWideRowPitch;  // bytes
 
 template <class XT, class Hook = NoHook>
-__device__ __forceinline__ void stage_activations_wide(const XT* __restrict__ x, int K, uint8_t* xrec,
+__device__ __forceinline__ void stage_activations_wide(const XT* x, int K, uint8_t* xrec,
                                                        uint8_t* gscratch, Hook after_loads = Hook()) {
   const int nblk    = K / 32;
   const int lane    = threadIdx.x & 31;
@@ -1301,7 +1301,7 @@ __device__ float unit_eval_generic(const uint8_t* row, int c, const int8_t* xq, 
 }
 
 template <class XT>
-__global__ void quantize_act_kernel(const XT* __restrict__ x, int K, uint8_t* scratch) {
+__global__ void quantize_act_kernel(const XT* x, int K, uint8_t* scratch) {
   const int nblk    = K / 32;
   const int lane    = threadIdx.x & 31, l8 = lane & 7;
   const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & (sizeof(XT) * 4 - 1)) == 0;
@@ -1325,8 +1325,8 @@ __global__ void quantize_act_kernel(const XT* __restrict__ x, int K, uint8_t* sc
 
 // one warp per row over a staged activation row in global memory
 template <uint32_t DT, class YT>
-__global__ void gemv_generic_kernel(const uint8_t* __restrict__ w, size_t row_bytes, int rows,
-                                    int K, const uint8_t* __restrict__ scratch, YT* y) {
+__global__ void gemv_generic_kernel(const uint8_t* w, size_t row_bytes, int rows,
+                                    int K, const uint8_t* scratch, YT* y) {
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (row >= rows) return;
   const int8_t* xq = reinterpret_cast<const int8_t*>(scratch);
@@ -1341,8 +1341,8 @@ __global__ void gemv_generic_kernel(const uint8_t* __restrict__ w, size_t row_by
 }
 
 template <uint32_t DT>
-__global__ void unit_dots_kernel(const uint8_t* __restrict__ w, size_t row_bytes, int rows, int K,
-                                 const uint8_t* __restrict__ scratch, int32_t* out) {
+__global__ void unit_dots_kernel(const uint8_t* w, size_t row_bytes, int rows, int K,
+                                 const uint8_t* scratch, int32_t* out) {
   const int nu       = K / 32;
   const size_t total = static_cast<size_t>(rows) * nu;
   const int8_t* xq   = reinterpret_cast<const int8_t*>(scratch);

@@ -37,6 +37,7 @@ struct MmaParams {
   int* status;
   int passes_z;          // CTAs along z that share a group's 32-row passes (0 = 1)
   int early;             // launch as a programmatic dependent (only worth it behind a tiny kernel, see launch_chained_if)
+  PeerOut po;            // MODE 0: po.out[0] != null sends the rows to the token owners' slot-indexed buffers
 };
 
 __device__ __forceinline__ int4 lds128_g(uint32_t a) {
@@ -150,7 +151,8 @@ struct M2Layout {
   static constexpr size_t xs    = xq + 2 * kM2NT * kM2XPitch;                          // [2][KC/32][NT] float dx
   static constexpr size_t xp    = xs + 2 * (kM2KC / 32) * kM2NT * 4;                   // [2][KC/256][3 parts][NT][8 bf16]
   static constexpr size_t rowp  = xp + 2 * (kM2KC / 256) * 3 * kM2NT * 16;             // [NT] activation row offsets
-  static constexpr size_t tab   = rowp + kM2NT * 8;                                    // [warps][16 rows]{sw[8], mn[8] bf16, -dmin, pad}
+  static constexpr size_t outp  = rowp + kM2NT * 8;                                    // [NT] output rows in the owners' buffers (scatter mode)
+  static constexpr size_t tab   = outp + kM2NT * 8;                                    // [warps][16 rows]{sw[8], mn[8] bf16, -dmin, pad}
   static constexpr size_t ring  = (tab + kM2Warps * 16 * 4 * 16 + 127) & ~size_t(127); // [warps][stages][16][WPitch]
   static constexpr size_t total = ring + kM2Warps * kM2Stages * kM2StageBytes + 128;
 };
@@ -297,11 +299,15 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
   const int gid = lane >> 2, tig = lane & 3;
   const int g   = blockIdx.y;
   const int beg = p.offs[g], n_g = p.offs[g + 1] - beg;
-  if (n_g <= 0) return;
+  if (n_g <= 0) {
+    if (MODE == 0) peer_out_finish(p.po, gridDim.x * gridDim.y * gridDim.z);
+    return;
+  }
 
   const uint32_t xq_u32 = smem_u32(m2_smem + L::xq), xs_u32 = smem_u32(m2_smem + L::xs);
   const uint32_t xp_u32 = smem_u32(m2_smem + L::xp);
   long long* rowp = reinterpret_cast<long long*>(m2_smem + L::rowp);
+  float** outp = reinterpret_cast<float**>(m2_smem + L::outp);
   const uint32_t tab_u32 = smem_u32(m2_smem + L::tab) + warp * (16 * 4 * 16);
   const uint32_t ring_u32 = smem_u32(m2_smem + L::ring) + warp * (kM2Stages * kM2StageBytes);
 
@@ -383,6 +389,8 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
         ro = static_cast<long long>(srow) * static_cast<long long>(p.x_pitch);
       }
       rowp[threadIdx.x] = ro;
+      if (MODE == 0 && p.po.out[0] != nullptr)
+        outp[threadIdx.x] = threadIdx.x < nt ? peer_out_row(p.po, p.list[beg + t0 + threadIdx.x], p.S, p.N) : nullptr;
     }
     __syncthreads();
     stage_chunk(0);
@@ -505,6 +513,8 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
             if (MODE == 2) {
               const int srow = p.list[beg + t0 + tok] / p.S;
               store_scalar(static_cast<YT*>(p.dst) + static_cast<size_t>(srow) * p.ld_dst + j, acc[t][i]);
+            } else if (MODE == 0 && p.po.out[0] != nullptr) {
+              outp[tok][j] = acc[t][i];
             } else {
               static_cast<float*>(p.dst)[static_cast<size_t>(beg + t0 + tok) * p.N + j] = acc[t][i];
             }
@@ -512,6 +522,7 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
         }
     }
   }
+  if (MODE == 0) peer_out_finish(p.po, gridDim.x * gridDim.y * gridDim.z);
 }
 
 template <int MODE, class YT>
@@ -529,8 +540,8 @@ static cudaError_t launch_grouped_mma(const MmaParams& p, int groups, cudaStream
 // elements) -> reference staging layout at dst + r * pitch_bytes. Rows at or past
 // *nrows_dev (when given) are skipped.
 template <class SRC>
-__global__ void quantize_rows_kernel(const SRC* __restrict__ src, size_t ld, int nrows, int K,
-                                     const int* __restrict__ nrows_dev, uint8_t* __restrict__ dst,
+__global__ void quantize_rows_kernel(const SRC* src, size_t ld, int nrows, int K,
+                                     const int* nrows_dev, uint8_t* dst,
                                      size_t pitch_bytes) {
   pdl_chain_entry();
   const int row = blockIdx.y;

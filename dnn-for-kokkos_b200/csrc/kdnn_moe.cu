@@ -20,6 +20,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <atomic>
 
 namespace kdnn {
@@ -97,22 +98,16 @@ int set_tile_kind(int k) { return k >= 0 && k <= 3 ? g_tile_kind.exchange(k) : g
 // times with the reference's tie rule (strict '>' scanning ids upward = lowest id
 // among equals), weights are recomputed from the logits by lane 0 in the
 // reference's order (:114-146).
-template <class ST>
-__global__ void moe_route_kernel(const ST* __restrict__ logits, size_t ld, int T, int E,
-                                 const ST* __restrict__ bias, int top_k, int norm_topk,
-                                 float routed_scale, int sigmoid, int32_t* __restrict__ top_idx,
-                                 float* __restrict__ top_w) {
-  pdl_chain_entry();
-  extern __shared__ float route_smem[];
+// Top-k selection and weights of ONE token by one warp. `lg(e)` / `bs(e)`: the logit and the bias of expert e
+// as floats (already rounded to the Scalar they are stored in); `score`: E floats of shared memory.
+template <class GetLogit, class GetBias>
+__device__ __forceinline__ void route_warp(GetLogit lg, GetBias bs, bool has_bias, int E, int top_k, int norm_topk,
+                                           float routed_scale, int sigmoid, float* score, int32_t* idx, float* w,
+                                           int lane) {
   constexpr float NEG = -3.4028235e38f;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
-  const int t = blockIdx.x * wpb + warp;
-  if (t >= T) return;
-  float* score = route_smem + static_cast<size_t>(warp) * E;
-  const ST* lg = logits + static_cast<size_t>(t) * ld;
   for (int e = lane; e < E; e += 32) {
-    const float raw = to_f32(lg[e]);
-    const float b   = bias ? to_f32(bias[e]) : 0.0f;
+    const float raw = lg(e);
+    const float b   = has_bias ? bs(e) : 0.0f;
     score[e]        = sigmoid ? (1.0f / (1.0f + expf(-raw))) + b : raw + b;
   }
   __syncwarp();
@@ -124,8 +119,6 @@ __global__ void moe_route_kernel(const ST* __restrict__ logits, size_t ld, int T
       for (int e = 0; e < E; ++e) gsum += expf(score[e] - gmx);
     }
   }
-  int32_t* idx = top_idx + static_cast<size_t>(t) * top_k;
-  float* w     = top_w + static_cast<size_t>(t) * top_k;
   for (int k = 0; k < top_k; ++k) {
     float best = NEG;
     int be     = 0x7fffffff;
@@ -155,8 +148,8 @@ __global__ void moe_route_kernel(const ST* __restrict__ logits, size_t ld, int T
   if (lane != 0) return;
   auto logit = [&](int k) {
     const int i     = idx[k];
-    const float raw = to_f32(lg[i < 0 ? 0 : i]);
-    return sigmoid ? 1.0f / (1.0f + expf(-raw)) : raw + (bias ? to_f32(bias[i < 0 ? 0 : i]) : 0.0f);
+    const float raw = lg(i < 0 ? 0 : i);
+    return sigmoid ? 1.0f / (1.0f + expf(-raw)) : raw + (has_bias ? bs(i < 0 ? 0 : i) : 0.0f);
   };
   if (sigmoid) {
     if (norm_topk) {
@@ -175,6 +168,22 @@ __global__ void moe_route_kernel(const ST* __restrict__ logits, size_t ld, int T
   } else {
     for (int k = 0; k < top_k; ++k) w[k] = expf(logit(k) - gmx) / gsum * routed_scale;
   }
+}
+
+template <class ST>
+__global__ void moe_route_kernel(const ST* logits, size_t ld, int T, int E,
+                                 const ST* bias, int top_k, int norm_topk,
+                                 float routed_scale, int sigmoid, int32_t* top_idx,
+                                 float* top_w) {
+  pdl_chain_entry();
+  extern __shared__ float route_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const int t = blockIdx.x * wpb + warp;
+  if (t >= T) return;
+  const ST* lg = logits + static_cast<size_t>(t) * ld;
+  route_warp([&](int e) { return to_f32(lg[e]); }, [&](int e) { return to_f32(bias[e]); }, bias != nullptr, E, top_k,
+             norm_topk, routed_scale, sigmoid, route_smem + static_cast<size_t>(warp) * E,
+             top_idx + static_cast<size_t>(t) * top_k, top_w + static_cast<size_t>(t) * top_k, lane);
 }
 
 cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, int scalar,
@@ -207,9 +216,9 @@ cudaError_t moe_route_launch(const void* logits, size_t ld, size_t T, size_t E, 
 // depend on it. Several small CTAs: every CTA counts all slots (shared-memory atomics) and
 // forms the same prefix sums, then places only its own experts -- a warp per expert sweeps
 // the slot ids upward 32 at a time, ranks come from one ballot per sweep step.
-__global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_slots, int e_first,
-                                int e_count, int* __restrict__ offs, int* __restrict__ list,
-                                int* __restrict__ pos, int cache_slots) {
+__global__ void moe_sort_kernel(const int32_t* idx, int n_slots, int e_first,
+                                int e_count, int* offs, int* list,
+                                int* pos, int cache_slots) {
   pdl_chain_entry();
   extern __shared__ int sort_smem[];  // counts[e_count], cursor[e_count], then (when it fits) the local expert of every slot
   int* counts = sort_smem;
@@ -291,11 +300,21 @@ __device__ void moe_sort_block(const PrepParams& p, uint32_t* sm) {
   int* starts = counts + E;
   int* gst    = starts + E + 1;
   int* dup    = gst + E + 1;
+  // the routed expert of up to eight slots per thread is read once, all loads in flight together, and kept
+  // in registers for the placement pass (a single CTA lives on memory latency here)
+  constexpr int kPer = 8;
+  const bool cached = p.n_slots <= nt * kPer;
+  int ev[kPer];
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int i = tid + j * nt;
+    ev[j] = cached && i < p.n_slots ? p.idx[i] - p.e_first : -1;
+  }
   for (int i = tid; i < E * W; i += nt) mask[i] = 0u;
   if (tid == 0) *dup = 0;
   __syncthreads();
-  for (int i = tid; i < p.n_slots; i += nt) {
-    const int e = p.idx[i] - p.e_first;
+  for (int i = tid, j = 0; i < p.n_slots; i += nt, ++j) {
+    const int e = cached ? ev[j < kPer ? j : 0] : p.idx[i] - p.e_first;
     if (e >= 0 && e < E) {
       const int t = i / p.S;
       const uint32_t bit = 1u << (t & 31);
@@ -352,8 +371,8 @@ __device__ void moe_sort_block(const PrepParams& p, uint32_t* sm) {
         if (p.idx[i] - p.e_first == e) { p.list[c2] = i; p.pos[i] = c2; ++c2; }
     }
   }
-  for (int i = tid; i < p.n_slots; i += nt) {
-    const int e = p.idx[i] - p.e_first;
+  for (int i = tid, j = 0; i < p.n_slots; i += nt, ++j) {
+    const int e = cached ? ev[j < kPer ? j : 0] : p.idx[i] - p.e_first;
     if (e < 0 || e >= E) {
       p.pos[i] = -1;
     } else if (!has_dup) {
@@ -371,7 +390,7 @@ inline size_t moe_sort_smem(size_t e_count, size_t T) {
 
 // One warp-iteration = eight 32-blocks of one row (four lanes per block), as quantize_rows_kernel.
 template <class SRC>
-__device__ void quantize_rows_part(const SRC* __restrict__ src, size_t ld, int nrows, int K, uint8_t* __restrict__ dst,
+__device__ void quantize_rows_part(const SRC* src, size_t ld, int nrows, int K, uint8_t* dst,
                                    size_t pitch_bytes, int gwarp, int nwarp) {
   const int nblk = K / 32, per_row = (nblk + 7) / 8;
   const int lane = threadIdx.x & 31, l4 = lane & 3;
@@ -430,8 +449,8 @@ constexpr size_t kPrepSmemLimit = 160 * 1024;
 // (src/KokkosDNN_MoE.hpp:326-331; zero-weight and unrouted slots skipped,
 // src/KokkosDNN_GGUF.hpp:2205-2207).
 template <class YT>
-__global__ void moe_combine_kernel(const float* __restrict__ out, const int* __restrict__ pos,
-                                   const float* __restrict__ wts, int T, int S, int H, YT* Y,
+__global__ void moe_combine_kernel(const float* out, const int* pos,
+                                   const float* wts, int T, int S, int H, YT* Y,
                                    size_t ldy) {
   pdl_chain_entry();
   const int t = blockIdx.y;
@@ -450,8 +469,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ out, const int* __r
 // The same sums, four columns per thread (16-byte loads of `out`; H % 4 == 0 and 16-byte / 8-byte
 // aligned output rows): every element is accumulated in the same slot order as above.
 template <class YT>
-__global__ void moe_combine4_kernel(const float* __restrict__ out, const int* __restrict__ pos,
-                                    const float* __restrict__ wts, int T, int S, int H, YT* Y,
+__global__ void moe_combine4_kernel(const float* out, const int* pos,
+                                    const float* wts, int T, int S, int H, YT* Y,
                                     size_t ldy) {
   pdl_chain_entry();
   const int t = blockIdx.y;
@@ -671,8 +690,8 @@ cudaError_t moe_ffn_launch(const void* X, size_t ldx, size_t T, int xs,
 // add after the MoE block (models/lfm2_5/KokkosDNN_LFM25Model.hpp:812-816) fused with the next block's
 // un-scaled RMS norm (src/KokkosDNN_RMSNorm.hpp:347-361). One CTA per row, fp32 statistics.
 template <class ST>
-__global__ void residual_rmsnorm_kernel(const ST* __restrict__ h, size_t ldh, const float* __restrict__ y,
-                                        size_t ldy, ST* __restrict__ out, size_t ldo, int H, float eps) {
+__global__ void residual_rmsnorm_kernel(const ST* h, size_t ldh, const float* y,
+                                        size_t ldy, ST* out, size_t ldo, int H, float eps) {
   pdl_chain_entry();
   __shared__ float red[32];
   const int t = blockIdx.x;
@@ -708,6 +727,421 @@ cudaError_t residual_rmsnorm_launch(const void* h, size_t ldh, const float* y, s
   return launch_chained(residual_rmsnorm_kernel<__nv_bfloat16>, dim3((unsigned)T), dim3(256), 0, st,
                         static_cast<const __nv_bfloat16*>(h), ldh, y, ldy, static_cast<__nv_bfloat16*>(out), ldo,
                         (int)H, eps);
+}
+
+
+// ===== the MoE block in four launches, single GPU or expert-parallel over peer memory ================
+//   1. moe_gate_kernel     router logits (x . Wr^T, fp32 accumulation, rounded to Scalar like the caller's
+//                          gemm, models/lfm2_5/KokkosDNN_LFM25Model.hpp:788-797), top-k + weights, per-32
+//                          quantization of the token rows -- written into EVERY rank's exchange region
+//                          (plain peer stores: the dispatch is an all-gather by push, 4 KB per token and
+//                          rank at hidden 2048); the last CTA to finish tells the peers, waits for theirs
+//                          and sorts all routed slots for the local experts
+//   2. gate/up tile kernel, 3. down tile kernel (its epilogue stores every output row straight into the
+//                          token owner's slot-indexed buffer and its last CTA raises the owners' flags)
+//   4. moe_combine_norm_kernel   waits for every rank's flag, sums the slots in slot order, adds the
+//                          residual and forms the next block's un-scaled RMS norm
+// Exchange region of one rank (all ranks use the same layout; T = tokens_local * world):
+struct ExLayout {
+  size_t xrows, idx, wts, out, xflag, oflag, total;
+};
+static ExLayout ex_layout(size_t Tl, size_t world, size_t S, size_t H) {
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  const size_t T = Tl * world;
+  ExLayout L{};
+  size_t o = 0;
+  L.xrows = o; o += up(T * act_row_pitch(H));
+  L.idx   = o; o += up(T * S * sizeof(int32_t));
+  L.wts   = o; o += up(T * S * sizeof(float));
+  L.out   = o; o += up(Tl * S * H * sizeof(float));
+  L.xflag = o; o += 256;
+  L.oflag = o; o += 256;
+  L.total = o;
+  return L;
+}
+size_t moe_exchange_bytes(size_t tokens_local, size_t world, size_t S, size_t H) {
+  return ex_layout(tokens_local, world, S, H).total;
+}
+
+constexpr int kGateThreads = 512;   // 16 warps: the logit loop lives on loads in flight
+struct GateParams {
+  const void* x; size_t ldx;
+  const void* rw; size_t ldr; const void* bias;
+  int Tl, H, E, top_k, norm_topk, sigmoid, world, rank;
+  float routed_scale;
+  uint8_t* region[kMaxRanks];   // every rank's exchange region
+  ExLayout L;
+  size_t x_pitch;
+  PrepParams sort;              // the slot sort of the last CTA (over all T tokens, local experts)
+  int* ticket; uint32_t* epoch; int* status;
+  unsigned long long wait_ns;
+};
+
+// TPC = tokens per CTA: 4 when this rank has many tokens (every CTA streams the whole router matrix from L2,
+// so fewer, fatter CTAs), 1 when it has few (more CTAs than a handful, so the kernel still shrinks with the
+// number of ranks).
+template <class ST, int kGateTokens>
+__global__ void __launch_bounds__(kGateThreads) moe_gate_kernel(const GateParams p) {
+  pdl_chain_entry();
+  extern __shared__ __align__(16) uint8_t gate_smem[];
+  float* xs = reinterpret_cast<float*>(gate_smem);                       // [kGateTokens][H]
+  float* lgs = xs + static_cast<size_t>(kGateTokens) * p.H;              // [kGateTokens][E] rounded logits
+  float* score = lgs + static_cast<size_t>(kGateTokens) * p.E;           // [kGateTokens][E]
+  int32_t* ridx = reinterpret_cast<int32_t*>(score + static_cast<size_t>(kGateTokens) * p.E);   // [kGateTokens][top_k]
+  float* rwts = reinterpret_cast<float*>(ridx + kGateTokens * p.top_k);                          // [kGateTokens][top_k]
+  __shared__ int s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t epoch = *p.epoch + 1u;                                  // this block call's epoch
+  const int t_first = blockIdx.x * kGateTokens;                          // local token index
+  const int nt = min(kGateTokens, p.Tl - t_first);
+  const ST* x = static_cast<const ST*>(p.x);
+  for (int i = threadIdx.x; i < nt * p.H; i += blockDim.x) {
+    const int t = i / p.H, k = i - t * p.H;
+    xs[t * p.H + k] = to_f32(x[static_cast<size_t>(t_first + t) * p.ldx + k]);
+  }
+  __syncthreads();
+  // ---- router logits: a warp owns E / 16 experts, lanes along the hidden dimension ----
+  // Per 256-element chunk of K a lane takes its eight activations of every token into registers ONCE and
+  // then streams the matching 16 bytes of each of its experts' rows (four rows in flight) against them:
+  // shared memory is read once per chunk instead of once per expert, and the loop runs on loads in flight.
+  const ST* rw = static_cast<const ST*>(p.rw);
+  constexpr int kWarps = kGateThreads / 32;
+  for (int e0 = warp; e0 < p.E; e0 += 8 * kWarps) {        // this warp's experts e0, e0 + 16, ... (eight at a time)
+    float acc[8][kGateTokens];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int t = 0; t < kGateTokens; ++t) acc[j][t] = 0.f;
+    for (int k = lane * 8; k < p.H; k += 256) {
+      float xv[kGateTokens][8];
+#pragma unroll
+      for (int t = 0; t < kGateTokens; ++t) {
+        const float4 a = *reinterpret_cast<const float4*>(xs + t * p.H + k);
+        const float4 b = *reinterpret_cast<const float4*>(xs + t * p.H + k + 4);
+        xv[t][0] = a.x; xv[t][1] = a.y; xv[t][2] = a.z; xv[t][3] = a.w;
+        xv[t][4] = b.x; xv[t][5] = b.y; xv[t][6] = b.z; xv[t][7] = b.w;
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float wv[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = e0 + (4 * h + j) * kWarps;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) wv[j][i] = 0.f;
+          if (e < p.E) load8<ST>(rw + static_cast<size_t>(e) * p.ldr, static_cast<size_t>(k), true, wv[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int t = 0; t < kGateTokens; ++t)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[4 * h + j][t] = fmaf(wv[j][i], xv[t][i], acc[4 * h + j][t]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = e0 + j * kWarps;
+#pragma unroll
+      for (int t = 0; t < kGateTokens; ++t) {
+        const float v = warp_sum(acc[j][t]);
+        if (lane == 0 && e < p.E) {
+          ST r;
+          store_scalar(&r, v);          // the logits reach the router in the Scalar type
+          lgs[t * p.E + e] = to_f32(r);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // ---- routing: one warp per token; results into every rank's region ----
+  const ST* bias = static_cast<const ST*>(p.bias);
+  if (warp < nt) {
+    const int tg = p.rank * p.Tl + t_first + warp;   // global token index
+    int32_t* my_idx = ridx + warp * p.top_k;         // selection and weights in shared memory (the weight pass
+    float* my_w = rwts + warp * p.top_k;             // reads the ids back several times), then out to every rank
+    const float* lgt = lgs + warp * p.E;
+    route_warp([&](int e) { return lgt[e]; }, [&](int e) { return to_f32(bias[e]); }, bias != nullptr, p.E, p.top_k,
+               p.norm_topk, p.routed_scale, p.sigmoid, score + warp * p.E, my_idx, my_w, lane);
+    __syncwarp();
+    for (int r = 0; r < p.world; ++r) {
+      int32_t* di = reinterpret_cast<int32_t*>(p.region[r] + p.L.idx) + static_cast<size_t>(tg) * p.top_k;
+      float* dw = reinterpret_cast<float*>(p.region[r] + p.L.wts) + static_cast<size_t>(tg) * p.top_k;
+      for (int k = lane; k < p.top_k; k += 32) {
+        di[k] = my_idx[k];
+        dw[k] = my_w[k];
+      }
+    }
+  }
+  // ---- per-32 quantization of the token rows (the reference's stage-1 quantizer), to every rank ----
+  {
+    const int nblk = p.H / 32, per_row = (nblk + 7) / 8, l4 = lane & 3;
+    for (int it = warp; it < nt * per_row; it += kGateThreads / 32) {
+      const int t = it / per_row, b = (it - t * per_row) * 8 + (lane >> 2);
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = b < nblk ? xs[t * p.H + b * 32 + l4 * 8 + i] : 0.f;
+      float d;
+      int part, total;
+      const uint2 packed = quantize_block_lane8(v, d, part, total);
+      if (b >= nblk) continue;
+      const size_t row_off = p.L.xrows + static_cast<size_t>(p.rank * p.Tl + t_first + t) * p.x_pitch;
+      const float ds = __fmul_rn(static_cast<float>(total), d);
+      for (int r = 0; r < p.world; ++r) {
+        uint8_t* out = p.region[r] + row_off;
+        reinterpret_cast<uint2*>(out + static_cast<size_t>(b) * 32)[l4] = packed;
+        if (l4 == 0) {
+          reinterpret_cast<ActHdr*>(out + act_hdr_offset(p.H))[b] = ActHdr{d, part, total - part, 0};
+          reinterpret_cast<float2*>(out + act_bytes(p.H))[b] = make_float2(d, ds);
+          store_sum_parts(out, act_parts_offset(static_cast<size_t>(p.H)), b, ds);
+        }
+      }
+    }
+  }
+  // ---- the last CTA: tell the peers, wait for them, sort ----
+  // every thread's stores are ordered at device scope before the CTA's barrier; one thread then extends the
+  // order to system scope (the peers) before it takes the ticket -- a system-scope fence by every thread of
+  // every CTA costs tens of microseconds
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (p.world > 1) __threadfence_system();
+    s_last = atomicAdd(p.ticket, 1) == static_cast<int>(gridDim.x) - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (p.world > 1) {
+    if (threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank)
+      st_release_sys(reinterpret_cast<uint32_t*>(p.region[threadIdx.x] + p.L.xflag) + p.rank, epoch);
+    if (threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank) {
+      if (!wait_epoch(reinterpret_cast<const uint32_t*>(p.region[p.rank] + p.L.xflag) + threadIdx.x, epoch, p.wait_ns))
+        atomicExch(p.status, KDNN_ERR_DEVICE_WAIT);
+    }
+    __syncthreads();
+  }
+  moe_sort_block(p.sort, reinterpret_cast<uint32_t*>(gate_smem));
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *p.epoch = epoch;
+    *p.ticket = 0;
+  }
+}
+
+// Y[t,:] = sum over the slots of w * out[slot,:] (slots ascending, fp32, src/KokkosDNN_MoE.hpp:326-331; slots
+// whose expert id is outside [0, E) or whose weight is zero are skipped, src/KokkosDNN_GGUF.hpp:2106-2110,
+// :2205-2207), then optionally the residual add and the next block's un-scaled RMS norm
+// (models/lfm2_5/KokkosDNN_LFM25Model.hpp:812-816, :770; src/KokkosDNN_RMSNorm.hpp:347-361):
+//   h_out = Scalar(float(resid) + Y),  xn_out = Scalar(h_out / sqrt(mean(h_out^2) + eps)).
+// One CTA per local token. With world > 1 the CTA first waits (bounded) for every rank's output flag.
+struct CombineParams {
+  const float* out; const int32_t* idx; const float* wts;   // this rank's region: out [Tl*S][H], idx/wts of ALL tokens
+  int Tl, S, H, e_lo, e_hi, world, rank;   // slots of experts in [e_lo, e_hi) have a row in `out`
+  const uint32_t* oflag; const uint32_t* epoch; int* status;
+  unsigned long long wait_ns;
+  float* y; size_t ldy;
+  const void* resid; size_t ldres; void* h_out; size_t ldh; void* xn_out; size_t ldxn;
+  float eps;
+};
+template <class ST>
+__global__ void __launch_bounds__(256) moe_combine_norm_kernel(const CombineParams p) {
+  pdl_chain_entry();
+  extern __shared__ float comb_smem[];   // [H] the row after the residual add
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  if (p.world > 1) {
+    if (threadIdx.x < p.world) {
+      if (!wait_epoch(p.oflag + threadIdx.x, *p.epoch, p.wait_ns)) atomicExch(p.status, KDNN_ERR_DEVICE_WAIT);
+    }
+    __syncthreads();
+  }
+  const int tg = p.rank * p.Tl + t;
+  const int32_t* idx = p.idx + static_cast<size_t>(tg) * p.S;
+  const float* wts = p.wts + static_cast<size_t>(tg) * p.S;
+  const ST* resid = static_cast<const ST*>(p.resid);
+  float ss = 0.f;
+  for (int d = threadIdx.x * 4; d < p.H; d += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < p.S; ++s) {
+      const int e = idx[s];
+      const float w = wts[s];
+      if (e < p.e_lo || e >= p.e_hi || w == 0.0f) continue;
+      const float4 v = *reinterpret_cast<const float4*>(p.out + (static_cast<size_t>(t) * p.S + s) * p.H + d);
+      acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    }
+    if (p.y) *reinterpret_cast<float4*>(p.y + static_cast<size_t>(t) * p.ldy + d) = acc;
+    if (resid) {
+      const float a[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ST r;
+        store_scalar(&r, to_f32(resid[static_cast<size_t>(t) * p.ldres + d + i]) + a[i]);
+        if (p.h_out) static_cast<ST*>(p.h_out)[static_cast<size_t>(t) * p.ldh + d + i] = r;
+        const float v = to_f32(r);
+        comb_smem[d + i] = v;
+        ss += v * v;
+      }
+    }
+  }
+  if (!resid || !p.xn_out) return;
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) red[0] = 1.0f / sqrtf(v / static_cast<float>(p.H) + p.eps);
+  }
+  __syncthreads();
+  const float inv = red[0];
+  for (int d = threadIdx.x; d < p.H; d += blockDim.x)
+    store_scalar(static_cast<ST*>(p.xn_out) + static_cast<size_t>(t) * p.ldxn + d, comb_smem[d] * inv);
+}
+
+// Local (not peer-visible) workspace of the block call.
+struct BlockWs {
+  size_t offs, list, pos, groups, ngroups, act, actq, sync, region, total;
+};
+static BlockWs block_ws_layout(size_t T, size_t S, size_t H, size_t F, size_t n_experts, size_t region_bytes) {
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  BlockWs w{};
+  size_t o = 0;
+  w.offs = o; o += up((n_experts + 1) * sizeof(int));
+  w.list = o; o += up(T * S * sizeof(int));
+  w.pos  = o; o += up(T * S * sizeof(int));
+  w.groups = o; o += up((n_experts + T * S / kTcNT + 1) * sizeof(int4));
+  w.ngroups = o; o += 256;
+  w.act  = o; o += up(T * S * F * sizeof(float));
+  w.actq = o; o += up(T * S * act_row_pitch(F));
+  w.sync = o; o += 256;          // gate ticket, down ticket, epoch
+  w.region = o; o += region_bytes;
+  w.total = o;
+  return w;
+}
+size_t moe_block_workspace_bytes(size_t tokens_local, size_t world, size_t S, size_t H, size_t F, size_t n_experts,
+                                 int with_region) {
+  const size_t T = tokens_local * world;
+  return block_ws_layout(T, S, H, F, n_experts, with_region ? moe_exchange_bytes(tokens_local, world, S, H) : 0).total;
+}
+
+
+cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
+  const size_t H = a.gate->cols, F = a.gate->rows, S = static_cast<size_t>(a.top_k), E = a.gate->n_experts;
+  const size_t world = static_cast<size_t>(a.world), T = a.Tl * world;
+  const ExLayout XL = ex_layout(a.Tl, world, S, H);
+  const BlockWs L = block_ws_layout(T, S, H, F, E, a.regions ? 0 : XL.total);
+  uint8_t* b = static_cast<uint8_t*>(a.ws);
+  int* sync = reinterpret_cast<int*>(b + L.sync);
+  int* status = nullptr;
+  cudaError_t err = moe_status_ptr(&status);
+  if (err != cudaSuccess) return err;
+  uint8_t* regions[kMaxRanks] = {};
+  for (size_t r = 0; r < world; ++r) regions[r] = a.regions ? static_cast<uint8_t*>(a.regions[r]) : b + L.region;
+  uint8_t* mine = regions[a.rank];
+
+  GateParams g{};
+  g.x = a.x; g.ldx = a.ldx; g.rw = a.rw; g.ldr = a.ldr; g.bias = a.bias;
+  g.Tl = (int)a.Tl; g.H = (int)H; g.E = (int)E; g.top_k = a.top_k; g.norm_topk = a.norm_topk; g.sigmoid = a.sigmoid;
+  g.world = a.world; g.rank = a.rank; g.routed_scale = a.routed_scale;
+  for (size_t r = 0; r < world; ++r) g.region[r] = regions[r];
+  g.L = XL; g.x_pitch = act_row_pitch(H);
+  g.sort.idx = reinterpret_cast<const int32_t*>(mine + XL.idx); g.sort.n_slots = (int)(T * S); g.sort.S = (int)S;
+  g.sort.e_first = (int)a.e_first; g.sort.e_count = (int)a.e_count; g.sort.words = (int)((T + 31) / 32);
+  g.sort.offs = reinterpret_cast<int*>(b + L.offs); g.sort.list = reinterpret_cast<int*>(b + L.list);
+  g.sort.pos = reinterpret_cast<int*>(b + L.pos); g.sort.groups = reinterpret_cast<int4*>(b + L.groups);
+  g.sort.n_groups = reinterpret_cast<int*>(b + L.ngroups); g.sort.X = nullptr; g.sort.T = (int)T; g.sort.H = (int)H;
+  g.ticket = sync; g.epoch = reinterpret_cast<uint32_t*>(sync + 2); g.status = status; g.wait_ns = a.wait_ns;
+  const int tpc = a.Tl >= 256 ? 4 : a.Tl >= 96 ? 2 : 1;
+  const size_t gsm = std::max((size_t)tpc * (H + 2 * E + 2 * S) * sizeof(float), moe_sort_smem(a.e_count, T));
+  using GateKern = void (*)(const GateParams);
+  const bool f32 = a.scalar == KDNN_F32;
+  const GateKern gk = tpc == 4 ? (f32 ? moe_gate_kernel<float, 4> : moe_gate_kernel<__nv_bfloat16, 4>)
+                    : tpc == 2 ? (f32 ? moe_gate_kernel<float, 2> : moe_gate_kernel<__nv_bfloat16, 2>)
+                               : (f32 ? moe_gate_kernel<float, 1> : moe_gate_kernel<__nv_bfloat16, 1>);
+  if (gsm > 48 * 1024) {
+    err = cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsm);
+    if (err != cudaSuccess) return err;
+  }
+  err = launch_chained(gk, dim3((unsigned)((a.Tl + tpc - 1) / tpc)), dim3(kGateThreads), gsm, st, g);
+  if (err != cudaSuccess) return err;
+
+  // ---- expert tiles over all T tokens' slots, local experts ----
+  PeerOut po{};
+  for (size_t r = 0; r < world; ++r) {
+    po.out[r] = reinterpret_cast<float*>(regions[r] + XL.out);
+    po.oflag[r] = reinterpret_cast<uint32_t*>(regions[r] + XL.oflag);
+  }
+  po.world = a.world; po.rank = a.rank; po.tokens_local = (int)a.Tl;
+  po.ticket = a.world > 1 ? sync + 1 : nullptr;
+  po.epoch = reinterpret_cast<const uint32_t*>(sync + 2);
+  if (a.e_count > 0) {
+    const int want = tile_kind() == 3 ? 1 : tile_kind();
+    const int kind = (want == 2 && !tc_covers(a.gate, a.up, a.down)) || want == 0 ? 1 : want;
+    const int n_slots = (int)(T * S);
+    int* offs = reinterpret_cast<int*>(b + L.offs);
+    int* list = reinterpret_cast<int*>(b + L.list);
+    uint8_t* xrows = mine + XL.xrows;
+    uint8_t* arows = b + L.actq;
+    float* act = reinterpret_cast<float*>(b + L.act);
+    if (kind == 2) {
+      const int max_groups = (int)a.e_count + n_slots / kTcNT;
+      TcParams t1{};
+      t1.maps0 = static_cast<const CUtensorMap*>(a.gate->tma); t1.maps1 = static_cast<const CUtensorMap*>(a.up->tma);
+      t1.N = (int)F; t1.K = (int)H; t1.tile_rows = 64; t1.row_tiles = (int)((F + 63) / 64);
+      t1.groups = reinterpret_cast<const int4*>(b + L.groups); t1.n_groups = reinterpret_cast<const int*>(b + L.ngroups);
+      t1.list = list; t1.S = (int)S; t1.xrows = xrows; t1.x_pitch = act_row_pitch(H);
+      t1.dst = act; t1.ld_dst = F; t1.round_bf16 = a.scalar == KDNN_BF16; t1.qdst = arows; t1.q_pitch = act_row_pitch(F);
+      t1.status = status;
+      err = launch_grouped_tc<1, float>(t1, max_groups * t1.row_tiles, st);
+      if (err != cudaSuccess) return err;
+      TcParams t0{};
+      t0.maps0 = static_cast<const CUtensorMap*>(a.down->tma);
+      t0.N = (int)H; t0.K = (int)F; t0.tile_rows = 128; t0.row_tiles = (int)((H + 127) / 128);
+      t0.groups = t1.groups; t0.n_groups = t1.n_groups; t0.list = list; t0.S = (int)S;
+      t0.xrows = arows; t0.x_pitch = act_row_pitch(F); t0.dst = nullptr; t0.ld_dst = H; t0.status = status; t0.po = po;
+      err = launch_grouped_tc<0, float>(t0, max_groups * t0.row_tiles, st);
+      if (err != cudaSuccess) return err;
+    } else {
+      MmaParams m1{};
+      m1.w0 = a.gate->base; m1.w1 = a.up->base; m1.row_bytes = (int)a.gate->row_bytes;
+      m1.N = (int)F; m1.K = (int)H; m1.offs = offs; m1.list = list; m1.S = (int)S; m1.g_first = (int)a.e_first;
+      m1.xrows = xrows; m1.x_pitch = act_row_pitch(H); m1.dst = act; m1.ld_dst = F;
+      m1.round_bf16 = a.scalar == KDNN_BF16; m1.status = status;
+      const int mean_rows = (int)((T * S + E - 1) / E);
+      const int passes_z = max(1, min(4, 1 + (2 * mean_rows) / 32));
+      m1.passes_z = passes_z; m1.qdst = arows; m1.q_pitch = act_row_pitch(F);
+      err = launch_grouped_mma<1, float>(m1, (int)a.e_count, st);
+      if (err != cudaSuccess) return err;
+      MmaParams m0{};
+      m0.w0 = a.down->base; m0.row_bytes = (int)a.down->row_bytes;
+      m0.N = (int)H; m0.K = (int)F; m0.offs = offs; m0.list = list; m0.S = (int)S; m0.g_first = (int)a.e_first;
+      m0.xrows = arows; m0.x_pitch = act_row_pitch(F); m0.dst = nullptr; m0.ld_dst = H; m0.status = status;
+      m0.passes_z = passes_z; m0.po = po;
+      err = launch_grouped_mma<0, float>(m0, (int)a.e_count, st);
+      if (err != cudaSuccess) return err;
+    }
+  }
+  // ---- combine on the token owner ----
+  CombineParams c{};
+  c.out = reinterpret_cast<const float*>(mine + XL.out);
+  c.idx = reinterpret_cast<const int32_t*>(mine + XL.idx); c.wts = reinterpret_cast<const float*>(mine + XL.wts);
+  c.Tl = (int)a.Tl; c.S = (int)S; c.H = (int)H; c.world = a.world; c.rank = a.rank;
+  c.e_lo = a.world > 1 ? 0 : (int)a.e_first; c.e_hi = a.world > 1 ? (int)E : (int)(a.e_first + a.e_count);
+  c.oflag = reinterpret_cast<const uint32_t*>(mine + XL.oflag); c.epoch = reinterpret_cast<const uint32_t*>(sync + 2);
+  c.status = status; c.wait_ns = a.wait_ns;
+  c.y = a.y; c.ldy = a.ldy; c.resid = a.resid; c.ldres = a.ldres; c.h_out = a.h_out; c.ldh = a.ldh;
+  c.xn_out = a.xn_out; c.ldxn = a.ldxn; c.eps = a.eps;
+  auto ck = a.scalar == KDNN_F32 ? moe_combine_norm_kernel<float> : moe_combine_norm_kernel<__nv_bfloat16>;
+  return launch_chained(ck, dim3((unsigned)a.Tl), dim3(256), H * sizeof(float), st, c);
+}
+
+void moe_block_routing(void* const* regions, int rank, void* ws, size_t Tl, size_t world, size_t S, size_t H, size_t F,
+                       size_t E, const int32_t** idx, const float** wts) {
+  const ExLayout XL = ex_layout(Tl, world, S, H);
+  const BlockWs L = block_ws_layout(Tl * world, S, H, F, E, regions ? 0 : XL.total);
+  uint8_t* mine = regions ? static_cast<uint8_t*>(regions[rank]) : static_cast<uint8_t*>(ws) + L.region;
+  *idx = reinterpret_cast<const int32_t*>(mine + XL.idx);
+  *wts = reinterpret_cast<const float*>(mine + XL.wts);
 }
 
 int moe_take_status() {

@@ -67,6 +67,7 @@ struct alignas(64) TcParams {
   size_t q_pitch;
   int* status;
   int32_t* dots;              // debug/parity: when set, raw int32 sub-block dots [pos][N][K/32] are stored too
+  PeerOut po;                 // MODE 0: po.out[0] != null sends the rows to the token owners' slot-indexed buffers
 };
 
 
@@ -83,6 +84,26 @@ struct TcLayout {
   static constexpr uint32_t bar  = ex + (MODE == 1 ? 2048 * 4 : 0);
   static constexpr uint32_t total = bar + 256 + 128;              // + slack for the 128-byte alignment of the base
 };
+
+// Loads of what the PREVIOUS kernel in the stream wrote (group records, slot list, quantized rows). They must
+// not be __ldg / invariant loads: the compiler may move an invariant load above griddepcontrol.wait, i.e. in
+// front of the moment the producer's data exists (seen as groups read as zero on every call but the first).
+__device__ __forceinline__ int ld_dep(const int* p) {
+  int v;
+  asm volatile("ld.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int4 ld_dep(const int4* p) {
+  int4 v;
+  asm volatile("ld.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 ld_dep(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.global.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int4 ld_dep128(const void* p) { return ld_dep(static_cast<const int4*>(p)); }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
@@ -286,7 +307,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
     return false;
   };
 
-  const int n_groups    = __ldg(p.n_groups);
+  const int n_groups    = ld_dep(p.n_groups);
   const int total_tiles = n_groups * p.row_tiles;
   const int nks         = p.K / 256;
   bool ok = true;
@@ -295,11 +316,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
     // ------------------------------------------------------------------ producer (one thread)
     if (lane == 0) {
       uint32_t seq = 0;
-      int e_next = blockIdx.x < total_tiles ? __ldg(p.groups + blockIdx.x / p.row_tiles).x : 0;
+      int e_next = blockIdx.x < total_tiles ? ld_dep(p.groups + blockIdx.x / p.row_tiles).x : 0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int g = t / p.row_tiles, rb = t - g * p.row_tiles;
         const int e = e_next;   // requested a tile ago
-        if (t + static_cast<int>(gridDim.x) < total_tiles) e_next = __ldg(p.groups + (t + gridDim.x) / p.row_tiles).x;
+        if (t + static_cast<int>(gridDim.x) < total_tiles) e_next = ld_dep(p.groups + (t + gridDim.x) / p.row_tiles).x;
         const CUtensorMap* m0 = p.maps0 ? p.maps0 + e : &p.one;
         const CUtensorMap* m1 = MODE == 1 ? p.maps1 + e : m0;
         if (p.maps0) {
@@ -348,11 +369,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
     // here since a tile ago) at the same moment, and the pieces of stage s + 1 while stage s is unpacked.
     struct Rows { const uint8_t* r0; const uint8_t* r1; const uint8_t* rs; };   // null past the group's rows
     const int xn = ((ut >> 7) << 3) | (ut & 7), xc16 = (ut >> 3) & 15;   // this thread's pieces: rows xn, xn + 16, 16-byte piece xc16
-    auto group_of = [&](int t) { return t < total_tiles ? __ldg(p.groups + t / p.row_tiles) : make_int4(0, 0, 0, 0); };
+    auto group_of = [&](int t) { return t < total_tiles ? ld_dep(p.groups + t / p.row_tiles) : make_int4(0, 0, 0, 0); };
     auto rows_of = [&](const int4& gi) {
       auto row_of = [&](int n) -> const uint8_t* {
         if (n >= gi.z) return nullptr;
-        const int srow = MODE == 0 ? gi.y + n : __ldg(p.list + gi.y + n) / p.S;
+        const int srow = MODE == 0 ? gi.y + n : ld_dep(p.list + gi.y + n) / p.S;
         return p.xrows + static_cast<size_t>(srow) * p.x_pitch;
       };
       return Rows{row_of(xn), row_of(xn + 16), row_of(ut & 31)};
@@ -368,9 +389,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
       f.sv = make_uint2(0u, 0u);
       if (f_t < total_tiles) {
         const size_t ko = static_cast<size_t>(f_ks) * 256 + xc16 * 16;
-        if (rows0.r0) f.x0 = ldg128(rows0.r0 + ko);
-        if (rows0.r1) f.x1 = ldg128(rows0.r1 + ko);
-        if (rows0.rs) f.sv = __ldg(reinterpret_cast<const uint2*>(rows0.rs + scale_off + static_cast<size_t>(f_ks) * 64 + (ut >> 5) * 8));
+        if (rows0.r0) f.x0 = ld_dep128(rows0.r0 + ko);
+        if (rows0.r1) f.x1 = ld_dep128(rows0.r1 + ko);
+        if (rows0.rs) f.sv = ld_dep(reinterpret_cast<const uint2*>(rows0.rs + scale_off + static_cast<size_t>(f_ks) * 64 + (ut >> 5) * 8));
       }
       if (++f_ks == nks) {   // the cursor enters the next tile
         f_ks = 0;
@@ -485,11 +506,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
     const int row = q * 32 + lane;
     const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + sh * (4 * kTcNT);
     uint32_t seq = 0, tile_no = 0;
-    int4 gi_next = blockIdx.x < total_tiles ? __ldg(p.groups + blockIdx.x / p.row_tiles) : make_int4(0, 0, 0, 0);
+    int4 gi_next = blockIdx.x < total_tiles ? ld_dep(p.groups + blockIdx.x / p.row_tiles) : make_int4(0, 0, 0, 0);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
       const int g = t / p.row_tiles, rb = t - g * p.row_tiles;
       const int4 gi = gi_next;   // requested a tile ago
-      if (t + static_cast<int>(gridDim.x) < total_tiles) gi_next = __ldg(p.groups + (t + gridDim.x) / p.row_tiles);
+      if (t + static_cast<int>(gridDim.x) < total_tiles) gi_next = ld_dep(p.groups + (t + gridDim.x) / p.row_tiles);
       // the group's activation rows are split between the warps that share a TMEM lane quadrant:
       // columns [0, h0) and [h0, n), h0 a multiple of 8
       const int h0 = min(gi.z, (((gi.z + 1) >> 1) + 7) & ~7);
@@ -621,8 +642,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
             if (c < ncol) {
               const int ps = gi.y + c0 + c;
               if (MODE == 2) {
-                const int srow = __ldg(p.list + ps) / p.S;
+                const int srow = ld_dep(p.list + ps) / p.S;
                 store_scalar(static_cast<YT*>(p.dst) + static_cast<size_t>(srow) * p.ld_dst + jrow, acc[c]);
+              } else if (MODE == 0 && p.po.out[0] != nullptr) {
+                peer_out_row(p.po, ld_dep(p.list + ps), p.S, p.N)[jrow] = acc[c];
               } else {
                 static_cast<float*>(p.dst)[static_cast<size_t>(ps) * p.N + jrow] = acc[c];
               }
@@ -633,6 +656,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
     }
   }
   if (!ok && lane == 0) atomicExch(p.status, KDNN_ERR_DEVICE_WAIT);
+  if (MODE == 0) peer_out_finish(p.po, gridDim.x);
   tc_before();
   __syncthreads();
   if (warp == kTcWarpMma)

@@ -21,9 +21,16 @@
 #include <climits>
 #include <cstddef>
 #include <cstdint>
+#include <map>
 #include <stdexcept>
 #include <string>
 #include <type_traits>
+#include <vector>
+
+#include <cuda_runtime.h>
+#if defined(KDNN_B200_NVTX)
+#include <nvtx3/nvToolsExt.h>
+#endif
 
 #include "kdnn_b200.h"
 
@@ -258,6 +265,150 @@ void moe_ffn(const ExecSpace& space, const XView& X, const Table& gate, const Ta
                                    StreamOf<ExecSpace>::get(space)),
                  "moe_ffn");
 }
+
+
+// ---- the reference's own signatures -------------------------------------------------------------------
+// Gguf::quant_gemv / quant_gemm / quant_moe_decode exactly as the reference declares them
+// (src/KokkosDNN_GGUF.hpp:2531-2537, :2564-2570, :2335-2346): handle first, views, label last, no extra
+// arguments. They are templates over the argument types, so they accept the reference's
+// DNNHandle<ExecSpace>, Gguf::QuantWeight<ExecSpace>, Gguf::QuantWeightTable<ExecSpace> and Kokkos::View
+// objects unchanged. What the C ABI needs beyond those arguments lives in a per-thread cache that grows on
+// first use and is then reused (like the handle's lazily created members, src/KokkosDNN_Handle.hpp:186-193):
+// the batched calls' workspace, and per weight table the TMA descriptors of its experts. A declined int8
+// GEMV lands in this library's fp kernel (the reference lands in its own, :2550).
+namespace Gguf {
+namespace detail {
+
+#if defined(KDNN_B200_NVTX)
+struct Range {
+  explicit Range(const std::string& label) { nvtxRangePushA(label.c_str()); }
+  ~Range() { nvtxRangePop(); }
+};
+#else
+struct Range {
+  explicit Range(const std::string&) {}
+};
+#endif
+
+// Device bytes that only grow; one buffer per host thread (a thread drives one stream at a time, as the
+// reference's one-handle-per-thread rule has it).
+inline void* workspace(std::size_t bytes) {
+  struct Buf { void* p = nullptr; std::size_t n = 0; };
+  static thread_local Buf b;
+  if (bytes > b.n) {
+    if (b.p) cudaFree(b.p);
+    b.p = nullptr;
+    b.n = 0;
+    const std::size_t want = (bytes + (std::size_t(1) << 20)) & ~((std::size_t(1) << 20) - 1);
+    if (cudaMalloc(&b.p, want) != cudaSuccess) throw std::runtime_error("KokkosDNN::B200: workspace allocation failed");
+    cudaMemset(b.p, 0, want);
+    b.n = want;
+  }
+  return b.p;
+}
+
+// TMA descriptors of a table's experts, built once per table (keyed by the device address of its pointer
+// array: payloads never move after load, models/lfm2_5/KokkosDNN_LFM25Model.hpp:557-560).
+template <class Table>
+inline const void* table_tma(const Table& t) {
+  static thread_local std::map<const void*, void*> cache;
+  const void* key = t.base.data();
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  void* dev = nullptr;
+  const std::size_t n = t.size();
+  std::vector<std::uintptr_t> host(n);
+  cudaMemcpy(host.data(), t.base.data(), n * sizeof(std::uintptr_t), cudaMemcpyDeviceToHost);
+  std::vector<unsigned char> maps(kdnn_b200_weight_table_tma_bytes(n));
+  if (kdnn_b200_weight_table_tma_encode(host.data(), static_cast<std::uint32_t>(t.dtype), t.rows, t.cols, n,
+                                        maps.data()) == KDNN_OK &&
+      cudaMalloc(&dev, maps.size()) == cudaSuccess)
+    cudaMemcpy(dev, maps.data(), maps.size(), cudaMemcpyHostToDevice);
+  cache[key] = dev;   // nullptr: no tensor-core descriptors for this table, the mma.sync kernel serves it
+  return dev;
+}
+
+template <class Table>
+inline kdnn_b200_weight_table table_c(const Table& t) {
+  kdnn_b200_weight_table c = table_of(t);
+  c.tma = table_tma(t);
+  return c;
+}
+
+template <class Handle>
+inline void* stream_of(const Handle&) { return nullptr; }   // the reference's quant ops ignore the handle and
+                                                            // launch on the default instance (:2347, :2400, :2571)
+}  // namespace detail
+
+// src/KokkosDNN_GGUF.hpp:2531-2551
+template <class Handle, class XView, class QuantWeight, class YView, class SView>
+void quant_gemv(const Handle& handle, const XView& x, const QuantWeight& w, const YView& y, const SView& act_scratch,
+                const std::string& label = "KokkosDNN::Gguf::quant_gemv") {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(x.data())>::type>::type;
+  detail::Range range(label);
+  if (x.extent(0) != w.cols || y.extent(0) != w.rows) throw std::invalid_argument("quant_gemv: dimension mismatch");
+  if (w.rows == 0 || w.cols == 0) return;
+  if (scalar_tag<Scalar>() < 0) throw std::invalid_argument("quant_gemv: Scalar must be float or bhalf_t");
+  int rc = KDNN_DECLINED;
+  if (x.stride(0) == 1 && y.stride(0) == 1)
+    rc = kdnn_b200_quant_gemv(static_cast<std::uint32_t>(w.dtype), w.data.data(), w.rows, w.cols, x.data(),
+                              scalar_tag<Scalar>(), y.data(), scalar_tag<Scalar>(), act_scratch.data(),
+                              act_scratch.extent(0), detail::stream_of(handle));
+  throw_on_error(rc, "quant_gemv");
+  if (rc == KDNN_DECLINED)   // the staging-free path, as the reference falls back to its own
+    throw_on_error(kdnn_b200_quant_gemv_fp(static_cast<std::uint32_t>(w.dtype), w.data.data(), w.rows, w.cols, x.data(),
+                                           scalar_tag<Scalar>(), y.data(), scalar_tag<Scalar>(),
+                                           detail::stream_of(handle)),
+                   "quant_gemv");
+}
+
+// src/KokkosDNN_GGUF.hpp:2564-2593
+template <class Handle, class XView, class QuantWeight, class YView>
+void quant_gemm(const Handle& handle, const XView& X, const QuantWeight& w, const YView& Y,
+                const std::string& label = "KokkosDNN::Gguf::quant_gemm") {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(X.data())>::type>::type;
+  detail::Range range(label);
+  const std::size_t M = X.extent(0), K = X.extent(1), N = w.rows;
+  if (w.cols != K || Y.extent(0) != M || Y.extent(1) != N) throw std::invalid_argument("quant_gemm: dimension mismatch");
+  if (M == 0 || N == 0 || K == 0) return;
+  if (scalar_tag<Scalar>() < 0 || X.stride(1) != 1 || Y.stride(1) != 1)
+    throw std::invalid_argument("quant_gemm: views must be LayoutRight float or bhalf_t");
+  const std::size_t wsb = kdnn_b200_gemm_workspace_bytes(M, K);
+  const int rc = kdnn_b200_quant_gemm(static_cast<std::uint32_t>(w.dtype), w.data.data(), N, K, X.data(), X.stride(0), M,
+                                      scalar_tag<Scalar>(), Y.data(), Y.stride(0), scalar_tag<Scalar>(),
+                                      detail::workspace(wsb), wsb, detail::stream_of(handle));
+  throw_on_error(rc, "quant_gemm");
+  if (rc == KDNN_DECLINED) throw std::invalid_argument("quant_gemm: unsupported dtype");   // :2573-2574
+}
+
+// src/KokkosDNN_GGUF.hpp:2335-2391 (int8 activation numerics, see kdnn_b200_moe_ffn)
+template <class Handle, class XView, class Table, class IView, class WView, class AView, class YView>
+void quant_moe_decode(const Handle& handle, const XView& X, const Table& gate, const Table& up, const Table& down,
+                      const IView& idx, const WView& wts, const AView& act, const YView& Y,
+                      const std::string& label = "KokkosDNN::Gguf::quant_moe_decode") {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(X.data())>::type>::type;
+  detail::Range range(label);
+  if (X.extent(0) != 1 || Y.extent(0) != 1) throw std::invalid_argument("quant_moe_decode: expected one row");
+  const std::size_t K = X.extent(1), MI = gate.rows;
+  const std::size_t S = idx.extent(0) == 0 ? 0 : idx.extent(1);
+  if (gate.cols != K || up.cols != K || up.rows != MI || down.rows != K || down.cols != MI || Y.extent(1) != K)
+    throw std::invalid_argument("quant_moe_decode: dimension mismatch");
+  if (gate.size() == 0 || gate.size() != up.size() || gate.size() != down.size())
+    throw std::invalid_argument("quant_moe_decode: expert table mismatch");
+  if (idx.extent(0) != 1 || wts.extent(0) != 1 || wts.extent(1) != S)
+    throw std::invalid_argument("quant_moe_decode: routing dimension mismatch");
+  if (act.extent(0) < S || (S > 0 && act.extent(1) != MI))
+    throw std::invalid_argument("quant_moe_decode: act scratch too small");
+  if (S == 0 || K == 0 || MI == 0) return;
+  const kdnn_b200_weight_table g = detail::table_c(gate), u = detail::table_c(up), d = detail::table_c(down);
+  const std::size_t wsb = kdnn_b200_moe_workspace_bytes(1, S, K, MI, gate.size());
+  throw_on_error(kdnn_b200_moe_ffn(X.data(), X.stride(0), 1, scalar_tag<Scalar>(), &g, &u, &d, idx.data(), wts.data(), S,
+                                   Y.data(), Y.stride(0), scalar_tag<Scalar>(), 0, gate.size(), detail::workspace(wsb),
+                                   wsb, detail::stream_of(handle)),
+                 "quant_moe_decode");
+}
+
+}  // namespace Gguf
 
 }  // namespace B200
 }  // namespace KokkosDNN

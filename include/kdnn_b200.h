@@ -248,6 +248,66 @@ int kdnn_b200_moe_ffn(const void* X, size_t ldx, size_t T, int x_scalar,
                       size_t expert_first, size_t expert_count,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- the MoE block in four launches, single GPU or expert-parallel --------------------------------- */
+
+/* Expert-parallel exchange over peer memory (NVLink): every rank owns one region of
+ * kdnn_b200_moe_exchange_bytes() that ALL ranks can address (cudaMalloc + cudaIpc handles, or any other
+ * peer-mapped allocation; zero it once before the first call). `regions[r]` is rank r's region as seen from
+ * THIS process; regions[rank] is the local one. Every rank makes the same sequence of block calls with the
+ * same tokens_local, world, top_k and hidden size. No counterpart in the reference, which is single-device
+ * (there is no collective anywhere in it); the partition rule is expert e on rank e / (E / world). */
+typedef struct {
+  int rank, world;            /* world <= 8 */
+  void* const* regions;       /* host array [world] of device addresses */
+  unsigned long long wait_ns; /* bound of every device-side wait for a peer; 0 = 2 s */
+} kdnn_b200_moe_exchange;
+
+size_t kdnn_b200_moe_exchange_bytes(size_t tokens_local, size_t world, size_t top_k, size_t H);
+
+/* Workspace bytes of kdnn_b200_moe_block (256-byte aligned, zeroed once before the first call;
+ * with_region != 0 includes the exchange region of a single-GPU call). */
+size_t kdnn_b200_moe_block_workspace_bytes(size_t tokens_local, size_t world, size_t top_k, size_t H, size_t F,
+                                           size_t n_experts, int with_region);
+
+/* One MoE block for this rank's tokens_local tokens:
+ *   logits = Scalar(x . router_w^T)  (the caller's gemm, models/lfm2_5/KokkosDNN_LFM25Model.hpp:796)
+ *   -> moe_route / moe_route_sigmoid (src/KokkosDNN_MoE.hpp:240-304)
+ *   -> the expert feed-forward with int8 activations on this rank's experts [expert_first, +expert_count)
+ *      for the routed slots of ALL ranks' tokens (kdnn_b200_moe_ffn's numerics)
+ *   -> y = sum over the slots (slot order, fp32) on the token's owner
+ *   -> optionally h_out = Scalar(float(resid) + y) (:812-816) and xn_out = rmsnorm_noscale(h_out)
+ *      (src/KokkosDNN_RMSNorm.hpp:347-361, the next block's :770).
+ * Four kernel launches: router + routing + row quantizer + slot sort, gate/up tiles, down tiles, combine.
+ * With `ex` != NULL the token rows travel to every rank inside the first kernel (plain peer stores) and the
+ * down kernel stores its output rows straight into the token owner's region; every wait for a peer is
+ * bounded (KDNN_ERR_DEVICE_WAIT in kdnn_b200_device_status() when one gave up; the call never hangs).
+ *   x [tokens_local, H] Scalar; router_w [E, H] Scalar, 16-byte aligned rows; router_bias [E] or NULL;
+ *   y [tokens_local, H] float or NULL; resid / h_out / xn_out [tokens_local, H] Scalar or NULL.
+ * Q4_K tables only (KDNN_DECLINED otherwise: compose kdnn_b200_moe_route + kdnn_b200_moe_ffn instead). */
+int kdnn_b200_moe_block(const void* x, size_t ldx, size_t tokens_local, int scalar,
+                        const void* router_w, size_t ldr, const void* router_bias,
+                        int top_k, int norm_topk, float routed_scale, int sigmoid,
+                        const kdnn_b200_weight_table* gate, const kdnn_b200_weight_table* up,
+                        const kdnn_b200_weight_table* down, size_t expert_first, size_t expert_count,
+                        float* y, size_t ldy, const void* resid, size_t ldres, void* h_out, size_t ldh,
+                        void* xn_out, size_t ldxn, float eps,
+                        const kdnn_b200_moe_exchange* ex, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Copies the routing result of the last kdnn_b200_moe_block call for ALL tokens (token-major over the
+ * ranks) out of the exchange region / workspace into the caller's device buffers, on `stream`:
+ * idx_out [T, top_k] int32, wts_out [T, top_k] float. */
+int kdnn_b200_moe_block_routing(const kdnn_b200_moe_exchange* ex, void* workspace, size_t tokens_local, size_t world,
+                                size_t top_k, size_t H, size_t F, size_t n_experts, int32_t* idx_out, float* wts_out,
+                                void* stream);
+
+/* Peer-visible device memory for the exchange regions: cudaMalloc + cudaIpcGetMemHandle on the owner,
+ * cudaIpcOpenMemHandle on the peers (handle = 64 opaque bytes to pass between the processes). These are
+ * the only entry points of the library that allocate. */
+int kdnn_b200_peer_alloc(size_t bytes, void** ptr, void* handle64);
+int kdnn_b200_peer_open(const void* handle64, void** ptr);
+int kdnn_b200_peer_close(void* ptr);
+int kdnn_b200_peer_free(void* ptr);
+
 /* out[t,:] = Scalar(r / sqrt(mean(r^2) + eps)), r = Scalar(float(h[t,:]) + y[t,:]): the residual add that
  * follows the MoE block (models/lfm2_5/KokkosDNN_LFM25Model.hpp:812-816) fused with the next block's
  * un-scaled RMS norm, KokkosDNN::rmsnorm_noscale, src/KokkosDNN_RMSNorm.hpp:347-361.
@@ -255,6 +315,35 @@ int kdnn_b200_moe_ffn(const void* X, size_t ldx, size_t T, int x_scalar,
  *   kdnn_b200_moe_ffn. */
 int kdnn_b200_residual_rmsnorm(const void* h, size_t ldh, const float* y, size_t ldy, void* out, size_t ldo,
                                size_t T, size_t H, float eps, int scalar, void* stream);
+
+/* ---- the small MoE operators, for callers that keep the reference's per-expert loop ------------------
+ * (models/lfm2_5/KokkosDNN_LFM25Model.hpp:441-547). Rows are contiguous, pitches in elements; argument
+ * errors the reference throws for return KDNN_ERR_INVALID; zero extents return KDNN_OK without a launch. */
+
+/* out[t, f] = Scalar(silu(float(gate[t, f])) * float(up[t, f])), fp32 arithmetic:
+ * KokkosDNN::swiglu, src/KokkosDNN_SwiGLU.hpp:24-38 (silu :12-14). */
+int kdnn_b200_swiglu(const void* gate, size_t ldg, const void* up, size_t ldu, void* out, size_t ldo, size_t T, size_t F,
+                     int scalar, void* stream);
+
+/* y[t, d] = Scalar(sum_k top_w[t, k] * float(expert_out[t, k, d])), k ascending, fp32:
+ * KokkosDNN::moe_expert_weighted_sum, src/KokkosDNN_MoE.hpp:313-332. expert_out [T, K, D] contiguous. */
+int kdnn_b200_moe_expert_weighted_sum(const void* expert_out, const float* top_w, void* y, size_t ldy, size_t T, size_t K,
+                                      size_t D, int scalar, void* stream);
+
+/* dst[n, :] = src[rows[n], :], 0 <= rows[n] < C (not checked on the device, as in the reference):
+ * KokkosDNN::moe_gather_rows, src/KokkosDNN_MoE.hpp:337-351. */
+int kdnn_b200_moe_gather_rows(const void* src, size_t lds, size_t C, const int32_t* rows, void* dst, size_t ldd, size_t N,
+                              size_t D, int scalar, void* stream);
+
+/* dst[rows[n], d] = Scalar(float(dst[rows[n], d]) + weights[n] * float(src[n, d])); `rows` must hold unique
+ * entries (no atomics): KokkosDNN::moe_scatter_add_weighted, src/KokkosDNN_MoE.hpp:360-381. */
+int kdnn_b200_moe_scatter_add_weighted(const void* src, size_t lds, const int32_t* rows, const float* weights, void* dst,
+                                       size_t ldd, size_t C, size_t N, size_t D, int scalar, void* stream);
+
+/* Measurement aid: streams [src, src + bytes) once with 128-bit read-only loads and discards the data
+ * (`sink`: one device word). The read-only ceiling next to which the reference quotes its GEMV bandwidths
+ * (benchmarks/Bench_GGUFGemv.cpp:65-81, benchmarks/Bench_MoeDecode.cpp:217-257). src 16-byte aligned. */
+int kdnn_b200_read_probe(const void* src, size_t bytes, void* sink, void* stream);
 
 /* Y[r, k] = Scalar(dequant(W[r, k])): replaces KokkosDNN::Gguf::dequant_to_dense,
  * src/KokkosDNN_GGUF.hpp:2839-2934 (block formulas :300-384). Types Q4_K, Q5_K, Q6_K, Q8_0; fp32 outputs are

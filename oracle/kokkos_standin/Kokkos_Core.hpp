@@ -40,6 +40,9 @@ namespace Kokkos {
 // which is what Kokkos::rint lowers to on every backend.
 inline float rint(float v) { return ::nearbyintf(v); }
 inline float expf(float v) { return ::expf(v); }
+inline float sqrtf(float v) { return ::sqrtf(v); }
+inline float cosf(float v) { return ::cosf(v); }
+inline float sinf(float v) { return ::sinf(v); }
 
 // ---- spaces -------------------------------------------------------------
 struct HostSpace {};

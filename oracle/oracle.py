@@ -421,6 +421,26 @@ class Ref:
             return bf16_bits_to_f32(Y), bf16_bits_to_f32(act)
         return Y, act
 
+    def rmsnorm_noscale(self, x, eps, bf16=False):
+        """KokkosDNN::rmsnorm_noscale (src/KokkosDNN_RMSNorm.hpp:347-361)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        T, D = x.shape
+        xs = self._scalar(x, bf16)
+        y = np.zeros((T, D), dtype=np.uint16 if bf16 else np.float32)
+        self._check(self.lib.kref_rmsnorm_noscale(_ptr(xs), C.c_int(int(bf16)), C.c_size_t(T), C.c_size_t(D),
+                                                  C.c_float(eps), _ptr(y)))
+        return bf16_bits_to_f32(y) if bf16 else y
+
+    def swiglu(self, gate, up, bf16=False):
+        """KokkosDNN::swiglu (src/KokkosDNN_SwiGLU.hpp:24-38)."""
+        gate = np.ascontiguousarray(gate, dtype=np.float32)
+        up = np.ascontiguousarray(up, dtype=np.float32)
+        T, F = gate.shape
+        out = np.zeros((T, F), dtype=np.uint16 if bf16 else np.float32)
+        self._check(self.lib.kref_swiglu(_ptr(self._scalar(gate, bf16)), _ptr(self._scalar(up, bf16)), C.c_int(int(bf16)),
+                                         C.c_size_t(T), C.c_size_t(F), _ptr(out)))
+        return bf16_bits_to_f32(out) if bf16 else out
+
     def moe_weighted_sum(self, expert_out, top_w, bf16=False):
         eo = np.ascontiguousarray(expert_out, dtype=np.float32)
         T, K, D = eo.shape

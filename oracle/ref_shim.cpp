@@ -13,6 +13,8 @@
 #include "KokkosDNN_GGUF.hpp"
 #include "KokkosDNN_GGUF_Synthetic.hpp"
 #include "KokkosDNN_MoE.hpp"
+#include "KokkosDNN_RMSNorm.hpp"
+#include "KokkosDNN_SwiGLU.hpp"
 
 #include <cstdint>
 #include <cstdio>
@@ -440,6 +442,34 @@ int kref_gguf_read_kv(const char* path, const char* key, int kind, char* buf, si
       *f32 = f.kv_f32(key);
     } else {
       *u32 = f.kv_u32(key);
+    }
+  });
+}
+
+// src/KokkosDNN_RMSNorm.hpp:347 rmsnorm_noscale: y = x / sqrt(mean(x^2) + eps), rows of a [T, D] view
+int kref_rmsnorm_noscale(const void* x, int bf16, size_t T, size_t D, float eps, void* y) {
+  return guarded([&] {
+    if (bf16) {
+      V2<BHalf> xv(static_cast<BHalf*>(const_cast<void*>(x)), T, D), yv(static_cast<BHalf*>(y), T, D);
+      KokkosDNN::rmsnorm_noscale<Exec, BHalf>(xv, eps, yv);
+    } else {
+      V2<float> xv(static_cast<float*>(const_cast<void*>(x)), T, D), yv(static_cast<float*>(y), T, D);
+      KokkosDNN::rmsnorm_noscale<Exec, float>(xv, eps, yv);
+    }
+  });
+}
+
+// src/KokkosDNN_SwiGLU.hpp:24 swiglu: out = Scalar(silu(gate) * up), [T, F]
+int kref_swiglu(const void* gate, const void* up, int bf16, size_t T, size_t F, void* out) {
+  return guarded([&] {
+    if (bf16) {
+      V2<BHalf> g(static_cast<BHalf*>(const_cast<void*>(gate)), T, F), u(static_cast<BHalf*>(const_cast<void*>(up)), T, F),
+          o(static_cast<BHalf*>(out), T, F);
+      KokkosDNN::swiglu<Exec, BHalf>(g, u, o);
+    } else {
+      V2<float> g(static_cast<float*>(const_cast<void*>(gate)), T, F), u(static_cast<float*>(const_cast<void*>(up)), T, F),
+          o(static_cast<float*>(out), T, F);
+      KokkosDNN::swiglu<Exec, float>(g, u, o);
     }
   });
 }

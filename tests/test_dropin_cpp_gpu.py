@@ -14,3 +14,17 @@ def test_cpp_dropin_layer(kd):
     res = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "all checks passed" in res.stdout
+
+
+def test_cpp_dropin_with_the_reference_types(kd):
+    """tests/cpp/dropin_ref_types_test.cpp passes the reference's own DNNHandle / QuantWeight / QuantWeightTable
+    objects through the reference-signature wrappers (KokkosDNN::B200::Gguf). It compiles only where the
+    reference's headers are; elsewhere the prebuilt binary runs, and the test is skipped if there is none."""
+    import __graft_entry__ as ge
+    ge.build_cpp_dropin_test()
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cpp", "dropin_ref_types_test")
+    if not os.path.exists(exe):
+        pytest.skip("built only where the reference's headers are present")
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "all checks passed" in res.stdout

@@ -74,9 +74,20 @@ def test_expert_parallel_partials_sum_to_full_gloo(tmp_path):
     assert all(open(tmp_path / f"ok{r}").read() == "1" for r in range(2))
 
 
+def test_token_range():
+    ms = _stack_module()
+    assert [ms.token_range(r, 8, 256) for r in range(8)] == [(32 * r, 32) for r in range(8)]
+    assert ms.token_range(0, 1, 7) == (0, 7)
+    with pytest.raises(ValueError):
+        ms.token_range(0, 3, 256)
+
+
 @pytest.mark.gpu
 def test_residual_rmsnorm(kd):
+    """out = Scalar(rmsnorm_noscale(Scalar(h + y))) against the reference's own rmsnorm_noscale
+    (src/KokkosDNN_RMSNorm.hpp:347-361, through its compiled headers when present) applied to the residual sum."""
     dev = "cuda:0"
+    ref = O.Ref() if O.Ref.available() else None
     for dt in (torch.float32, torch.bfloat16):
         g = torch.Generator().manual_seed(1)
         h = torch.randn(37, 2048, generator=g).to(dt)
@@ -85,27 +96,33 @@ def test_residual_rmsnorm(kd):
         kd.residual_rmsnorm(h.to(dev), y.to(dev), out, 1e-6)
         torch.cuda.synchronize()
         r = (h.float() + y).to(dt).float()
-        ref = (r / torch.sqrt((r * r).mean(dim=1, keepdim=True) + 1e-6)).to(dt).float()
+        if ref is not None:
+            want = torch.from_numpy(ref.rmsnorm_noscale(r.numpy(), 1e-6, bf16=(dt == torch.bfloat16)))
+        else:
+            want = (r / torch.sqrt((r * r).mean(dim=1, keepdim=True) + 1e-6)).to(dt).float()
         tol = 1e-5 if dt == torch.float32 else 2.0 ** -7
-        assert (out.float().cpu() - ref).abs().max() <= tol * ref.abs().max()
+        assert (out.float().cpu() - want).abs().max() <= tol * want.abs().max()
 
 
 @pytest.mark.gpu
-def test_two_layer_stack_matches_checker(kd, port):
+@pytest.mark.parametrize("mode", ["push", "allreduce"])
+def test_two_layer_stack_matches_checker(kd, port, mode):
+    """x = rmsnorm(h); y = ffn(route(x W_r^T), x); h' = h + y, two layers, against the CPU checker."""
     ms = _stack_module()
     dev = torch.device("cuda:0")
     cfg = ms.StackConfig(layers=2, hidden=512, ffn=256, experts=8, top_k=2, tokens=12, seed=5)
-    stack = ms.MoeStack(kd, dev, cfg)
+    stack = ms.MoeStack(kd, dev, cfg, exchange=mode)
     g = torch.Generator(device=dev).manual_seed(cfg.seed)
     h0 = torch.randn(cfg.tokens, cfg.hidden, device=dev, generator=g).to(torch.bfloat16)
     out = stack.forward(h0)
     torch.cuda.synchronize()
     assert kd.device_status() == 0
     # same stack on the CPU checker
+    norm = lambda r: O.bf16_round(r / np.sqrt((r * r).mean(axis=1, keepdims=True) + 1e-6))
     h = h0.float().cpu().numpy()
+    x = norm(h)
     for l in range(cfg.layers):
-        wr = stack.routers[l].float().cpu().numpy()
-        logits = O.bf16_round((torch.from_numpy(h).to(torch.bfloat16).to(dev) @ stack.routers[l].t()).float().cpu().numpy())
+        logits = O.bf16_round((torch.from_numpy(x).to(torch.bfloat16).to(dev) @ stack.routers[l].t()).float().cpu().numpy())
         idx, wts = port.moe_route(logits, None, cfg.top_k, True)
         tg, tu, td = stack.layers[l]
         eb_g = cfg.ffn * (cfg.hidden // 256 * 144)
@@ -114,8 +131,25 @@ def test_two_layer_stack_matches_checker(kd, port):
         gate = [O.aligned_copy(gbuf[e * eb_g:(e + 1) * eb_g]) for e in range(cfg.experts)]
         up = [O.aligned_copy(ubuf[e * eb_g:(e + 1) * eb_g]) for e in range(cfg.experts)]
         down = [O.aligned_copy(dbuf[e * eb_d:(e + 1) * eb_d]) for e in range(cfg.experts)]
-        y = port.moe_ffn_int8(h, gate, up, down, idx, wts, cfg.ffn, bf16=True)
-        r = O.bf16_round(h + y)
-        h = O.bf16_round(r / np.sqrt((r * r).mean(axis=1, keepdims=True) + 1e-6))
+        y = port.moe_ffn_int8(x, gate, up, down, idx, wts, cfg.ffn, bf16=True)
+        h = O.bf16_round(h + y)
+        x = norm(h)
     got = out.float().cpu().numpy()
     assert np.abs(got - h).max() <= 2.0 ** -6 * np.abs(h).max()
+
+
+@pytest.mark.gpu
+def test_expert_parallel_stack_on_two_gpus(kd):
+    """The push exchange and the all-reduce design on two ranks (one process per GPU, peer memory through IPC
+    handles) against the same stack on one rank. Needs two GPUs."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import subprocess
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.join(ROOT, "bench.py"),
+                        "--gpus", "2", "--check-multi-rank"], capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    import json
+    line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["push"] <= 1e-3 and line["allreduce"] <= 2.0 ** -6 and line["device_status"] == 0, line
