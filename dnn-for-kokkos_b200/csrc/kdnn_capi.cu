@@ -379,7 +379,9 @@ int kdnn_b200_moe_block(const void* x, size_t ldx, size_t tokens_local, int scal
   if (world > 1 && expert_count == 0) return fail(KDNN_ERR_INVALID, "moe_block: every rank needs at least one expert");
   const size_t T = tokens_local * static_cast<size_t>(world);
   if (T * static_cast<size_t>(top_k) > static_cast<size_t>(INT_MAX) / 4) return fail(KDNN_ERR_INVALID, "moe_block: T*S too large");
-  if ((T + 31) / 32 * E * 8 + 16 * E > 160 * 1024) return KDNN_DECLINED;   // slot matrix beyond the one-CTA sort
+  if (world > 1 && (expert_count * static_cast<size_t>(world) != E || expert_first != static_cast<size_t>(rank) * expert_count))
+    return fail(KDNN_ERR_INVALID, "moe_block: with several ranks the experts split evenly, rank r owning [r*E/world, (r+1)*E/world)");
+  if (expert_count > 4096 || (H + 2 * E + 2 * static_cast<size_t>(top_k) + 512) * 4 + 16 * (H + 32) > 200 * 1024) return KDNN_DECLINED;
   if (workspace_bytes < kdnn::moe_block_workspace_bytes(tokens_local, world, top_k, H, F, E, ex == nullptr) ||
       (reinterpret_cast<uintptr_t>(workspace) & 255u))
     return fail(KDNN_ERR_INVALID, "moe_block: workspace too small or not 256-byte aligned");

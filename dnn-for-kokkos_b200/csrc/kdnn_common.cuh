@@ -217,7 +217,7 @@ __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* x, siz
   }
 }
 
-// ---- mbarrier + bulk copy (TMA 1-D, no multicast) ----------------------------
+// ---- mbarrier + bulk copy (TMA 1-D, one destination CTA) ----------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -316,6 +316,20 @@ inline cudaError_t launch_chained_if(bool early, void (*kern)(KArgs...), dim3 gr
   cfg.attrs = attr; cfg.numAttrs = early && pdl_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
+// The same with a thread-block cluster of `cluster` CTAs along x (grid.x must be a multiple of it).
+template <class... KArgs, class... Args>
+inline cudaError_t launch_chained_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, unsigned cluster,
+                                          cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 template <class... KArgs, class... Args>
 inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                                   Args&&... args) {
@@ -353,11 +367,12 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch,
   }
   return false;
 }
-// What the down-projection kernels need to hand their rows to the token owners and to tell them.
+// What the down-projection kernels of the MoE block need: where their rows go and whom to tell.
 struct PeerOut {
-  float* out[kMaxRanks];        // every rank's slot-indexed output rows [tokens_local * S][N]; null = plain position-indexed dst
+  float* out;                   // THIS rank's slot-indexed output rows [all tokens * S][N] (the token owners read
+                                // them from here); null = plain position-indexed dst
   uint32_t* oflag[kMaxRanks];   // every rank's "outputs of rank r are complete" flags [world]
-  int world, rank, tokens_local;
+  int world, rank;
   int* ticket;                  // grid-completion counter (this GPU), null when world == 1
   const uint32_t* epoch;        // this GPU's current epoch
 };
@@ -365,10 +380,9 @@ struct PeerOut {
 // publishes this rank's epoch to every rank's flag array.
 __device__ __forceinline__ void peer_out_finish(const PeerOut& po, unsigned total_ctas) {
   if (po.ticket == nullptr) return;
-  __threadfence();   // device scope by everybody, system scope by the one thread that takes the ticket
+  __threadfence();   // device scope by everybody, system scope by the one thread that raises the flags
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
     if (atomicAdd(po.ticket, 1) == static_cast<int>(total_ctas) - 1) {
       *po.ticket = 0;
       __threadfence_system();
@@ -377,10 +391,9 @@ __device__ __forceinline__ void peer_out_finish(const PeerOut& po, unsigned tota
     }
   }
 }
-// Destination of the output row of slot `slot` (token-major slot id over ALL tokens): the owner's buffer.
-__device__ __forceinline__ float* peer_out_row(const PeerOut& po, int slot, int S, int N) {
-  const int t = slot / S, owner = t / po.tokens_local;
-  return po.out[owner] + (static_cast<size_t>(t - owner * po.tokens_local) * S + (slot - t * S)) * N;
+// Output row of slot `slot` (token-major slot id over ALL tokens) in this rank's buffer.
+__device__ __forceinline__ float* peer_out_row(const PeerOut& po, int slot, int N) {
+  return po.out + static_cast<size_t>(slot) * N;
 }
 
 // Arguments of one MoE block call (kdnn_capi.cu validates and fills them, kdnn_moe.cu launches).

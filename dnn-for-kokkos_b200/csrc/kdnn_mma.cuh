@@ -37,7 +37,7 @@ struct MmaParams {
   int* status;
   int passes_z;          // CTAs along z that share a group's 32-row passes (0 = 1)
   int early;             // launch as a programmatic dependent (only worth it behind a tiny kernel, see launch_chained_if)
-  PeerOut po;            // MODE 0: po.out[0] != null sends the rows to the token owners' slot-indexed buffers
+  PeerOut po;            // MODE 0: po.out != null writes the rows into this rank's slot-indexed buffer (read by the token owners)
 };
 
 __device__ __forceinline__ int4 lds128_g(uint32_t a) {
@@ -389,8 +389,8 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
         ro = static_cast<long long>(srow) * static_cast<long long>(p.x_pitch);
       }
       rowp[threadIdx.x] = ro;
-      if (MODE == 0 && p.po.out[0] != nullptr)
-        outp[threadIdx.x] = threadIdx.x < nt ? peer_out_row(p.po, p.list[beg + t0 + threadIdx.x], p.S, p.N) : nullptr;
+      if (MODE == 0 && p.po.out != nullptr)
+        outp[threadIdx.x] = threadIdx.x < nt ? peer_out_row(p.po, p.list[beg + t0 + threadIdx.x], p.N) : nullptr;
     }
     __syncthreads();
     stage_chunk(0);
@@ -513,7 +513,7 @@ __global__ void __launch_bounds__(kM2Warps * 32, 2) grouped_mma2_q4k_kernel(cons
             if (MODE == 2) {
               const int srow = p.list[beg + t0 + tok] / p.S;
               store_scalar(static_cast<YT*>(p.dst) + static_cast<size_t>(srow) * p.ld_dst + j, acc[t][i]);
-            } else if (MODE == 0 && p.po.out[0] != nullptr) {
+            } else if (MODE == 0 && p.po.out != nullptr) {
               outp[tok][j] = acc[t][i];
             } else {
               static_cast<float*>(p.dst)[static_cast<size_t>(beg + t0 + tok) * p.N + j] = acc[t][i];

@@ -12,6 +12,7 @@
 //   5. tile GEMM, MODE 0    out[pos, d] = down_e[d,:] . act[pos,:]
 //   6. moe_combine_kernel   Y[t, d] = Scalar(sum_s w[t,s] * out[pos(t,s), d])
 // Workspace (caller-owned): offsets, slot list, slot positions, int8 items, act, out.
+#include <type_traits>
 #include "kdnn_grouped.cuh"
 #include "kdnn_mma.cuh"
 #include "kdnn_tc.cuh"
@@ -168,6 +169,88 @@ __device__ __forceinline__ void route_warp(GetLogit lg, GetBias bs, bool has_bia
   } else {
     for (int k = 0; k < top_k; ++k) w[k] = expf(logit(k) - gmx) / gsum * routed_scale;
   }
+}
+
+// The same selection and weights for E <= 256 and top_k <= 32 with the scores in registers (lane l holds the
+// experts l, l + 32, ...): a selection round is two warp reductions (largest score, then smallest expert id among
+// the lanes that hold it -- the reference's first-maximum rule), the weights are formed by lanes 0..top_k-1 in
+// parallel and summed in slot order. The global-softmax denominator (neither sigmoid nor norm_topk) is a lane-wise
+// then tree sum instead of the reference's sequential one: within 1e-6 relative of it.
+// On return lane k < top_k holds slot k: sel_e (expert id or -1) and sel_w.
+template <int J, class GetLogit, class GetBias>
+__device__ __forceinline__ void route_warp_regs(GetLogit lg, GetBias bs, bool has_bias, int E, int top_k, int norm_topk,
+                                                float routed_scale, int sigmoid, int lane, int& sel_e, float& sel_w) {
+  constexpr float NEG = -3.4028235e38f;   // J = experts per lane (E <= 32 * J)
+  float raw[J], bia[J], sc[J];
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int e = lane + 32 * j;
+    raw[j] = 0.f; bia[j] = 0.f; sc[j] = NEG;
+    if (e < E) {
+      raw[j] = lg(e);
+      bia[j] = has_bias ? bs(e) : 0.0f;
+      sc[j] = sigmoid ? (1.0f / (1.0f + expf(-raw[j]))) + bia[j] : raw[j] + bia[j];
+    }
+  }
+  float gmx = NEG, gsum = 0.0f;
+  if (!sigmoid && !norm_topk) {
+#pragma unroll
+    for (int j = 0; j < J; ++j)
+      if (lane + 32 * j < E && sc[j] > gmx) gmx = sc[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) gmx = fmaxf(gmx, __shfl_xor_sync(0xffffffffu, gmx, o));
+#pragma unroll
+    for (int j = 0; j < J; ++j)
+      if (lane + 32 * j < E) gsum += expf(sc[j] - gmx);
+    gsum = warp_sum(gsum);
+  }
+  const float raw0 = __shfl_sync(0xffffffffu, raw[0], 0), bia0 = __shfl_sync(0xffffffffu, bia[0], 0);
+  int my_e = -1;
+  float my_raw = raw0, my_b = bia0;   // an empty slot reads expert 0, like the reference's weight pass
+  for (int k = 0; k < top_k; ++k) {
+    float best = NEG, braw = 0.f, bb = 0.f;
+    int bj = -1;
+#pragma unroll
+    for (int j = 0; j < J; ++j)
+      if (sc[j] > best) { best = sc[j]; bj = j; braw = raw[j]; bb = bia[j]; }
+    const uint32_t u = __float_as_uint(best + 0.0f);
+    const uint32_t key = bj < 0 ? 0u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+    const uint32_t top = __reduce_max_sync(0xffffffffu, key);
+    const uint32_t mine = (top != 0u && key == top) ? static_cast<uint32_t>(lane + 32 * bj) : 0xffffffffu;
+    const uint32_t be = __reduce_min_sync(0xffffffffu, mine);
+    const int src = static_cast<int>(be & 31u);
+    const float wraw = __shfl_sync(0xffffffffu, braw, src), wb = __shfl_sync(0xffffffffu, bb, src);
+    if (be != 0xffffffffu) {
+      if (lane == src) {
+#pragma unroll
+        for (int j = 0; j < J; ++j)
+          if (j == static_cast<int>(be >> 5)) sc[j] = NEG;
+      }
+      if (lane == k) { my_e = static_cast<int>(be); my_raw = wraw; my_b = wb; }
+    }
+  }
+  const float l = sigmoid ? 1.0f / (1.0f + expf(-my_raw)) : my_raw + (has_bias ? my_b : 0.0f);
+  float wgt = 0.f;
+  if (sigmoid) {
+    if (norm_topk) {
+      float sum = 0.0f;
+      for (int k = 0; k < top_k; ++k) sum += __shfl_sync(0xffffffffu, l, k);
+      wgt = l / (sum + 1e-6f) * routed_scale;
+    } else {
+      wgt = l * routed_scale;
+    }
+  } else if (norm_topk) {
+    float mx = NEG;
+    for (int k = 0; k < top_k; ++k) mx = fmaxf(mx, __shfl_sync(0xffffffffu, l, k));
+    const float ex = expf(l - mx);
+    float sum = 0.0f;
+    for (int k = 0; k < top_k; ++k) sum += __shfl_sync(0xffffffffu, ex, k);
+    wgt = ex / sum * routed_scale;
+  } else {
+    wgt = expf(l - gmx) / gsum * routed_scale;
+  }
+  sel_e = my_e;
+  sel_w = wgt;
 }
 
 template <class ST>
@@ -742,8 +825,17 @@ cudaError_t residual_rmsnorm_launch(const void* h, size_t ldh, const float* y, s
 //   4. moe_combine_norm_kernel   waits for every rank's flag, sums the slots in slot order, adds the
 //                          residual and forms the next block's un-scaled RMS norm
 // Exchange region of one rank (all ranks use the same layout; T = tokens_local * world):
+//   xrows  [T] quantized token rows        written by every rank's gate kernel (its own tokens)
+//   idx    [T][S] routed expert ids        written by every rank's gate kernel (its own tokens)
+//   rel    [T][S] rank of the slot inside its expert's run on the expert's owner (only the owner's copy
+//                 of a slot's entry is written)
+//   wts    [T][S] routing weights          local use only (the owner's combine)
+//   out    [T][S][H] down-projection rows of the slots whose expert lives HERE; the token owners read them
+//   cnt    [kMaxLocalExperts] rows routed to each local expert this call (peers add with system-scope atomics)
+//   xflag / oflag  [world] epochs: "rank r's rows and routing are here" / "rank r's out rows are complete"
+constexpr size_t kMaxLocalExperts = 4096;
 struct ExLayout {
-  size_t xrows, idx, wts, out, xflag, oflag, total;
+  size_t xrows, idx, rel, wts, out, cnt, xflag, oflag, total;
 };
 static ExLayout ex_layout(size_t Tl, size_t world, size_t S, size_t H) {
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
@@ -752,8 +844,10 @@ static ExLayout ex_layout(size_t Tl, size_t world, size_t S, size_t H) {
   size_t o = 0;
   L.xrows = o; o += up(T * act_row_pitch(H));
   L.idx   = o; o += up(T * S * sizeof(int32_t));
+  L.rel   = o; o += up(T * S * sizeof(int32_t));
   L.wts   = o; o += up(T * S * sizeof(float));
-  L.out   = o; o += up(Tl * S * H * sizeof(float));
+  L.out   = o; o += up(T * S * H * sizeof(float));
+  L.cnt   = o; o += up(kMaxLocalExperts * sizeof(int));
   L.xflag = o; o += 256;
   L.oflag = o; o += 256;
   L.total = o;
@@ -763,129 +857,263 @@ size_t moe_exchange_bytes(size_t tokens_local, size_t world, size_t S, size_t H)
   return ex_layout(tokens_local, world, S, H).total;
 }
 
-constexpr int kGateThreads = 512;   // 16 warps: the logit loop lives on loads in flight
+constexpr int kGateThreads = 512;   // 16 warps
+constexpr int kGateCluster = 4;     // CTAs of one cluster split the experts of the logit product
 struct GateParams {
   const void* x; size_t ldx;
   const void* rw; size_t ldr; const void* bias;
   int Tl, H, E, top_k, norm_topk, sigmoid, world, rank;
   float routed_scale;
+  int e_per_rank;               // experts per rank (world > 1: E / world), owner of expert e = e / e_per_rank
   uint8_t* region[kMaxRanks];   // every rank's exchange region
   ExLayout L;
   size_t x_pitch;
-  PrepParams sort;              // the slot sort of the last CTA (over all T tokens, local experts)
+  int e_first, e_count;         // this rank's experts
+  int* offs; int* list; int4* groups; int* n_groups;   // outputs of the last CTA (this rank's workspace)
   int* ticket; uint32_t* epoch; int* status;
   unsigned long long wait_ns;
 };
 
-// TPC = tokens per CTA: 4 when this rank has many tokens (every CTA streams the whole router matrix from L2,
-// so fewer, fatter CTAs), 1 when it has few (more CTAs than a handful, so the kernel still shrinks with the
-// number of ranks).
-template <class ST, int kGateTokens>
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of `p` (a shared-memory pointer of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ float* cluster_map(float* p, unsigned rank) {
+  uint64_t out;
+  asm volatile("mapa.u64 %0, %1, %2;" : "=l"(out) : "l"(reinterpret_cast<uint64_t>(p)), "r"(rank));
+  return reinterpret_cast<float*>(out);
+}
+
+// One cluster of kGateCluster CTAs owns TPC tokens. Every CTA of the cluster holds the tokens' rows in
+// shared memory and forms the logits of ITS quarter of the experts (so a CTA streams a quarter of the
+// router matrix from L2); the logits land, through distributed shared memory, in the CTA that routes the
+// token (token i of the cluster belongs to CTA i % kGateCluster), which then also quantizes its row.
+template <class ST, int TPC>
 __global__ void __launch_bounds__(kGateThreads) moe_gate_kernel(const GateParams p) {
   pdl_chain_entry();
+  constexpr int C = kGateCluster, RT = (TPC + C - 1) / C, TH = TPC > 4 ? 4 : TPC;
   extern __shared__ __align__(16) uint8_t gate_smem[];
-  float* xs = reinterpret_cast<float*>(gate_smem);                       // [kGateTokens][H]
-  float* lgs = xs + static_cast<size_t>(kGateTokens) * p.H;              // [kGateTokens][E] rounded logits
-  float* score = lgs + static_cast<size_t>(kGateTokens) * p.E;           // [kGateTokens][E]
-  int32_t* ridx = reinterpret_cast<int32_t*>(score + static_cast<size_t>(kGateTokens) * p.E);   // [kGateTokens][top_k]
-  float* rwts = reinterpret_cast<float*>(ridx + kGateTokens * p.top_k);                          // [kGateTokens][top_k]
+  float* xs = reinterpret_cast<float*>(gate_smem);                       // [TPC][H]
+  float* lgs = xs + static_cast<size_t>(TPC) * p.H;                      // [RT][E] rounded logits of the tokens routed here
+  float* score = lgs + static_cast<size_t>(RT) * p.E;                    // [RT][E] (only the router for E > 256)
+  int32_t* ridx = reinterpret_cast<int32_t*>(score + static_cast<size_t>(RT) * p.E);   // [RT][top_k]
+  float* rwts = reinterpret_cast<float*>(ridx + RT * p.top_k);                          // [RT][top_k]
+  float* part = rwts + RT * p.top_k;                                     // [16 warps][TPC][32] partial logits
+  // bf16 tokens: a second copy of the rows as stored, [8][H + 32] (rows past nt are zero), for the tensor-core product
+  __nv_bfloat16* xb = reinterpret_cast<__nv_bfloat16*>(part + (kGateThreads / 32) * TPC * 32);
+  constexpr bool kTensor = std::is_same<ST, __nv_bfloat16>::value;
+  const int xb_pitch = p.H + 32;
   __shared__ int s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned crank = cluster_cta_rank();
   const uint32_t epoch = *p.epoch + 1u;                                  // this block call's epoch
-  const int t_first = blockIdx.x * kGateTokens;                          // local token index
-  const int nt = min(kGateTokens, p.Tl - t_first);
+  const int t_first = static_cast<int>(blockIdx.x / C) * TPC;            // local token index of the cluster's first token
+  const int nt = max(0, min(TPC, p.Tl - t_first));
   const ST* x = static_cast<const ST*>(p.x);
-  for (int i = threadIdx.x; i < nt * p.H; i += blockDim.x) {
-    const int t = i / p.H, k = i - t * p.H;
-    xs[t * p.H + k] = to_f32(x[static_cast<size_t>(t_first + t) * p.ldx + k]);
+  {
+    const int h8 = p.H / 8;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (p.ldx * sizeof(ST)) % 16 == 0;
+    for (int i = threadIdx.x; i < nt * h8; i += kGateThreads) {
+      const int t = i / h8, k = (i - t * h8) * 8;
+      float v[8];
+      load8<ST>(x + static_cast<size_t>(t_first + t) * p.ldx, static_cast<size_t>(k), vec_ok, v);
+      *reinterpret_cast<float4*>(xs + t * p.H + k) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(xs + t * p.H + k + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    for (int i = nt * p.H + threadIdx.x; i < TPC * p.H; i += kGateThreads) xs[i] = 0.f;
+    if (kTensor) {
+      for (int i = threadIdx.x; i < 8 * h8; i += kGateThreads) {
+        const int t = i / h8, k = (i - t * h8) * 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (t < nt) {
+          const ST* src = x + static_cast<size_t>(t_first + t) * p.ldx + k;
+          if (vec_ok) v = *reinterpret_cast<const uint4*>(src);
+          else memcpy(&v, src, 16);
+        }
+        *reinterpret_cast<uint4*>(xb + t * xb_pitch + k) = v;
+      }
+    }
   }
   __syncthreads();
-  // ---- router logits: a warp owns E / 16 experts, lanes along the hidden dimension ----
-  // Per 256-element chunk of K a lane takes its eight activations of every token into registers ONCE and
-  // then streams the matching 16 bytes of each of its experts' rows (four rows in flight) against them:
-  // shared memory is read once per chunk instead of once per expert, and the loop runs on loads in flight.
-  const ST* rw = static_cast<const ST*>(p.rw);
-  constexpr int kWarps = kGateThreads / 32;
-  for (int e0 = warp; e0 < p.E; e0 += 8 * kWarps) {        // this warp's experts e0, e0 + 16, ... (eight at a time)
-    float acc[8][kGateTokens];
+  // ---- router logits of this CTA's experts: lane = expert (32 at a time), warp = one sixteenth of the hidden
+  // dimension. A lane streams its expert's row piece 16 bytes at a time and meets the tokens' values as
+  // shared-memory broadcasts; partial sums (even and odd elements apart, packed fp32 FMA) go through shared
+  // memory and are added warp 0 first. The order is the same for every grid shape, so the logits do not
+  // depend on how many ranks share the tokens.
+  {
+    const ST* rw = static_cast<const ST*>(p.rw);
+    constexpr int kWarps = kGateThreads / 32;
+    const int Ec = (p.E + C - 1) / C, e_lo = static_cast<int>(crank) * Ec, e_hi = min(p.E, e_lo + Ec);
+    const int kw = p.H / kWarps, k_lo = warp * kw;          // this warp's piece of K (a multiple of 16 elements)
+    if (kTensor) {
+      // bf16: the product runs on the tensor cores (mma.sync m16n8k16, fp32 accumulators): experts are the M
+      // rows, the (up to eight) tokens the N columns. A lane takes 16 bytes of an expert row and of a token row
+      // at the same place, which is the fragment of TWO k-steps under one fixed permutation of the 32 elements
+      // of that piece of K (the same permutation on both operands leaves the dot product unchanged).
+      const int g = lane >> 2, tq = lane & 3;
+      const __nv_bfloat16* rwb = reinterpret_cast<const __nv_bfloat16*>(rw);
+      for (int eb = e_lo; eb < e_hi; eb += 32) {
+        float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        for (int k = 0; k < kw; k += 128) {               // up to four 32-element pieces with all loads in flight
+          uint4 av[4][2][2];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+          for (int u = 0; u < 4; ++u)
 #pragma unroll
-      for (int t = 0; t < kGateTokens; ++t) acc[j][t] = 0.f;
-    for (int k = lane * 8; k < p.H; k += 256) {
-      float xv[kGateTokens][8];
+            for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int t = 0; t < kGateTokens; ++t) {
-        const float4 a = *reinterpret_cast<const float4*>(xs + t * p.H + k);
-        const float4 b = *reinterpret_cast<const float4*>(xs + t * p.H + k + 4);
-        xv[t][0] = a.x; xv[t][1] = a.y; xv[t][2] = a.z; xv[t][3] = a.w;
-        xv[t][4] = b.x; xv[t][5] = b.y; xv[t][6] = b.z; xv[t][7] = b.w;
+              for (int hh = 0; hh < 2; ++hh) {
+                const int er = min(eb + 16 * mt + 8 * hh + g, e_hi - 1);
+                const int kk = k + 32 * u < kw ? k + 32 * u : k;
+                av[u][mt][hh] = *reinterpret_cast<const uint4*>(rwb + static_cast<size_t>(er) * p.ldr + k_lo + kk + 8 * tq);
+              }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (k + 32 * u >= kw) break;
+            const uint4 bv = *reinterpret_cast<const uint4*>(xb + g * xb_pitch + k_lo + k + 32 * u + 8 * tq);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+              const uint4 lo = av[u][mt][0], hi = av[u][mt][1];
+              asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                           : "+f"(d[mt][0]), "+f"(d[mt][1]), "+f"(d[mt][2]), "+f"(d[mt][3])
+                           : "r"(lo.x), "r"(hi.x), "r"(lo.y), "r"(hi.y), "r"(bv.x), "r"(bv.y));
+              asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                           : "+f"(d[mt][0]), "+f"(d[mt][1]), "+f"(d[mt][2]), "+f"(d[mt][3])
+                           : "r"(lo.z), "r"(hi.z), "r"(lo.w), "r"(hi.w), "r"(bv.z), "r"(bv.w));
+            }
+          }
+        }
+        __syncthreads();                                     // `part` free again (previous block of experts)
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int tok = 2 * tq + (i & 1), el = 16 * mt + 8 * (i >> 1) + g;
+            if (tok < TPC) part[(warp * TPC + tok) * 32 + el] = d[mt][i];
+          }
+        __syncthreads();
+        for (int i = threadIdx.x; i < TPC * 32; i += kGateThreads) {
+          const int t = i >> 5, el = i & 31;
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) v += part[(w * TPC + t) * 32 + el];
+          if (t < nt && eb + el < e_hi) {
+            ST r;
+            store_scalar(&r, v);          // the logits reach the router in the Scalar type
+            cluster_map(lgs, static_cast<unsigned>(t % C))[(t / C) * p.E + eb + el] = to_f32(r);
+          }
+        }
       }
+    } else
+    for (int eb = e_lo; eb < e_hi; eb += 32) {
+      const int e = eb + lane;
+      const bool live = e < e_hi;
+      const ST* row = rw + static_cast<size_t>(live ? e : eb) * p.ldr + k_lo;
+      float2 acc[TPC];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int t = 0; t < TPC; ++t) acc[t] = make_float2(0.f, 0.f);
+      for (int k = 0; k < kw; k += 32) {
         float wv[4][8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int e = e0 + (4 * h + j) * kWarps;
+        for (int u = 0; u < 4; ++u) load8<ST>(row, static_cast<size_t>(k + 8 * u < kw ? k + 8 * u : k), true, wv[u]);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) wv[j][i] = 0.f;
-          if (e < p.E) load8<ST>(rw + static_cast<size_t>(e) * p.ldr, static_cast<size_t>(k), true, wv[j]);
+        for (int u = 0; u < 4; ++u) {
+          if (k + 8 * u >= kw) break;
+#pragma unroll
+          for (int t = 0; t < TPC; ++t) {
+            const float4 xa = *reinterpret_cast<const float4*>(xs + t * p.H + k_lo + k + 8 * u);
+            const float4 xb = *reinterpret_cast<const float4*>(xs + t * p.H + k_lo + k + 8 * u + 4);
+            float2 a = acc[t];
+            a = ffma2(make_float2(wv[u][0], wv[u][1]), make_float2(xa.x, xa.y), a);
+            a = ffma2(make_float2(wv[u][2], wv[u][3]), make_float2(xa.z, xa.w), a);
+            a = ffma2(make_float2(wv[u][4], wv[u][5]), make_float2(xb.x, xb.y), a);
+            a = ffma2(make_float2(wv[u][6], wv[u][7]), make_float2(xb.z, xb.w), a);
+            acc[t] = a;
+          }
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int t = 0; t < kGateTokens; ++t)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[4 * h + j][t] = fmaf(wv[j][i], xv[t][i], acc[4 * h + j][t]);
       }
-    }
+      __syncthreads();                                       // `part` free again (previous block of experts)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int e = e0 + j * kWarps;
+      for (int t = 0; t < TPC; ++t) part[(warp * TPC + t) * 32 + lane] = acc[t].x + acc[t].y;
+      __syncthreads();
+      for (int i = threadIdx.x; i < TPC * 32; i += kGateThreads) {
+        const int t = i >> 5, el = i & 31;
+        float v = 0.f;
 #pragma unroll
-      for (int t = 0; t < kGateTokens; ++t) {
-        const float v = warp_sum(acc[j][t]);
-        if (lane == 0 && e < p.E) {
+        for (int w = 0; w < kWarps; ++w) v += part[(w * TPC + t) * 32 + el];
+        if (t < nt && eb + el < e_hi) {
           ST r;
           store_scalar(&r, v);          // the logits reach the router in the Scalar type
-          lgs[t * p.E + e] = to_f32(r);
+          cluster_map(lgs, static_cast<unsigned>(t % C))[(t / C) * p.E + eb + el] = to_f32(r);
         }
       }
     }
   }
-  __syncthreads();
-  // ---- routing: one warp per token; results into every rank's region ----
+  cluster_sync_all();
+  // ---- routing: one warp per token of this CTA (cluster token crank + C * warp) ----
   const ST* bias = static_cast<const ST*>(p.bias);
-  if (warp < nt) {
-    const int tg = p.rank * p.Tl + t_first + warp;   // global token index
-    int32_t* my_idx = ridx + warp * p.top_k;         // selection and weights in shared memory (the weight pass
-    float* my_w = rwts + warp * p.top_k;             // reads the ids back several times), then out to every rank
+  const int my_tokens = nt > static_cast<int>(crank) ? (nt - static_cast<int>(crank) + C - 1) / C : 0;
+  if (warp < my_tokens) {
+    const int tl = t_first + static_cast<int>(crank) + C * warp;   // local token index
+    const int tg = p.rank * p.Tl + tl;                              // global token index
     const float* lgt = lgs + warp * p.E;
-    route_warp([&](int e) { return lgt[e]; }, [&](int e) { return to_f32(bias[e]); }, bias != nullptr, p.E, p.top_k,
-               p.norm_topk, p.routed_scale, p.sigmoid, score + warp * p.E, my_idx, my_w, lane);
-    __syncwarp();
-    for (int r = 0; r < p.world; ++r) {
-      int32_t* di = reinterpret_cast<int32_t*>(p.region[r] + p.L.idx) + static_cast<size_t>(tg) * p.top_k;
-      float* dw = reinterpret_cast<float*>(p.region[r] + p.L.wts) + static_cast<size_t>(tg) * p.top_k;
-      for (int k = lane; k < p.top_k; k += 32) {
-        di[k] = my_idx[k];
-        dw[k] = my_w[k];
+    int e = -1;
+    float wk = 0.f;
+    if (p.E <= 256 && p.top_k <= 32) {
+      if (p.E <= 128)
+        route_warp_regs<4>([&](int i) { return lgt[i]; }, [&](int i) { return to_f32(bias[i]); }, bias != nullptr, p.E,
+                           p.top_k, p.norm_topk, p.routed_scale, p.sigmoid, lane, e, wk);
+      else
+        route_warp_regs<8>([&](int i) { return lgt[i]; }, [&](int i) { return to_f32(bias[i]); }, bias != nullptr, p.E,
+                           p.top_k, p.norm_topk, p.routed_scale, p.sigmoid, lane, e, wk);
+    } else {
+      int32_t* my_idx = ridx + warp * p.top_k;
+      float* my_w = rwts + warp * p.top_k;
+      route_warp([&](int i) { return lgt[i]; }, [&](int i) { return to_f32(bias[i]); }, bias != nullptr, p.E, p.top_k,
+                 p.norm_topk, p.routed_scale, p.sigmoid, score + warp * p.E, my_idx, my_w, lane);
+      __syncwarp();
+    }
+    for (int k = lane; k < p.top_k; k += 32) {
+      if (!(p.E <= 256 && p.top_k <= 32)) { e = ridx[warp * p.top_k + k]; wk = rwts[warp * p.top_k + k]; }
+      const size_t slot = static_cast<size_t>(tg) * p.top_k + k;
+      reinterpret_cast<float*>(p.region[p.rank] + p.L.wts)[slot] = wk;
+      for (int r = 0; r < p.world; ++r) reinterpret_cast<int32_t*>(p.region[r] + p.L.idx)[slot] = e;
+      if (e >= 0 && e < p.E) {
+        // the slot takes the next row of its expert on the expert's owner
+        const int owner = p.world > 1 ? e / p.e_per_rank : 0;
+        const int el = e - (p.world > 1 ? owner * p.e_per_rank : p.e_first);
+        if (el >= 0 && el < (p.world > 1 ? p.e_per_rank : p.e_count)) {
+          int* cnt = reinterpret_cast<int*>(p.region[owner] + p.L.cnt) + el;
+          const int rel = owner == p.rank ? atomicAdd(cnt, 1) : atomicAdd_system(cnt, 1);
+          reinterpret_cast<int32_t*>(p.region[owner] + p.L.rel)[slot] = rel;
+        }
       }
     }
   }
-  // ---- per-32 quantization of the token rows (the reference's stage-1 quantizer), to every rank ----
+  // ---- per-32 quantization of this CTA's token rows (the reference's stage-1 quantizer), to every rank ----
   {
     const int nblk = p.H / 32, per_row = (nblk + 7) / 8, l4 = lane & 3;
-    for (int it = warp; it < nt * per_row; it += kGateThreads / 32) {
-      const int t = it / per_row, b = (it - t * per_row) * 8 + (lane >> 2);
+    for (int it = warp; it < my_tokens * per_row; it += kGateThreads / 32) {
+      const int tq = it / per_row, b = (it - tq * per_row) * 8 + (lane >> 2);
+      const int tc = static_cast<int>(crank) + C * tq;   // token of the cluster
       float v[8];
+      if (b < nblk) {
+        const float4 a = *reinterpret_cast<const float4*>(xs + tc * p.H + b * 32 + l4 * 8);
+        const float4 c = *reinterpret_cast<const float4*>(xs + tc * p.H + b * 32 + l4 * 8 + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+      } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = b < nblk ? xs[t * p.H + b * 32 + l4 * 8 + i] : 0.f;
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      }
       float d;
       int part, total;
       const uint2 packed = quantize_block_lane8(v, d, part, total);
       if (b >= nblk) continue;
-      const size_t row_off = p.L.xrows + static_cast<size_t>(p.rank * p.Tl + t_first + t) * p.x_pitch;
+      const size_t row_off = p.L.xrows + static_cast<size_t>(p.rank * p.Tl + t_first + tc) * p.x_pitch;
       const float ds = __fmul_rn(static_cast<float>(total), d);
       for (int r = 0; r < p.world; ++r) {
         uint8_t* out = p.region[r] + row_off;
@@ -898,7 +1126,7 @@ __global__ void __launch_bounds__(kGateThreads) moe_gate_kernel(const GateParams
       }
     }
   }
-  // ---- the last CTA: tell the peers, wait for them, sort ----
+  // ---- the last CTA: tell the peers, wait for them, turn the counts into runs ----
   // every thread's stores are ordered at device scope before the CTA's barrier; one thread then extends the
   // order to system scope (the peers) before it takes the ticket -- a system-scope fence by every thread of
   // every CTA costs tens of microseconds
@@ -920,7 +1148,89 @@ __global__ void __launch_bounds__(kGateThreads) moe_gate_kernel(const GateParams
     }
     __syncthreads();
   }
-  moe_sort_block(p.sort, reinterpret_cast<uint32_t*>(gate_smem));
+  // counts -> exclusive prefix sums (runs and 32-row groups), by one warp, 32 experts per step; the counts are
+  // cleared for the next call (no peer touches them before this rank's down kernel of THIS call has signalled)
+  int* starts = reinterpret_cast<int*>(gate_smem);   // [e_count + 1]  (the token rows are no longer needed)
+  int* cnt = reinterpret_cast<int*>(p.region[p.rank] + p.L.cnt);
+  const int n_slots = p.Tl * p.world * p.top_k;
+  // the first 4 * 512 slots' expert and rank are fetched now, together with the counts: one trip to L2, not two
+  const int32_t* idx = reinterpret_cast<const int32_t*>(p.region[p.rank] + p.L.idx);
+  const int32_t* rel = reinterpret_cast<const int32_t*>(p.region[p.rank] + p.L.rel);
+  int ev0[4], rv0[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = threadIdx.x + u * kGateThreads;
+    ev0[u] = i < n_slots ? __ldcg(idx + i) - p.e_first : -1;
+    rv0[u] = i < n_slots ? __ldcg(rel + i) : 0;
+  }
+  if (warp == 0) {
+    int run = 0, grun = 0;
+    int pre[8];   // the first 256 counts are fetched together
+#pragma unroll
+    for (int j = 0; j < 8; ++j) pre[j] = lane + 32 * j < p.e_count ? __ldcg(cnt + lane + 32 * j) : 0;
+    for (int eb = 0; eb < p.e_count; eb += 32) {
+      const int e = eb + lane;
+      int c = 0;
+      if (e < p.e_count) {
+        int raw = 0;
+        if (eb < 256) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j == (eb >> 5)) raw = pre[j];
+        } else {
+          raw = __ldcg(cnt + e);
+        }
+        c = min(max(raw, 0), n_slots);
+        cnt[e] = 0;
+      }
+      const int gc = (c + kTcNT - 1) / kTcNT;
+      int incl = c, gincl = gc;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, o), gv = __shfl_up_sync(0xFFFFFFFFu, gincl, o);
+        if (lane >= o) { incl += v; gincl += gv; }
+      }
+      if (e < p.e_count) {
+        const int st = run + incl - c, g0 = grun + gincl - gc;
+        starts[e] = st;
+        p.offs[e] = st;
+        for (int q = 0; q * kTcNT < c; ++q)
+          p.groups[g0 + q] = make_int4(p.e_first + e, st + q * kTcNT, min(kTcNT, c - q * kTcNT), 0);
+      }
+      run += __shfl_sync(0xFFFFFFFFu, incl, 31);
+      grun += __shfl_sync(0xFFFFFFFFu, gincl, 31);
+    }
+    if (lane == 0) {
+      starts[p.e_count] = run;
+      p.offs[p.e_count] = run;
+      *p.n_groups = grun;
+    }
+  }
+  __syncthreads();
+  {
+    const int total = starts[p.e_count];
+    for (int i0 = threadIdx.x; i0 < n_slots; i0 += 4 * kGateThreads) {
+      int ev[4], rv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kGateThreads;
+        if (i0 == static_cast<int>(threadIdx.x)) {
+          ev[u] = ev0[u]; rv[u] = rv0[u];
+        } else {
+          ev[u] = i < n_slots ? __ldcg(idx + i) - p.e_first : -1;
+          rv[u] = i < n_slots ? __ldcg(rel + i) : 0;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kGateThreads;
+        if (ev[u] >= 0 && ev[u] < p.e_count) {
+          const int ps = starts[ev[u]] + rv[u];
+          if (ps >= starts[ev[u]] && ps < starts[ev[u] + 1] && ps < total) p.list[ps] = i;
+        }
+      }
+    }
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     *p.epoch = epoch;
@@ -935,8 +1245,9 @@ __global__ void __launch_bounds__(kGateThreads) moe_gate_kernel(const GateParams
 //   h_out = Scalar(float(resid) + Y),  xn_out = Scalar(h_out / sqrt(mean(h_out^2) + eps)).
 // One CTA per local token. With world > 1 the CTA first waits (bounded) for every rank's output flag.
 struct CombineParams {
-  const float* out; const int32_t* idx; const float* wts;   // this rank's region: out [Tl*S][H], idx/wts of ALL tokens
-  int Tl, S, H, e_lo, e_hi, world, rank;   // slots of experts in [e_lo, e_hi) have a row in `out`
+  const float* out[kMaxRanks];             // every rank's slot-indexed rows [T*S][H] (a slot's row lives on its expert's owner)
+  const int32_t* idx; const float* wts;    // this rank's region, [T][S]
+  int Tl, S, H, e_lo, e_hi, e_per_rank, world, rank;   // slots of experts in [e_lo, e_hi) have a row; owner = e / e_per_rank
   const uint32_t* oflag; const uint32_t* epoch; int* status;
   unsigned long long wait_ns;
   float* y; size_t ldy;
@@ -962,12 +1273,26 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const CombinePara
   float ss = 0.f;
   for (int d = threadIdx.x * 4; d < p.H; d += blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < p.S; ++s) {
-      const int e = idx[s];
-      const float w = wts[s];
-      if (e < p.e_lo || e >= p.e_hi || w == 0.0f) continue;
-      const float4 v = *reinterpret_cast<const float4*>(p.out + (static_cast<size_t>(t) * p.S + s) * p.H + d);
-      acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    for (int s0 = 0; s0 < p.S; s0 += 8) {        // eight rows in flight (they may come over NVLink), summed in slot order
+      float4 v[8];
+      float w[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int s = s0 + u;
+        const int e = s < p.S ? idx[s] : -1;
+        w[u] = s < p.S ? wts[s] : 0.0f;
+        if (e < p.e_lo || e >= p.e_hi) w[u] = 0.0f;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (w[u] != 0.0f) {
+          const float* src = p.out[p.world > 1 ? e / p.e_per_rank : 0];
+          v[u] = __ldcg(reinterpret_cast<const float4*>(src + (static_cast<size_t>(tg) * p.S + s) * p.H + d));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (w[u] == 0.0f) continue;
+        acc.x += w[u] * v[u].x; acc.y += w[u] * v[u].y; acc.z += w[u] * v[u].z; acc.w += w[u] * v[u].w;
+      }
     }
     if (p.y) *reinterpret_cast<float4*>(p.y + static_cast<size_t>(t) * p.ldy + d) = acc;
     if (resid) {
@@ -1045,33 +1370,38 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
   g.world = a.world; g.rank = a.rank; g.routed_scale = a.routed_scale;
   for (size_t r = 0; r < world; ++r) g.region[r] = regions[r];
   g.L = XL; g.x_pitch = act_row_pitch(H);
-  g.sort.idx = reinterpret_cast<const int32_t*>(mine + XL.idx); g.sort.n_slots = (int)(T * S); g.sort.S = (int)S;
-  g.sort.e_first = (int)a.e_first; g.sort.e_count = (int)a.e_count; g.sort.words = (int)((T + 31) / 32);
-  g.sort.offs = reinterpret_cast<int*>(b + L.offs); g.sort.list = reinterpret_cast<int*>(b + L.list);
-  g.sort.pos = reinterpret_cast<int*>(b + L.pos); g.sort.groups = reinterpret_cast<int4*>(b + L.groups);
-  g.sort.n_groups = reinterpret_cast<int*>(b + L.ngroups); g.sort.X = nullptr; g.sort.T = (int)T; g.sort.H = (int)H;
+  g.e_per_rank = a.world > 1 ? (int)a.e_count : 0; g.e_first = (int)a.e_first; g.e_count = (int)a.e_count;
+  g.offs = reinterpret_cast<int*>(b + L.offs); g.list = reinterpret_cast<int*>(b + L.list);
+  g.groups = reinterpret_cast<int4*>(b + L.groups); g.n_groups = reinterpret_cast<int*>(b + L.ngroups);
   g.ticket = sync; g.epoch = reinterpret_cast<uint32_t*>(sync + 2); g.status = status; g.wait_ns = a.wait_ns;
-  const int tpc = a.Tl >= 256 ? 4 : a.Tl >= 96 ? 2 : 1;
-  const size_t gsm = std::max((size_t)tpc * (H + 2 * E + 2 * S) * sizeof(float), moe_sort_smem(a.e_count, T));
+  // tokens per cluster: about 128 CTAs whatever the token count (a CTA streams a quarter of the router matrix)
+  int tpc = a.Tl >= 256 ? 8 : a.Tl >= 128 ? 4 : a.Tl >= 64 ? 2 : 1;
+  auto gate_smem = [&](int n) {
+    const size_t rt = (n + kGateCluster - 1) / kGateCluster;
+    return std::max(((size_t)n * H + rt * (2 * E + 2 * S) + (size_t)(kGateThreads / 32) * n * 32) * sizeof(float),
+                    (a.e_count + 1) * sizeof(int)) + (a.scalar == KDNN_BF16 ? 8 * (H + 32) * 2 : 0);
+  };
+  while (tpc > 1 && gate_smem(tpc) > 200 * 1024) tpc >>= 1;
+  const size_t gsm = gate_smem(tpc);
   using GateKern = void (*)(const GateParams);
   const bool f32 = a.scalar == KDNN_F32;
-  const GateKern gk = tpc == 4 ? (f32 ? moe_gate_kernel<float, 4> : moe_gate_kernel<__nv_bfloat16, 4>)
+  const GateKern gk = tpc == 8 ? (f32 ? moe_gate_kernel<float, 8> : moe_gate_kernel<__nv_bfloat16, 8>)
+                    : tpc == 4 ? (f32 ? moe_gate_kernel<float, 4> : moe_gate_kernel<__nv_bfloat16, 4>)
                     : tpc == 2 ? (f32 ? moe_gate_kernel<float, 2> : moe_gate_kernel<__nv_bfloat16, 2>)
                                : (f32 ? moe_gate_kernel<float, 1> : moe_gate_kernel<__nv_bfloat16, 1>);
   if (gsm > 48 * 1024) {
     err = cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsm);
     if (err != cudaSuccess) return err;
   }
-  err = launch_chained(gk, dim3((unsigned)((a.Tl + tpc - 1) / tpc)), dim3(kGateThreads), gsm, st, g);
+  err = launch_chained_cluster(gk, dim3((unsigned)((a.Tl + tpc - 1) / tpc) * kGateCluster), dim3(kGateThreads), gsm,
+                               kGateCluster, st, g);
   if (err != cudaSuccess) return err;
 
   // ---- expert tiles over all T tokens' slots, local experts ----
   PeerOut po{};
-  for (size_t r = 0; r < world; ++r) {
-    po.out[r] = reinterpret_cast<float*>(regions[r] + XL.out);
-    po.oflag[r] = reinterpret_cast<uint32_t*>(regions[r] + XL.oflag);
-  }
-  po.world = a.world; po.rank = a.rank; po.tokens_local = (int)a.Tl;
+  po.out = reinterpret_cast<float*>(mine + XL.out);
+  for (size_t r = 0; r < world; ++r) po.oflag[r] = reinterpret_cast<uint32_t*>(regions[r] + XL.oflag);
+  po.world = a.world; po.rank = a.rank;
   po.ticket = a.world > 1 ? sync + 1 : nullptr;
   po.epoch = reinterpret_cast<const uint32_t*>(sync + 2);
   if (a.e_count > 0) {
@@ -1123,7 +1453,8 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
   }
   // ---- combine on the token owner ----
   CombineParams c{};
-  c.out = reinterpret_cast<const float*>(mine + XL.out);
+  for (size_t r = 0; r < world; ++r) c.out[r] = reinterpret_cast<const float*>(regions[r] + XL.out);
+  c.e_per_rank = a.world > 1 ? (int)a.e_count : 1;
   c.idx = reinterpret_cast<const int32_t*>(mine + XL.idx); c.wts = reinterpret_cast<const float*>(mine + XL.wts);
   c.Tl = (int)a.Tl; c.S = (int)S; c.H = (int)H; c.world = a.world; c.rank = a.rank;
   c.e_lo = a.world > 1 ? 0 : (int)a.e_first; c.e_hi = a.world > 1 ? (int)E : (int)(a.e_first + a.e_count);

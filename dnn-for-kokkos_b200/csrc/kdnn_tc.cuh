@@ -7,7 +7,7 @@
 //
 //   warp 24      producer: per 256-element super-block of K one stage of the ring =
 //                128 packed rows x 144 bytes by tensor-map TMA (cp.async.bulk.tensor.2d,
-//                32-row boxes, this GPU's memory only, no multicast)
+//                32-row boxes, this GPU's memory only, one destination CTA)
 //   warps 16-23  unpack: thread = (weight row, half of its sub-blocks); nibbles -> int8 in the K-major core-matrix
 //                layout the MMA reads (eight 128 x 32 A tiles per stage), the 6-bit scales
 //                and mins -> fp32 tables; the group's quantized activations (a few KB per stage,
@@ -67,7 +67,7 @@ struct alignas(64) TcParams {
   size_t q_pitch;
   int* status;
   int32_t* dots;              // debug/parity: when set, raw int32 sub-block dots [pos][N][K/32] are stored too
-  PeerOut po;                 // MODE 0: po.out[0] != null sends the rows to the token owners' slot-indexed buffers
+  PeerOut po;                 // MODE 0: po.out != null writes the rows into this rank's slot-indexed buffer (read by the token owners)
 };
 
 
@@ -644,8 +644,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) grouped_tc_q4k_kernel(const __g
               if (MODE == 2) {
                 const int srow = ld_dep(p.list + ps) / p.S;
                 store_scalar(static_cast<YT*>(p.dst) + static_cast<size_t>(srow) * p.ld_dst + jrow, acc[c]);
-              } else if (MODE == 0 && p.po.out[0] != nullptr) {
-                peer_out_row(p.po, ld_dep(p.list + ps), p.S, p.N)[jrow] = acc[c];
+              } else if (MODE == 0 && p.po.out != nullptr) {
+                peer_out_row(p.po, ld_dep(p.list + ps), p.N)[jrow] = acc[c];
               } else {
                 static_cast<float*>(p.dst)[static_cast<size_t>(ps) * p.N + jrow] = acc[c];
               }
