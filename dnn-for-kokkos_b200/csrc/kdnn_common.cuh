@@ -380,15 +380,19 @@ struct PeerOut {
 // publishes this rank's epoch to every rank's flag array.
 __device__ __forceinline__ void peer_out_finish(const PeerOut& po, unsigned total_ctas) {
   if (po.ticket == nullptr) return;
-  __threadfence();   // device scope by everybody, system scope by the one thread that raises the flags
+  __shared__ int s_fin;
+  __threadfence();   // device scope by everybody, system scope by the threads that raise the flags
   __syncthreads();
   if (threadIdx.x == 0) {
-    if (atomicAdd(po.ticket, 1) == static_cast<int>(total_ctas) - 1) {
-      *po.ticket = 0;
-      __threadfence_system();
-      const uint32_t e = *po.epoch;
-      for (int r = 0; r < po.world; ++r) st_release_sys(po.oflag[r] + po.rank, e);
-    }
+    s_fin = atomicAdd(po.ticket, 1) == static_cast<int>(total_ctas) - 1;
+    if (s_fin) *po.ticket = 0;
+  }
+  __syncthreads();
+  // one thread per peer, so that the release fences run side by side: one thread storing to eight peers
+  // in turn spent 2 us per peer
+  if (s_fin && static_cast<int>(threadIdx.x) < po.world) {
+    __threadfence();
+    st_release_sys(po.oflag[threadIdx.x] + po.rank, *po.epoch);
   }
 }
 // Output row of slot `slot` (token-major slot id over ALL tokens) in this rank's buffer.

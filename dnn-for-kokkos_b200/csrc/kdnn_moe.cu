@@ -1140,7 +1140,7 @@ __global__ void __launch_bounds__(kGateThreads) moe_gate_kernel(const GateParams
   if (!s_last) return;
   __threadfence();
   if (p.world > 1) {
-    if (threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank)
+    if (threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank)   // one thread per peer: the fences overlap
       st_release_sys(reinterpret_cast<uint32_t*>(p.region[threadIdx.x] + p.L.xflag) + p.rank, epoch);
     if (threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank) {
       if (!wait_epoch(reinterpret_cast<const uint32_t*>(p.region[p.rank] + p.L.xflag) + threadIdx.x, epoch, p.wait_ns))
@@ -1255,20 +1255,27 @@ struct CombineParams {
   float eps;
 };
 template <class ST>
-__global__ void __launch_bounds__(256) moe_combine_norm_kernel(const CombineParams p) {
+__global__ void __launch_bounds__(512) moe_combine_norm_kernel(const CombineParams p) {
   pdl_chain_entry();
   extern __shared__ float comb_smem[];   // [H] the row after the residual add
   __shared__ float red[32];
+  __shared__ int s_e[64];
+  __shared__ float s_w[64];
   const int t = blockIdx.x;
-  if (p.world > 1) {
-    if (threadIdx.x < p.world) {
-      if (!wait_epoch(p.oflag + threadIdx.x, *p.epoch, p.wait_ns)) atomicExch(p.status, KDNN_ERR_DEVICE_WAIT);
-    }
-    __syncthreads();
-  }
   const int tg = p.rank * p.Tl + t;
   const int32_t* idx = p.idx + static_cast<size_t>(tg) * p.S;
   const float* wts = p.wts + static_cast<size_t>(tg) * p.S;
+  const bool cached = p.S <= 64;         // the token's routing (written by this rank's gate kernel) is read before the wait
+  if (cached && static_cast<int>(threadIdx.x) < p.S) {
+    s_e[threadIdx.x] = idx[threadIdx.x];
+    s_w[threadIdx.x] = wts[threadIdx.x];
+  }
+  if (p.world > 1) {
+    if (static_cast<int>(threadIdx.x) < p.world) {
+      if (!wait_epoch(p.oflag + threadIdx.x, *p.epoch, p.wait_ns)) atomicExch(p.status, KDNN_ERR_DEVICE_WAIT);
+    }
+  }
+  __syncthreads();
   const ST* resid = static_cast<const ST*>(p.resid);
   float ss = 0.f;
   for (int d = threadIdx.x * 4; d < p.H; d += blockDim.x * 4) {
@@ -1279,8 +1286,8 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const CombinePara
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int s = s0 + u;
-        const int e = s < p.S ? idx[s] : -1;
-        w[u] = s < p.S ? wts[s] : 0.0f;
+        const int e = s < p.S ? (cached ? s_e[s] : idx[s]) : -1;
+        w[u] = s < p.S ? (cached ? s_w[s] : wts[s]) : 0.0f;
         if (e < p.e_lo || e >= p.e_hi) w[u] = 0.0f;
         v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (w[u] != 0.0f) {
@@ -1463,7 +1470,8 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
   c.y = a.y; c.ldy = a.ldy; c.resid = a.resid; c.ldres = a.ldres; c.h_out = a.h_out; c.ldh = a.ldh;
   c.xn_out = a.xn_out; c.ldxn = a.ldxn; c.eps = a.eps;
   auto ck = a.scalar == KDNN_F32 ? moe_combine_norm_kernel<float> : moe_combine_norm_kernel<__nv_bfloat16>;
-  return launch_chained(ck, dim3((unsigned)a.Tl), dim3(256), H * sizeof(float), st, c);
+  const unsigned cthreads = (unsigned)std::min<size_t>(512, std::max<size_t>(128, (H / 4 + 31) / 32 * 32));
+  return launch_chained(ck, dim3((unsigned)a.Tl), dim3(cthreads), H * sizeof(float), st, c);
 }
 
 void moe_block_routing(void* const* regions, int rank, void* ws, size_t Tl, size_t world, size_t S, size_t H, size_t F,
