@@ -36,7 +36,7 @@ F32, BF16 = 0, 1
 # every symbol include/kdnn_b200.h declares (checked by the CPU test-suite)
 EXPORTS = [
     "kdnn_b200_last_error", "kdnn_b200_device_status", "kdnn_b200_gemv_scratch_bytes",
-    "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quant_gemv_ex", "kdnn_b200_quant_gemv_noalloc",
+    "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quant_gemv_ex", "kdnn_b200_quant_gemv_multi", "kdnn_b200_launch_chaining", "kdnn_b200_quant_gemv_noalloc",
     "kdnn_b200_quant_gemv_noalloc_ex", "kdnn_b200_quantize_act_q8", "kdnn_b200_quant_gemm_dots", "kdnn_b200_tile_kind",
     "kdnn_b200_weight_table_tma_bytes", "kdnn_b200_weight_table_tma_encode",
     "kdnn_b200_moe_exchange_bytes", "kdnn_b200_moe_block_workspace_bytes", "kdnn_b200_moe_block",
@@ -88,6 +88,9 @@ def _load() -> C.CDLL:
     lib.kdnn_b200_gemv_supported.argtypes = [C.c_uint32, C.c_size_t, C.c_int]
     lib.kdnn_b200_quant_gemv.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                          C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.kdnn_b200_quant_gemv_multi.argtypes = [C.c_uint32, C.c_size_t, C.POINTER(C.c_void_p), C.c_size_t, C.c_size_t,
+                                               C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_void_p,
+                                               C.c_size_t, C.c_void_p, C.c_void_p]
     lib.kdnn_b200_quant_gemv_ex.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                             C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t,
                                             C.POINTER(GemvLayoutC), C.c_void_p]
@@ -216,6 +219,8 @@ class QuantWeight:
     @staticmethod
     def from_numpy(packed, dtype: int, rows: int, cols: int, device="cuda") -> "QuantWeight":
         t = torch.from_numpy(packed.reshape(-1)).to(device)
+        if t.is_cuda:   # weights are complete before any kernel that may request them ahead of its dependency
+            torch.cuda.current_stream(t.device).synchronize()
         return QuantWeight(t, dtype, rows, cols)
 
 
@@ -288,6 +293,44 @@ def quant_gemv(x: torch.Tensor, w: QuantWeight, y: torch.Tensor, act_scratch: to
                                      y.data_ptr(), _scalar(y), act_scratch.data_ptr(), act_scratch.numel(),
                                      _layout(layout), _stream())
     _check(rc, "quant_gemv")
+
+
+def launch_chaining(on: int = -1) -> int:
+    """Switches programmatic dependent launch of the library's kernels (kdnn_b200_launch_chaining); returns the
+    previous setting, a negative argument only queries."""
+    return int(lib.kdnn_b200_launch_chaining(int(on)))
+
+
+def quant_gemv_multi(x: torch.Tensor, ws: Sequence[QuantWeight], ys: Sequence[torch.Tensor], act_scratch: torch.Tensor,
+                     layout=None) -> None:
+    """ys[i] = ws[i] . x for matrices of one format and shape that share the activation row
+    (kdnn_b200_quant_gemv_multi): what a decoder does for wgate / wup or wk / wv, taken together so that
+    Q4_K rows of up to 4096 elements run up to four matrices per launch. Same results as quant_gemv per matrix."""
+    if len(ws) != len(ys):
+        raise ValueError("quant_gemv_multi: as many outputs as matrices")
+    if not ws:
+        return
+    w0 = ws[0]
+    for w, y in zip(ws, ys):
+        if (w.dtype, w.rows, w.cols) != (w0.dtype, w0.rows, w0.cols):
+            raise ValueError("quant_gemv_multi: matrices of one format and shape")
+        if x.numel() != w.cols or y.numel() != w.rows:
+            raise ValueError("quant_gemv_multi: dimension mismatch")
+        _quant_check(w, "quant_gemv_multi")
+        _cuda(y, "y"); _cuda(w.data, "w")
+        if y.stride(0) != 1 or _scalar(y) != _scalar(ys[0]):
+            raise Declined("quant_gemv_multi: outputs of one scalar type with unit stride")
+    _cuda(x, "x"); _cuda(act_scratch, "act_scratch")
+    if w0.rows == 0 or w0.cols == 0:
+        return
+    if x.stride(0) != 1:
+        raise Declined("quant_gemv_multi: non-unit stride")
+    n = len(ws)
+    wp = (C.c_void_p * n)(*[w.data.data_ptr() for w in ws])
+    yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    rc = lib.kdnn_b200_quant_gemv_multi(w0.dtype, n, wp, w0.rows, w0.cols, x.data_ptr(), _scalar(x), yp, _scalar(ys[0]),
+                                        act_scratch.data_ptr(), act_scratch.numel(), _layout(layout), _stream())
+    _check(rc, "quant_gemv_multi")
 
 
 def quant_gemv_host(x_host: torch.Tensor, w: QuantWeight, y_host: torch.Tensor, x_dev: torch.Tensor,

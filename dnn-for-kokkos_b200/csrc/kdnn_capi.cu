@@ -11,6 +11,9 @@
 namespace kdnn {
 cudaError_t gemv_launch(uint32_t dt, const void* w, size_t rows, size_t cols, const void* x, int xs,
                         void* y, int ys, void* scratch, const kdnn_b200_gemv_layout* layout, cudaStream_t stream);
+cudaError_t gemv_multi_launch(uint32_t dt, int n, const void* const* w, size_t rows, size_t cols, const void* x, int xs,
+                              void* const* y, int ys, void* scratch, const kdnn_b200_gemv_layout* layout,
+                              cudaStream_t stream);
 cudaError_t quantize_act_launch(const void* x, int xs, size_t K, void* scratch, cudaStream_t st);
 cudaError_t unit_dots_launch(uint32_t dt, const void* w, size_t rows, size_t cols,
                              const void* scratch, int32_t* out, cudaStream_t st);
@@ -164,6 +167,41 @@ int kdnn_b200_quant_gemv_ex(uint32_t ggml_type, const void* w, size_t rows, size
                                        act_scratch, layout,
                                        static_cast<cudaStream_t>(stream)),
                      "quant_gemv");
+}
+
+int kdnn_b200_launch_chaining(int on) {
+  std::atomic<int>& f = kdnn::pdl_flag();
+  const int prev = f.load(std::memory_order_relaxed);
+  if (on >= 0) f.store(on != 0, std::memory_order_relaxed);
+  return prev;
+}
+
+int kdnn_b200_quant_gemv_multi(uint32_t ggml_type, size_t n, const void* const* w, size_t rows, size_t cols,
+                               const void* x, int x_scalar, void* const* y, int y_scalar, void* act_scratch,
+                               size_t act_scratch_bytes, const kdnn_b200_gemv_layout* layout, void* stream) {
+  if (!scalar_ok(x_scalar) || !scalar_ok(y_scalar))
+    return fail(KDNN_ERR_INVALID, "quant_gemv_multi: scalar must be KDNN_F32 or KDNN_BF16");
+  if (n == 0) return KDNN_OK;
+  if (w == nullptr || y == nullptr) return fail(KDNN_ERR_INVALID, "quant_gemv_multi: null pointer array");
+  // per matrix the decline list of kdnn_b200_quant_gemv; nothing is launched unless every matrix passes
+  if (!int8_type(ggml_type) || act_scratch == nullptr || x == nullptr) return KDNN_DECLINED;
+  if (!kdnn::block_aligned(ggml_type, cols) || rows == 0 || rows > static_cast<size_t>(INT_MAX) ||
+      cols > static_cast<size_t>(INT_MAX) || act_scratch_bytes < kdnn::act_bytes(cols) ||
+      (reinterpret_cast<uintptr_t>(act_scratch) & 15u) != 0u)
+    return KDNN_DECLINED;
+  for (size_t i = 0; i < n; ++i) {
+    if (w[i] == nullptr || y[i] == nullptr || (reinterpret_cast<uintptr_t>(w[i]) & 1u) != 0u) return KDNN_DECLINED;
+    if ((ggml_type == KDNN_GGML_Q4_K || ggml_type == KDNN_GGML_Q5_K) && (reinterpret_cast<uintptr_t>(w[i]) & 15u) != 0u)
+      return KDNN_DECLINED;
+  }
+  for (size_t i = 0; i < n; i += 4) {
+    const int m = static_cast<int>(n - i < 4 ? n - i : 4);
+    const int rc = cuda_result(kdnn::gemv_multi_launch(ggml_type, m, w + i, rows, cols, x, x_scalar, y + i, y_scalar,
+                                                       act_scratch, layout, static_cast<cudaStream_t>(stream)),
+                               "quant_gemv_multi");
+    if (rc != KDNN_OK) return rc;
+  }
+  return KDNN_OK;
 }
 
 int kdnn_b200_quant_gemv_host(uint32_t ggml_type, const void* w, size_t rows, size_t cols,

@@ -294,14 +294,13 @@ __device__ __forceinline__ void pdl_chain_entry() {
   pdl_launch_dependents();
   pdl_wait();
 }
-// KDNN_NO_PDL=1 launches without programmatic stream serialization (A/B aid).
-inline bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("KDNN_NO_PDL");
-    return !(e && e[0] == '1');
-  }();
+// Programmatic dependent launch for the library's launches: on unless kdnn_b200_launch_chaining(0) was called
+// (a caller that writes packed weights on the same stream right before a call needs it off, see kdnn_b200.h).
+inline std::atomic<int>& pdl_flag() {
+  static std::atomic<int> on{1};
   return on;
 }
+inline bool pdl_enabled() { return pdl_flag().load(std::memory_order_relaxed) != 0; }
 // Launches a kernel that begins with pdl_chain_entry() (never one that does not: it would start early).
 // `early` = false gives a plain launch: a grid of about one wave placed while the previous kernel still
 // holds some SMs lands two CTAs on the free SMs and none on the busy ones, and stays that unbalanced.

@@ -328,6 +328,9 @@ struct GemvParams {
   uint32_t upg_magic;  // ceil(2^32 / upg): u / upg == umulhi(u, magic) for the unit counts that occur
   int part_floats;     // partial sums kept in shared memory (upg > 1)
   int stage_bytes;
+  int nmat;                 // 0 / 1: one matrix; 2..4: matrices of one shape against the same x in ONE launch
+  const uint8_t* w_more[3]; // matrices 1..3
+  void* y_more[3];
 };
 
 // Sum RW per-lane values across the warp. Afterwards lane l (l < RW) holds the total of
@@ -816,6 +819,10 @@ struct XregParams {
   int part_floats;
   int early;          // ring stages requested before the activation window is quantized
   int split_first;    // request only the first row of the first stage before the dependency
+  int nmat, gpm;      // matrices in this launch (same shape, same x) and row groups per matrix; row group g belongs
+                      // to matrix g / gpm
+  const uint8_t* w_more[3];
+  void* y_more[3];
 };
 
 // Half a super-block of one row: 128 weights against the lane's register window.
@@ -864,7 +871,7 @@ __device__ __forceinline__ float q4k_half_dot(uint32_t blk, uint32_t qoff, int h
   return dd.x * p - dd.y * m;
 }
 
-template <class XT, class YT, int RW, int STAGES>
+template <class XT, class YT, int RW, int STAGES, bool MULTI>
 __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(const XregParams p) {
   constexpr int kStage = RW * kWideRowPitch;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -898,18 +905,30 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
 
   // ---- producer (state uniform across the warp; lane 0 issues the copies) ----
   int m_group[STAGES];
-  const uint8_t* wsrc = p.w + static_cast<size_t>(sb0) * 144;
+  // several matrices in one launch: row group g of the launch is row group g % gpm of matrix g / gpm
+  auto matrix_of = [&](int g, int& lg) {
+    if (!MULTI) { lg = g; return 0; }
+    const int m = g / p.gpm;
+    lg = g - m * p.gpm;
+    return m;
+  };
+  auto w_of = [&](int m) { return !MULTI || m == 0 ? p.w : m == 1 ? p.w_more[0] : m == 2 ? p.w_more[1] : p.w_more[2]; };
+  auto y_of = [&](int m) {
+    return static_cast<YT*>(!MULTI || m == 0 ? p.y : m == 1 ? p.y_more[0] : m == 2 ? p.y_more[1] : p.y_more[2]);
+  };
   const bool contiguous = p.nchunks == 1 && p.row_bytes == kWideRowPitch;
   // part 0: the whole unit; part 1: its first row only (the barrier already expects all bytes);
   // part 2: the remaining rows of a unit started with part 1
   auto issue_unit = [&](int s, int u, int part = 0) {
     m_group[s]     = u;
-    const int row0 = (c0 + u) * RW;
+    int lg;
+    const int mat  = matrix_of(c0 + u, lg);
+    const int row0 = lg * RW;
     const int nrow = min(RW, p.rows - row0);
     if (lane == 0) {
       const uint32_t bar = bar_u32 + s * 8;
       if (part != 2) mbar_expect_tx(bar, cb * nrow);
-      const uint8_t* src = wsrc + static_cast<size_t>(row0) * p.row_bytes;
+      const uint8_t* src = w_of(mat) + static_cast<size_t>(sb0) * 144 + static_cast<size_t>(row0) * p.row_bytes;
       const uint32_t dst = ring_u32 + s * kStage;
       if (contiguous && part == 0) {   // one chunk per row and full rows: the unit is one run of bytes
         bulk_g2s(dst, src, cb * nrow, bar);
@@ -982,7 +1001,6 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
   const float4 dsv = make_float4(__int_as_float(dsi.x), __int_as_float(dsi.y), __int_as_float(dsi.z), __int_as_float(dsi.w));
   const uint32_t lane_blk = sb * 144, qoff = 16 + 64 * half;
 
-  YT* y = static_cast<YT*>(p.y);
   uint32_t phase = 0;
   bool ok = true, more = true, first_round = true;
   while (more) {
@@ -998,7 +1016,9 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
         break;
       }
       const int lrow0 = m_group[s] * RW;
-      const int nrow  = min(RW, p.rows - (c0 * RW + lrow0));
+      int lg;
+      const int mat   = matrix_of(c0 + m_group[s], lg);
+      const int nrow  = min(RW, p.rows - lg * RW);
       float acc[RW];
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
@@ -1011,7 +1031,7 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
       const float v = reduce_rows<RW>(acc, lane);
       if (lane < nrow) {
         const int lrow = lrow0 + lane;
-        if (p.nchunks == 1) store_scalar(y + c0 * RW + lrow, v);
+        if (p.nchunks == 1) store_scalar(y_of(mat) + lg * RW + lane, v);
         else part[lrow * p.nchunks + chunk] = v;
       }
       __syncwarp();   // every lane has read this stage
@@ -1028,7 +1048,7 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
     for (int r = threadIdx.x; r < nloc; r += blockDim.x) {
       float v = 0.f;
       for (int j = 0; j < p.nchunks; ++j) v += part[r * p.nchunks + j];
-      store_scalar(y + c0 * RW + r, v);
+      store_scalar(static_cast<YT*>(p.y) + c0 * RW + r, v);   // one matrix per launch on this path
     }
   }
 }
@@ -1444,7 +1464,11 @@ static bool launch_q4k_xreg(const GemvParams& base, cudaStream_t stream, cudaErr
   if (p.nchunks > kGemvMaxWarps) return false;
   p.csb     = (p.nsb + p.nchunks - 1) / p.nchunks;   // near-equal chunks
   p.nchunks = (p.nsb + p.csb - 1) / p.csb;
-  p.ngroups = (p.rows + RW - 1) / RW;
+  p.gpm     = (p.rows + RW - 1) / RW;
+  p.nmat    = base.nmat > 1 ? base.nmat : 1;
+  if (p.nmat > 1 && p.nchunks != 1) return false;   // several matrices per launch: rows of one chunk only
+  for (int i = 0; i < 3; ++i) { p.w_more[i] = base.w_more[i]; p.y_more[i] = base.y_more[i]; }
+  p.ngroups = p.gpm * p.nmat;
   const int grid  = max(1, min(di.sms, p.ngroups));
   const int gpc0  = (p.ngroups + grid - 1) / grid;
   // Warps per chunk: units are equal-sized and handed out dynamically, so a CTA takes
@@ -1486,10 +1510,13 @@ static bool launch_q4k_xreg(const GemvParams& base, cudaStream_t stream, cudaErr
   // the activation loads would queue behind all of it: request half of it first, the rest behind those loads.
   p.split_first = gpc <= p.wpc ? 1 : 0;
   using Kern = void (*)(const XregParams);
-  const Kern kern = stages == 2 ? gemv_q4k_xreg_kernel<XT, YT, RW, 2>
-                  : stages == 3 ? gemv_q4k_xreg_kernel<XT, YT, RW, 3> : gemv_q4k_xreg_kernel<XT, YT, RW, 4>;
-  static SmemAttrOnce once[5];
-  err = set_max_smem_once(once[stages], kern, di.max_smem);
+  const bool multi = p.nmat > 1;
+  const Kern kern = multi ? (stages == 2 ? gemv_q4k_xreg_kernel<XT, YT, RW, 2, true>
+                             : stages == 3 ? gemv_q4k_xreg_kernel<XT, YT, RW, 3, true> : gemv_q4k_xreg_kernel<XT, YT, RW, 4, true>)
+                          : (stages == 2 ? gemv_q4k_xreg_kernel<XT, YT, RW, 2, false>
+                             : stages == 3 ? gemv_q4k_xreg_kernel<XT, YT, RW, 3, false> : gemv_q4k_xreg_kernel<XT, YT, RW, 4, false>);
+  static SmemAttrOnce once[2][5];
+  err = set_max_smem_once(once[multi][stages], kern, di.max_smem);
   if (err != cudaSuccess) return true;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(warps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
@@ -1701,6 +1728,47 @@ cudaError_t gemv_launch(uint32_t dt, const void* w, size_t rows, size_t cols, co
     case KDNN_GGML_Q6_K: return launch_generic_dt<KDNN_GGML_Q6_K>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, sb, stream);
     default: return launch_generic_dt<KDNN_GGML_Q8_0>(wb, rb, (int)rows, (int)cols, x, xs, y, ys, sb, stream);
   }
+}
+
+// n (2..4) matrices of one format and shape against the SAME activation row in one launch (a decoder's gate
+// and up projections, or q / k / v of equal width): the launch-sized ramp and tail are paid once. Covered by
+// the Q4_K register-window kernel for rows of one chunk (K <= 4096); everything else runs as n launches.
+cudaError_t gemv_multi_launch(uint32_t dt, int n, const void* const* w, size_t rows, size_t cols, const void* x, int xs,
+                              void* const* y, int ys, void* scratch, const kdnn_b200_gemv_layout* layout,
+                              cudaStream_t stream) {
+  const size_t rb = row_bytes_of(dt, cols);
+  bool fused = dt == KDNN_GGML_Q4_K && n >= 2 && n <= 4 && rb % 16 == 0 && cols % 256 == 0 && rb <= INT_MAX &&
+               rows * static_cast<size_t>(n) <= static_cast<size_t>(INT_MAX) && !(layout && layout->kernel >= 2);
+  for (int i = 0; i < n && fused; ++i) fused = (reinterpret_cast<uintptr_t>(w[i]) & 15u) == 0;
+  if (fused) {
+    t_lay = layout != nullptr ? *layout : kdnn_b200_gemv_layout{};
+    GemvParams p{};
+    p.w = static_cast<const uint8_t*>(w[0]); p.x = x; p.y = y[0]; p.scratch = static_cast<uint8_t*>(scratch);
+    p.rows = static_cast<int>(rows); p.K = static_cast<int>(cols); p.row_bytes = static_cast<int>(rb);
+    p.nitems = static_cast<int>(cols / 64); p.nchunks = (p.nitems + kChunkItems - 1) / kChunkItems;
+    p.nmat = n;
+    for (int i = 1; i < n; ++i) { p.w_more[i - 1] = static_cast<const uint8_t*>(w[i]); p.y_more[i - 1] = y[i]; }
+    cudaError_t err = cudaSuccess;
+    bool done = false;
+    const int rw = t_lay.rows_per_group == 1 ? 1 : 2;
+    if (xs == KDNN_F32 && ys == KDNN_F32)
+      done = rw == 1 ? launch_q4k_xreg<float, float, 1>(p, stream, err) : launch_q4k_xreg<float, float, 2>(p, stream, err);
+    else if (xs == KDNN_BF16 && ys == KDNN_BF16)
+      done = rw == 1 ? launch_q4k_xreg<__nv_bfloat16, __nv_bfloat16, 1>(p, stream, err)
+                     : launch_q4k_xreg<__nv_bfloat16, __nv_bfloat16, 2>(p, stream, err);
+    else if (xs == KDNN_BF16 && ys == KDNN_F32)
+      done = rw == 1 ? launch_q4k_xreg<__nv_bfloat16, float, 1>(p, stream, err)
+                     : launch_q4k_xreg<__nv_bfloat16, float, 2>(p, stream, err);
+    else
+      done = rw == 1 ? launch_q4k_xreg<float, __nv_bfloat16, 1>(p, stream, err)
+                     : launch_q4k_xreg<float, __nv_bfloat16, 2>(p, stream, err);
+    if (done) return err;
+  }
+  for (int i = 0; i < n; ++i) {
+    const cudaError_t e = gemv_launch(dt, w[i], rows, cols, x, xs, y[i], ys, scratch, layout, stream);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 cudaError_t quantize_act_launch(const void* x, int xs, size_t K, void* scratch, cudaStream_t st) {

@@ -179,6 +179,15 @@ def _row_bytes(dtype: int, cols: int) -> int:
     return cols // blk * bsz
 
 
+def _weights_ready(t):
+    """Packed weights must be complete before the kernel that precedes their first use starts (the library's
+    kernels request weight bytes ahead of their stream dependency): finish the upload / repack here."""
+    import torch
+    if t.is_cuda:
+        torch.cuda.current_stream(t.device).synchronize()
+    return t
+
+
 def load_quant_weight(kd, file: GgufFile, info: GgufTensorInfo, device="cuda"):
     """One 1-D / 2-D tensor's packed payload on the device as a QuantWeight
     (load_quant_weight, src/KokkosDNN_GGUF.hpp:864-885): dims {cols, rows} -> [rows, cols]."""
@@ -190,7 +199,7 @@ def load_quant_weight(kd, file: GgufFile, info: GgufTensorInfo, device="cuda"):
     rows, cols = info.rows(), info.cols()
     if rows * _row_bytes(info.dtype, cols) != info.nbytes:
         raise RuntimeError(f"load_quant_weight: size mismatch for '{info.name}'")
-    data = torch.from_numpy(np.array(file.payload(info))).to(device)
+    data = _weights_ready(torch.from_numpy(np.array(file.payload(info))).to(device))
     return kd.QuantWeight(data, info.dtype, rows, cols)
 
 
@@ -211,6 +220,7 @@ def load_expert_weights(kd, file: GgufFile, info: GgufTensorInfo, device="cuda")
     host = torch.from_numpy(np.array(file.payload(info))).view(experts, per)
     data = torch.zeros(experts * stride, dtype=torch.uint8, device=device)
     data.view(experts, stride)[:, :per].copy_(host)
+    _weights_ready(data)
     return [kd.QuantWeight(data[e * stride:e * stride + per], info.dtype, rows, cols) for e in range(experts)]
 
 
@@ -235,8 +245,9 @@ def tensor_to_float(kd, file: GgufFile, info: GgufTensorInfo, device="cuda"):
         raise RuntimeError("tensor_to_float: packed types are expanded on the GPU; pass a CUDA device")
     w = kd.QuantWeight(torch.from_numpy(np.array(raw)).to(device), info.dtype, rows, cols)
     out = torch.empty(rows, cols, dtype=torch.float32, device=device)
+    _weights_ready(w.data)
     kd.dequant_to_dense(w, out)
-    return out
+    return _weights_ready(out)
 
 
 # ---- writer (tests, synthetic checkpoints) ----------------------------------------------

@@ -105,6 +105,27 @@ int kdnn_b200_quant_gemv_ex(uint32_t ggml_type, const void* w, size_t rows, size
                             void* act_scratch, size_t act_scratch_bytes,
                             const kdnn_b200_gemv_layout* layout, void* stream);
 
+/* Launch chaining and the weights. Every kernel of this library is launched as a programmatic dependent of the
+ * kernel before it on the stream and requests its first PACKED WEIGHT bytes before it waits for that kernel
+ * (activations, routing and workspaces are only touched after the wait). So packed weights (w, the expert
+ * payloads) must be complete and visible before the PREVIOUS kernel on the stream starts: weights that were
+ * uploaded, repacked or dequantized on the same stream need a stream / event synchronisation before the first
+ * call that reads them (the Python loaders do that), or chaining switched off around that call.
+ * kdnn_b200_launch_chaining(0 / 1) switches it for the whole process and returns the previous setting;
+ * a negative argument only queries. Results do not depend on it. */
+int kdnn_b200_launch_chaining(int on);
+
+/* n matrices of ONE format and shape against the SAME activation row: y[i] = W[i] . x, i < n. A decoder calls the
+ * reference's quant_gemv once per projection with the same normed row (wgate and wup of the feed-forward,
+ * models/glimmer/KokkosDNN_GlimmerModel.hpp:650-653; wk and wv, :523-526); this entry point takes those calls
+ * together, and for Q4_K rows of up to 4096 elements runs up to four matrices per launch, so the ramp and the
+ * tail of a launch that streams only tens of MB are paid once. Other formats and longer rows run as n launches.
+ * w and y are HOST arrays of n device pointers. Results equal n calls of kdnn_b200_quant_gemv bit for bit.
+ * Declines as kdnn_b200_quant_gemv does, for any of the matrices, before anything is launched. */
+int kdnn_b200_quant_gemv_multi(uint32_t ggml_type, size_t n, const void* const* w, size_t rows, size_t cols,
+                               const void* x, int x_scalar, void* const* y, int y_scalar, void* act_scratch,
+                               size_t act_scratch_bytes, const kdnn_b200_gemv_layout* layout, void* stream);
+
 /* The same GEMV for callers that have no scratch buffer to give and may not create one: a
  * host runtime that reserved the whole device up front and forbids cudaMalloc in its
  * plug-ins, or a decode loop that is not allowed to touch the allocator because an

@@ -277,3 +277,86 @@ def test_host_buffer_call_with_pageable_memory(kd):
     torch.cuda.synchronize()
     assert torch.equal(y_host, y_want.cpu())
     assert kd.device_status() == 0
+
+
+@pytest.mark.parametrize("n,rows,K,dtype_name,x_dtype", [
+    (2, 1500, 4096, "Q4_K", torch.bfloat16),     # gate + up: one launch
+    (3, 257, 2048, "Q4_K", torch.float32),       # odd row count: the last row group of every matrix is half full
+    (4, 64, 256, "Q4_K", torch.bfloat16),        # fewer row groups than CTAs
+    (5, 96, 1024, "Q4_K", torch.float32),        # more than four matrices: 4 + 1
+    (2, 40, 8192, "Q4_K", torch.float32),        # rows of two chunks: runs as two launches
+    (2, 130, 2048, "Q6_K", torch.bfloat16),      # another format: runs as two launches
+])
+def test_multi_matrix_call_equals_single_calls(kd, n, rows, K, dtype_name, x_dtype):
+    """kdnn_b200_quant_gemv_multi against kdnn_b200_quant_gemv per matrix: bit for bit (the same kernel adds
+    the same terms in the same order whichever launch a row lands in)."""
+    dev = torch.device("cuda:0")
+    dtype = getattr(kd, dtype_name)
+    ws = [kd.QuantWeight.from_numpy(kd.ggml_pack.random_payload(dtype, rows, K, 900 + i), dtype, rows, K, dev)
+          for i in range(n)]
+    x = torch.randn(K, generator=torch.Generator().manual_seed(5)).to(x_dtype).to(dev)
+    scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+    singles = []
+    for w in ws:
+        y = torch.full((rows,), float("nan"), dtype=torch.float32, device=dev)
+        kd.quant_gemv(x, w, y, scratch)
+        singles.append(y)
+    for rep in range(2):
+        ys = [torch.full((rows,), float("nan"), dtype=torch.float32, device=dev) for _ in range(n)]
+        kd.quant_gemv_multi(x, ws, ys, scratch)
+        torch.cuda.synchronize()
+        for a, b in zip(ys, singles):
+            assert torch.equal(a, b)
+    assert kd.device_status() == 0
+
+
+def test_multi_matrix_call_rejects_mixed_shapes(kd):
+    dev = torch.device("cuda:0")
+    mk = lambda r: kd.QuantWeight.from_numpy(kd.ggml_pack.random_payload(kd.Q4_K, r, 256, 1), kd.Q4_K, r, 256, dev)
+    scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(256), dtype=torch.uint8, device=dev)
+    with pytest.raises(ValueError):
+        kd.quant_gemv_multi(torch.zeros(256, device=dev), [mk(4), mk(6)],
+                            [torch.zeros(4, device=dev), torch.zeros(6, device=dev)], scratch)
+
+
+def test_launch_chaining_switch_does_not_change_results(kd):
+    dev = torch.device("cuda:0")
+    rows, K = 300, 4096
+    w = kd.QuantWeight.from_numpy(kd.ggml_pack.random_payload(kd.Q4_K, rows, K, 77), kd.Q4_K, rows, K, dev)
+    x = torch.randn(K, generator=torch.Generator().manual_seed(6)).to(dev)
+    scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+    outs = []
+    prev = kd.launch_chaining(-1)
+    try:
+        for on in (1, 0):
+            kd.launch_chaining(on)
+            assert kd.launch_chaining(-1) == on
+            y = torch.empty(rows, dtype=torch.float32, device=dev)
+            for _ in range(3):
+                kd.quant_gemv(x, w, y, scratch)
+            torch.cuda.synchronize()
+            outs.append(y.clone())
+    finally:
+        kd.launch_chaining(prev)
+    assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_second_device_in_the_same_process(kd, port):
+    """The per-kernel shared-memory attribute belongs to the (kernel, device) pair: a host thread that moves to a
+    second GPU must get it set there too. Kernels with more than 48 KB of dynamic shared memory on both devices."""
+    from oracle import oracle as O
+    rows, K = 600, 4096
+    packed = kd.ggml_pack.random_payload(kd.Q4_K, rows, K, 78)
+    xh = torch.randn(K, generator=torch.Generator().manual_seed(7))
+    ref, _ = port.gemv_int8(kd.Q4_K, O.aligned_copy(packed), rows, K, xh.numpy())
+    for d in (0, 1, 0):
+        dev = torch.device("cuda", d)
+        with torch.cuda.device(dev):
+            w = kd.QuantWeight.from_numpy(packed, kd.Q4_K, rows, K, dev)
+            y = torch.empty(rows, dtype=torch.float32, device=dev)
+            scratch = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+            kd.quant_gemv(xh.to(dev), w, y, scratch)
+            torch.cuda.synchronize(dev)
+            assert np.abs(y.cpu().numpy() - ref).max() <= 1e-3 * np.abs(ref).max()
+            assert kd.device_status() == 0
