@@ -575,6 +575,46 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """One small workload on one GPU, a few hundred MB on the device and a handful of launches: the thing to
+    put under a profiler (`--case gemv_q4k | gemv_q6k | gemv_q80 | gemv_q4k_pair | moe_block | moe_block_tcgen05`).
+    gemv_*: 13 cold copies of the matrix, three passes over them. moe_block*: one 128-expert / top-8 / hidden
+    2048 / FFN 768 block on 256 tokens, three calls."""
+    import torch
+    import __graft_entry__ as ge
+    kd = ge.load_package()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    if args.case.startswith("gemv"):
+        dt, rows, K = {"gemv_q4k": (Q4_K, 14336, 4096), "gemv_q4k_pair": (Q4_K, 14336, 4096),
+                       "gemv_q6k": (Q6_K, 4096, 14336), "gemv_q80": (Q8_0, 4096, 4096)}[args.case]
+        host = kd.ggml_pack.synth_weight(dt, rows, K, SEED, std=0.02)
+        ws = [kd.QuantWeight.from_numpy(host, dt, rows, K, dev) for _ in range(13 if rows * K > 2e7 else 26)]
+        x = torch.randn(K, generator=torch.Generator().manual_seed(SEED)).to(torch.bfloat16).to(dev)
+        ys = [torch.empty(rows, dtype=torch.float32, device=dev) for _ in range(2)]
+        scr = torch.zeros(kd.quant_gemv_int8_scratch_bytes(K), dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            if args.case == "gemv_q4k_pair":
+                for i in range(0, len(ws) - 1, 2):
+                    kd.quant_gemv_multi(x, ws[i:i + 2], ys, scr)
+            else:
+                for w in ws:
+                    kd.quant_gemv(x, w, ys[0], scr)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "launches": 3 * (len(ws) // 2 if args.case == "gemv_q4k_pair" else len(ws)), "matrix_bytes": int(host.nbytes),
+                          "device_status": kd.device_status()}))
+        return
+    ms = ge._load_module("_kd_moe_bench", os.path.join(ge.PKG_DIR, "moe_stack.py"))
+    kd.tile_kind(2 if args.case.endswith("tcgen05") else 3)
+    cfg = ms.StackConfig(layers=1)
+    stack = ms.MoeStack(kd, dev, cfg, 0, 1)
+    h0 = torch.randn(cfg.tokens, cfg.hidden, device=dev).to(torch.bfloat16)
+    for _ in range(3):
+        stack.forward(h0)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "block_calls": 3, "device_status": kd.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -584,8 +624,13 @@ def main():
     ap.add_argument("--no-moe", action="store_true")
     ap.add_argument("--check-multi-rank", action="store_true",
                     help="only compare the expert-parallel MoE stack with a one-rank run and print the errors")
+    ap.add_argument("--case", default=None,
+                    choices=["gemv_q4k", "gemv_q4k_pair", "gemv_q6k", "gemv_q80", "moe_block", "moe_block_tcgen05"],
+                    help="run one small workload only (for a profiler) instead of the benchmark")
     args = ap.parse_args()
-    if args.check_multi_rank:
+    if args.case:
+        run_case(args)
+    elif args.check_multi_rank:
         run_check_multi_rank(args)
     elif args.impl == "reference":
         run_reference(args)
