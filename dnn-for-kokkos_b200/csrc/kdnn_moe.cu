@@ -1445,7 +1445,10 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
       m1.xrows = xrows; m1.x_pitch = act_row_pitch(H); m1.dst = act; m1.ld_dst = F;
       m1.round_bf16 = a.scalar == KDNN_BF16; m1.status = status;
       const int mean_rows = (int)((T * S + E - 1) / E);
-      const int passes_z = max(1, min(4, 1 + (2 * mean_rows) / 32));
+      // CTAs along z share an expert's 32-row passes. Routing is uneven (an expert may get several times the
+      // mean), and a CTA without a pass leaves at once, so a small grid (few local experts) gets up to eight.
+      const int row_ctas = (int)((F + 63) / 64 * a.e_count);
+      const int passes_z = max(max(1, min(4, 1 + (2 * mean_rows) / 32)), min(8, 2048 / max(1, row_ctas)));
       m1.passes_z = passes_z; m1.qdst = arows; m1.q_pitch = act_row_pitch(F);
       err = launch_grouped_mma<1, float>(m1, (int)a.e_count, st);
       if (err != cudaSuccess) return err;
