@@ -36,7 +36,7 @@ F32, BF16 = 0, 1
 # every symbol include/kdnn_b200.h declares (checked by the CPU test-suite)
 EXPORTS = [
     "kdnn_b200_last_error", "kdnn_b200_device_status", "kdnn_b200_gemv_scratch_bytes",
-    "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quant_gemv_ex", "kdnn_b200_quant_gemv_multi", "kdnn_b200_launch_chaining", "kdnn_b200_quant_gemv_noalloc",
+    "kdnn_b200_gemv_supported", "kdnn_b200_quant_gemv", "kdnn_b200_quant_gemv_ex", "kdnn_b200_quant_gemv_multi", "kdnn_b200_launch_chaining", "kdnn_b200_host_copy_by_kernel", "kdnn_b200_quant_gemv_noalloc",
     "kdnn_b200_quant_gemv_noalloc_ex", "kdnn_b200_quantize_act_q8", "kdnn_b200_quant_gemm_dots", "kdnn_b200_tile_kind",
     "kdnn_b200_weight_table_tma_bytes", "kdnn_b200_weight_table_tma_encode",
     "kdnn_b200_moe_exchange_bytes", "kdnn_b200_moe_block_workspace_bytes", "kdnn_b200_moe_block",
@@ -293,6 +293,12 @@ def quant_gemv(x: torch.Tensor, w: QuantWeight, y: torch.Tensor, act_scratch: to
                                      y.data_ptr(), _scalar(y), act_scratch.data_ptr(), act_scratch.numel(),
                                      _layout(layout), _stream())
     _check(rc, "quant_gemv")
+
+
+def host_copy_by_kernel(on: int = -1) -> int:
+    """kdnn_b200_host_copy_by_kernel: 1 = kernels move page-locked host buffers of quant_gemv_host (default),
+    0 = the copy engine; returns the previous setting, a negative argument only queries."""
+    return int(lib.kdnn_b200_host_copy_by_kernel(int(on)))
 
 
 def launch_chaining(on: int = -1) -> int:

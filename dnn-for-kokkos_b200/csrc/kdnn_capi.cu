@@ -113,14 +113,9 @@ void* mapped_host_pointer(const void* host) {
 }
 // kdnn_b200_quant_gemv_host moves x and y with copy_bytes_kernel when the host buffers allow it
 // (measured on the three decode GEMVs: 1972 GB/s end to end against 1245 GB/s with the copy engine);
-// KDNN_HOST_COPY=dma keeps cudaMemcpyAsync for everything.
-bool host_copy_by_kernel() {
-  static const bool on = [] {
-    const char* e = getenv("KDNN_HOST_COPY");
-    return !(e != nullptr && e[0] == 'd');
-  }();
-  return on;
-}
+// kdnn_b200_host_copy_by_kernel(0) keeps cudaMemcpyAsync for everything.
+std::atomic<int> g_host_copy_kernel{1};
+bool host_copy_by_kernel() { return g_host_copy_kernel.load(std::memory_order_relaxed) != 0; }
 }  // namespace
 
 extern "C" {
@@ -167,6 +162,12 @@ int kdnn_b200_quant_gemv_ex(uint32_t ggml_type, const void* w, size_t rows, size
                                        act_scratch, layout,
                                        static_cast<cudaStream_t>(stream)),
                      "quant_gemv");
+}
+
+int kdnn_b200_host_copy_by_kernel(int on) {
+  const int prev = g_host_copy_kernel.load(std::memory_order_relaxed);
+  if (on >= 0) g_host_copy_kernel.store(on != 0, std::memory_order_relaxed);
+  return prev;
 }
 
 int kdnn_b200_launch_chaining(int on) {

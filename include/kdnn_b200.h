@@ -157,11 +157,15 @@ int kdnn_b200_quant_gemv_noalloc_ex(uint32_t ggml_type, const void* w, size_t ro
  * failed call has enqueued nothing. When the host buffers are page-locked (or registered) and 16-byte
  * aligned the two copies are small kernels over the mapped host pointers, chained with the GEMV like every
  * kernel of the library (the copy engine's hand-offs cost more than these kernels do); pageable buffers,
- * or KDNN_HOST_COPY=dma in the environment, take cudaMemcpyAsync. In the reference this is the host's deep_copy, quant_gemv, deep_copy
+ * or every buffer after kdnn_b200_host_copy_by_kernel(0), take cudaMemcpyAsync. In the reference this is the host's
+ * deep_copy, quant_gemv, deep_copy
  * sequence around src/KokkosDNN_GGUF.hpp:2531-2551 folded into one call; same decline list and results. */
 int kdnn_b200_quant_gemv_host(uint32_t ggml_type, const void* w, size_t rows, size_t cols,
                               const void* x_host, int x_scalar, void* y_host, int y_scalar, void* x_dev,
                               void* y_dev, void* act_scratch, size_t act_scratch_bytes, void* stream);
+/* 1 (default): page-locked host buffers of kdnn_b200_quant_gemv_host are moved by kernels; 0: always by the copy
+ * engine. Returns the previous setting; a negative argument only queries. */
+int kdnn_b200_host_copy_by_kernel(int on);
 
 /* Stage 1 alone: quantize one activation row into `scratch` (layout above).
  * Stands in for Impl::GgufMvq::QuantizeActQ8Functor, src/KokkosDNN_GGUFGemvInt8.hpp:198-239. */
@@ -298,10 +302,15 @@ size_t kdnn_b200_moe_block_workspace_bytes(size_t tokens_local, size_t world, si
  *   -> y = sum over the slots (slot order, fp32) on the token's owner
  *   -> optionally h_out = Scalar(float(resid) + y) (:812-816) and xn_out = rmsnorm_noscale(h_out)
  *      (src/KokkosDNN_RMSNorm.hpp:347-361, the next block's :770).
- * Four kernel launches: router + routing + row quantizer + slot sort, gate/up tiles, down tiles, combine.
- * With `ex` != NULL the token rows travel to every rank inside the first kernel (plain peer stores) and the
- * down kernel stores its output rows straight into the token owner's region; every wait for a peer is
- * bounded (KDNN_ERR_DEVICE_WAIT in kdnn_b200_device_status() when one gave up; the call never hangs).
+ * Four kernel launches: router + routing + row quantizer + slot runs, gate/up tiles, down tiles, combine.
+ * With `ex` != NULL rank r owns tokens [r * tokens_local, (r + 1) * tokens_local) and experts
+ * [r * E / world, (r + 1) * E / world) (expert_first / expert_count must say so, KDNN_ERR_INVALID otherwise):
+ * the quantized token rows and routed ids travel to every rank inside the first kernel (plain peer stores, one
+ * atomic add per routed slot on the expert owner's counter), the down kernel leaves its output rows in its own
+ * rank's region and the token owner's combine kernel reads them from there (plain peer loads). Every wait for a
+ * peer is bounded (KDNN_ERR_DEVICE_WAIT in kdnn_b200_device_status() when one gave up; the call never hangs).
+ * The workspace carries the call's epoch counters: one workspace per stream, the same one for every call of a
+ * sequence.
  *   x [tokens_local, H] Scalar; router_w [E, H] Scalar, 16-byte aligned rows; router_bias [E] or NULL;
  *   y [tokens_local, H] float or NULL; resid / h_out / xn_out [tokens_local, H] Scalar or NULL.
  * Q4_K tables only (KDNN_DECLINED otherwise: compose kdnn_b200_moe_route + kdnn_b200_moe_ffn instead). */
@@ -314,9 +323,9 @@ int kdnn_b200_moe_block(const void* x, size_t ldx, size_t tokens_local, int scal
                         void* xn_out, size_t ldxn, float eps,
                         const kdnn_b200_moe_exchange* ex, void* workspace, size_t workspace_bytes, void* stream);
 
-/* Copies the routing result of the last kdnn_b200_moe_block call for ALL tokens (token-major over the
- * ranks) out of the exchange region / workspace into the caller's device buffers, on `stream`:
- * idx_out [T, top_k] int32, wts_out [T, top_k] float. */
+/* Copies the routing result of the last kdnn_b200_moe_block call out of the exchange region / workspace into
+ * the caller's device buffers, on `stream`: idx_out [T, top_k] int32 (all ranks' tokens, token-major over the
+ * ranks), wts_out [T, top_k] float (only the rows of THIS rank's tokens are meaningful: the weights do not travel). */
 int kdnn_b200_moe_block_routing(const kdnn_b200_moe_exchange* ex, void* workspace, size_t tokens_local, size_t world,
                                 size_t top_k, size_t H, size_t F, size_t n_experts, int32_t* idx_out, float* wts_out,
                                 void* stream);
