@@ -2,6 +2,7 @@
 """Benchmark of the quantized-decode hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-moe] [--check-multi-rank]
+    python bench.py --case NAME        # one small workload only (for a profiler), see run_case
 
 Workload (``config.workload``): the mixed-format decode GEMVs at Llama-3-8B shapes,
 batch 1, bf16 activations ~ N(0,1), weights quantized from seeded N(0, 0.02) fp32:
@@ -13,7 +14,9 @@ Metric: GB/s of algorithmic bytes (packed weight bytes + x + y per GEMV, the
 reference's own convention of counting the packed payload). ``roofline`` is the Q4_K
 14336x4096 GEMV alone, timed with CUDA events on the launch stream, against the
 measured HBM copy bandwidth in MEASURED_PEAKS.json; it also carries the read-only streaming
-ceiling measured in the same run (``read_only_ceiling_GBps``), the other shapes (``by_shape``)
+ceiling measured in the same run (``read_only_ceiling_GBps`` over 1 GiB, ``read_only_same_size_GBps`` over the
+same 33 MB per launch), two and four matrices per launch (``matrices_per_launch``,
+kdnn_b200_quant_gemv_multi), the measured DRAM bytes of one launch (``traffic``), the other shapes (``by_shape``)
 and the batched sweep of 1..32 activation rows on the 14336x4096 matrix (``by_batch``).
 ``e2e`` is the same pass driven from pinned host buffers through
 kdnn_b200_quant_gemv_host: per GEMV the activation row goes host->device and the result row
