@@ -870,6 +870,7 @@ struct GateParams {
   size_t x_pitch;
   int e_first, e_count;         // this rank's experts
   int* offs; int* list; int4* groups; int* n_groups;   // outputs of the last CTA (this rank's workspace)
+  int* pos;                     // single rank: position of every slot in `list` (the down rows are kept by position)
   int* ticket; uint32_t* epoch; int* status;
   unsigned long long wait_ns;
 };
@@ -1226,7 +1227,10 @@ __global__ void __launch_bounds__(kGateThreads) moe_gate_kernel(const GateParams
         const int i = i0 + u * kGateThreads;
         if (ev[u] >= 0 && ev[u] < p.e_count) {
           const int ps = starts[ev[u]] + rv[u];
-          if (ps >= starts[ev[u]] && ps < starts[ev[u] + 1] && ps < total) p.list[ps] = i;
+          if (ps >= starts[ev[u]] && ps < starts[ev[u] + 1] && ps < total) {
+            p.list[ps] = i;
+            if (p.pos) p.pos[i] = ps;
+          }
         }
       }
     }
@@ -1247,6 +1251,7 @@ __global__ void __launch_bounds__(kGateThreads) moe_gate_kernel(const GateParams
 struct CombineParams {
   const float* out[kMaxRanks];             // every rank's slot-indexed rows [T*S][H] (a slot's row lives on its expert's owner)
   const int32_t* idx; const float* wts;    // this rank's region, [T][S]
+  const int* pos;                          // single rank: row of slot i is out[0] + pos[i] * H (null: row i)
   int Tl, S, H, e_lo, e_hi, e_per_rank, world, rank;   // slots of experts in [e_lo, e_hi) have a row; owner = e / e_per_rank
   const uint32_t* oflag; const uint32_t* epoch; int* status;
   unsigned long long wait_ns;
@@ -1261,6 +1266,7 @@ __global__ void __launch_bounds__(512) moe_combine_norm_kernel(const CombinePara
   __shared__ float red[32];
   __shared__ int s_e[64];
   __shared__ float s_w[64];
+  __shared__ int s_p[64];
   const int t = blockIdx.x;
   const int tg = p.rank * p.Tl + t;
   const int32_t* idx = p.idx + static_cast<size_t>(tg) * p.S;
@@ -1269,6 +1275,7 @@ __global__ void __launch_bounds__(512) moe_combine_norm_kernel(const CombinePara
   if (cached && static_cast<int>(threadIdx.x) < p.S) {
     s_e[threadIdx.x] = idx[threadIdx.x];
     s_w[threadIdx.x] = wts[threadIdx.x];
+    s_p[threadIdx.x] = p.pos ? p.pos[static_cast<size_t>(tg) * p.S + threadIdx.x] : 0;
   }
   if (p.world > 1) {
     if (static_cast<int>(threadIdx.x) < p.world) {
@@ -1292,7 +1299,8 @@ __global__ void __launch_bounds__(512) moe_combine_norm_kernel(const CombinePara
         v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (w[u] != 0.0f) {
           const float* src = p.out[p.world > 1 ? e / p.e_per_rank : 0];
-          v[u] = __ldcg(reinterpret_cast<const float4*>(src + (static_cast<size_t>(tg) * p.S + s) * p.H + d));
+          const size_t rowi = p.pos ? static_cast<size_t>(s_p[s & 63]) : static_cast<size_t>(tg) * p.S + s;
+          v[u] = __ldcg(reinterpret_cast<const float4*>(src + rowi * p.H + d));
         }
       }
 #pragma unroll
@@ -1380,6 +1388,8 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
   g.e_per_rank = a.world > 1 ? (int)a.e_count : 0; g.e_first = (int)a.e_first; g.e_count = (int)a.e_count;
   g.offs = reinterpret_cast<int*>(b + L.offs); g.list = reinterpret_cast<int*>(b + L.list);
   g.groups = reinterpret_cast<int4*>(b + L.groups); g.n_groups = reinterpret_cast<int*>(b + L.ngroups);
+  const bool by_position = a.world == 1 && S <= 64;   // where the down rows go, see below
+  g.pos = by_position ? reinterpret_cast<int*>(b + L.pos) : nullptr;
   g.ticket = sync; g.epoch = reinterpret_cast<uint32_t*>(sync + 2); g.status = status; g.wait_ns = a.wait_ns;
   // tokens per cluster: about 128 CTAs whatever the token count (a CTA streams a quarter of the router matrix)
   int tpc = a.Tl >= 256 ? 8 : a.Tl >= 128 ? 4 : a.Tl >= 64 ? 2 : 1;
@@ -1406,7 +1416,9 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
 
   // ---- expert tiles over all T tokens' slots, local experts ----
   PeerOut po{};
-  po.out = reinterpret_cast<float*>(mine + XL.out);
+  // several ranks: rows by slot (the token owners find them without asking); one rank: rows by position in the
+  // sorted list, as the tile kernels produce them (the scattered row pointers cost 6 us per block)
+  po.out = by_position ? nullptr : reinterpret_cast<float*>(mine + XL.out);
   for (size_t r = 0; r < world; ++r) po.oflag[r] = reinterpret_cast<uint32_t*>(regions[r] + XL.oflag);
   po.world = a.world; po.rank = a.rank;
   po.ticket = a.world > 1 ? sync + 1 : nullptr;
@@ -1435,7 +1447,7 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
       t0.maps0 = static_cast<const CUtensorMap*>(a.down->tma);
       t0.N = (int)H; t0.K = (int)F; t0.tile_rows = 128; t0.row_tiles = (int)((H + 127) / 128);
       t0.groups = t1.groups; t0.n_groups = t1.n_groups; t0.list = list; t0.S = (int)S;
-      t0.xrows = arows; t0.x_pitch = act_row_pitch(F); t0.dst = nullptr; t0.ld_dst = H; t0.status = status; t0.po = po;
+      t0.xrows = arows; t0.x_pitch = act_row_pitch(F); t0.dst = by_position ? mine + XL.out : nullptr; t0.ld_dst = H; t0.status = status; t0.po = po;
       err = launch_grouped_tc<0, float>(t0, max_groups * t0.row_tiles, st);
       if (err != cudaSuccess) return err;
     } else {
@@ -1455,7 +1467,7 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
       MmaParams m0{};
       m0.w0 = a.down->base; m0.row_bytes = (int)a.down->row_bytes;
       m0.N = (int)H; m0.K = (int)F; m0.offs = offs; m0.list = list; m0.S = (int)S; m0.g_first = (int)a.e_first;
-      m0.xrows = arows; m0.x_pitch = act_row_pitch(F); m0.dst = nullptr; m0.ld_dst = H; m0.status = status;
+      m0.xrows = arows; m0.x_pitch = act_row_pitch(F); m0.dst = by_position ? mine + XL.out : nullptr; m0.ld_dst = H; m0.status = status;
       m0.passes_z = passes_z; m0.po = po;
       err = launch_grouped_mma<0, float>(m0, (int)a.e_count, st);
       if (err != cudaSuccess) return err;
@@ -1465,6 +1477,7 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
   CombineParams c{};
   for (size_t r = 0; r < world; ++r) c.out[r] = reinterpret_cast<const float*>(regions[r] + XL.out);
   c.e_per_rank = a.world > 1 ? (int)a.e_count : 1;
+  c.pos = by_position ? reinterpret_cast<const int*>(b + L.pos) : nullptr;
   c.idx = reinterpret_cast<const int32_t*>(mine + XL.idx); c.wts = reinterpret_cast<const float*>(mine + XL.wts);
   c.Tl = (int)a.Tl; c.S = (int)S; c.H = (int)H; c.world = a.world; c.rank = a.rank;
   c.e_lo = a.world > 1 ? 0 : (int)a.e_first; c.e_hi = a.world > 1 ? (int)E : (int)(a.e_first + a.e_count);
