@@ -79,8 +79,11 @@ class ClockSampler:
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.idx = gpu_index
+    def __init__(self, gpu_index, enabled: bool = True):
+        """gpu_index: one index, or a list of indices (one nvidia-smi call samples them all). Only one process of a
+        multi-rank job should sample: a dozen concurrent nvidia-smi queries disturb the GPUs they look at."""
+        self.idx = ",".join(str(i) for i in gpu_index) if isinstance(gpu_index, (list, tuple)) else str(gpu_index)
+        self.enabled = enabled
         self.rows = []
         self._stop = threading.Event()
         self._t = threading.Thread(target=self._run, daemon=True)
@@ -89,7 +92,7 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.idx)], capture_output=True, text=True, timeout=5).stdout
+                                      "-i", self.idx], capture_output=True, text=True, timeout=5).stdout
                 for line in out.strip().splitlines():
                     self.rows.append([c.strip() for c in line.split(",")])
             except Exception:
@@ -97,12 +100,14 @@ class ClockSampler:
             self._stop.wait(0.2)
 
     def __enter__(self):
-        self._t.start()
+        if self.enabled:
+            self._t.start()
         return self
 
     def __exit__(self, *a):
         self._stop.set()
-        self._t.join(timeout=6)
+        if self.enabled:
+            self._t.join(timeout=6)
 
     def summary(self):
         sm, mx, reasons = [], [], set()
@@ -355,7 +360,7 @@ def run_ours(args):
         torch.cuda.synchronize()
         barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    with ClockSampler(list(range(world)) if world > 1 else local, enabled=(rank == 0)) as clocks:
         with torch.cuda.stream(stream):
             e0.record(stream)
             for _ in range(args.steps // chunk):
@@ -380,6 +385,15 @@ def run_ours(args):
     bytes_step = per_set * rotate
     value = world * bytes_step * args.steps / (ms_total * 1e-3) / 1e9
     launches = 3 * rotate * args.steps
+
+    # ---- the same twelve launches grouped by shape (all Q8_0, then all Q4_K, then all Q6_K): three different
+    # kernels taking turns cost more than the sum of their single-shape sequences, two do not ------------------
+    def grouped_pass():
+        for i in range(len(GEMV_SHAPES)):
+            for ws in sets:
+                kd.quant_gemv(xs[i], ws[i], ys[i], scr[i])
+    pass_order = {"interleaved_us": ms_total / args.steps * 1e3,
+                  "grouped_by_shape_us": _graph_time_us(torch, stream, lambda: [grouped_pass() for _ in range(10)], iters=5) / 10}
 
     # ---- per-kernel roofline: each shape alone, rotating copies, CUDA events -----------
     peak, peak_kind = measured_peaks()
@@ -477,7 +491,8 @@ def run_ours(args):
                 "read_only_same_size_GBps": read_only_same_size,
                 "frac_of_read_only_same_size": dom["achieved_GBps"] / read_only_same_size,
                 "matrices_per_launch": multi,
-                "traffic": measured_dram_traffic(), "by_shape": per_kernel, "by_batch": by_batch}
+                "traffic": measured_dram_traffic(), "by_shape": per_kernel, "by_batch": by_batch,
+                "pass_order": pass_order}
 
     # ---- end to end through the public call with host buffers --------------------------
     def e2e_pass():

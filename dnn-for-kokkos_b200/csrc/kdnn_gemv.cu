@@ -905,6 +905,18 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
 
   // ---- producer (state uniform across the warp; lane 0 issues the copies) ----
   int m_group[STAGES];
+  auto mg_get = [&](int st) {   // register array read / written with a run-time stage index
+    int v = m_group[0];
+#pragma unroll
+    for (int i = 1; i < STAGES; ++i)
+      if (st == i) v = m_group[i];
+    return v;
+  };
+  auto mg_set = [&](int st, int v) {
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i)
+      if (st == i) m_group[i] = v;
+  };
   // several matrices in one launch: row group g of the launch is row group g % gpm of matrix g / gpm
   auto matrix_of = [&](int g, int& lg) {
     if (!MULTI) { lg = g; return 0; }
@@ -920,7 +932,7 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
   // part 0: the whole unit; part 1: its first row only (the barrier already expects all bytes);
   // part 2: the remaining rows of a unit started with part 1
   auto issue_unit = [&](int s, int u, int part = 0) {
-    m_group[s]     = u;
+    mg_set(s, u);
     int lg;
     const int mat  = matrix_of(c0 + u, lg);
     const int row0 = lg * RW;
@@ -961,7 +973,7 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
   };
   auto issue = [&](int s) {
     if (pdone) {
-      m_group[s] = -1;
+      mg_set(s, -1);
       return;
     }
     issue_unit(s, pu);
@@ -1007,7 +1019,7 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
       if (!more) break;
-      if (m_group[s] < 0) {
+      if (mg_get(s) < 0) {
         more = false;
         break;
       }
@@ -1015,9 +1027,9 @@ __global__ void __launch_bounds__(kXregMaxWarps * 32, 1) gemv_q4k_xreg_kernel(co
         ok = more = false;
         break;
       }
-      const int lrow0 = m_group[s] * RW;
+      const int lrow0 = mg_get(s) * RW;
       int lg;
-      const int mat   = matrix_of(c0 + m_group[s], lg);
+      const int mat   = matrix_of(c0 + mg_get(s), lg);
       const int nrow  = min(RW, p.rows - lg * RW);
       float acc[RW];
 #pragma unroll
@@ -1092,10 +1104,22 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
 
   // ---- producer (state uniform across the warp; lane 0 issues the copies) ----
   int m_group[STAGES];
+  auto mg_get = [&](int st) {   // register array read / written with a run-time stage index
+    int v = m_group[0];
+#pragma unroll
+    for (int i = 1; i < STAGES; ++i)
+      if (st == i) v = m_group[i];
+    return v;
+  };
+  auto mg_set = [&](int st, int v) {
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i)
+      if (st == i) m_group[i] = v;
+  };
   const uint8_t* wsrc = p.w + static_cast<size_t>(chunk) * kRowPitch;
   const bool contiguous = p.nchunks == 1 && p.row_bytes == kRowPitch && cb == static_cast<uint32_t>(kRowPitch);
   auto issue_unit = [&](int s, int u) {
-    m_group[s]     = u;
+    mg_set(s, u);
     const int row0 = (c0 + u) * RW;
     const int nrow = min(RW, p.rows - row0);
     if (lane == 0) {
@@ -1132,7 +1156,7 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
   };
   auto issue = [&](int s) {
     if (pdone) {
-      m_group[s] = -1;
+      mg_set(s, -1);
       return;
     }
     issue_unit(s, pu);
@@ -1169,11 +1193,16 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
   YT* y = static_cast<YT*>(p.y);
   uint32_t phase = 0;
   bool ok = true, more = true, first_round = true;
+  // Code size matters here: three big kernels taking turns on a stream (a decoder's Q8_0 / Q4_K / Q6_K projections)
+  // evict one another from the instruction cache -- 27.5 us per triple against 24.0 us for the sum of the
+  // single-kernel sequences. The stage loop is therefore unrolled only for Q6_K (whose integer-bound inner loop loses
+  // 5 % to a run-time stage index); the Q8_0 kernel runs it with a run-time index and is a third smaller.
+  constexpr int kUnroll = DT == KDNN_GGML_Q6_K ? STAGES : 1;
   while (more) {
-#pragma unroll
+#pragma unroll kUnroll
     for (int s = 0; s < STAGES; ++s) {
       if (!more) break;
-      if (m_group[s] < 0) {
+      if (mg_get(s) < 0) {
         more = false;
         break;
       }
@@ -1181,7 +1210,7 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) gemv_item_xreg_kernel(c
         ok = more = false;
         break;
       }
-      const int lrow0 = m_group[s] * RW;
+      const int lrow0 = mg_get(s) * RW;
       const int nrow  = min(RW, p.rows - (c0 * RW + lrow0));
       float acc[RW];
 #pragma unroll
@@ -1554,7 +1583,7 @@ static bool launch_item_xreg(const GemvParams& base, cudaStream_t stream, cudaEr
   auto smem_for = [&](int st) { return fixed + static_cast<size_t>(kGemvMaxWarps) * st * (8 + kStage); };
   const int units_per_warp = (gpc + p.wpc - 1) / p.wpc;
   int stages = t_lay.stages;
-  if (stages == 0) stages = 3;
+  if (stages == 0) stages = DT == KDNN_GGML_Q6_K ? 2 : 3;   // measured: two stages are the best Q6_K point (11.9 against 12.4 us)
   stages = max(2, min(4, min(stages, max(2, units_per_warp))));
   while (stages > 2 && smem_for(stages) > static_cast<size_t>(di.max_smem)) --stages;
   if (smem_for(stages) > static_cast<size_t>(di.max_smem)) return false;
