@@ -368,6 +368,9 @@ def run_ours(args):
             for _ in range(args.steps % chunk):
                 graph.replay()
             e1.record(stream)
+        # the timed work is complete BEFORE the closing barrier is enqueued: its NCCL kernel would otherwise spin on a
+        # few SMs next to the last timed launches (that cost 15 % at 2 to 8 ranks)
+        stream.synchronize()
         barrier()
         ms_total = e0.elapsed_time(e1)
         # keep the GPU busy long enough for a few clock samples
