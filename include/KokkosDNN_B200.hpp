@@ -129,6 +129,42 @@ bool quant_gemv_host(const ExecSpace& space, const XHost& x_host, const QuantWei
   return rc == KDNN_OK;
 }
 
+// Several projections of ONE activation row in one call (the model's wgate / wup or wk / wv,
+// models/glimmer/KokkosDNN_GlimmerModel.hpp:650-653, :523-526): ys[i] = ws[i] . x for matrices of one format and
+// shape. `ws` and `ys` are any ranges of QuantWeight / views (std::array, std::vector, initializer_list).
+// Returns false when the int8 path declined (nothing launched): the caller then makes its single calls.
+template <class ExecSpace, class XView, class WRange, class YRange, class SView>
+bool quant_gemv_multi(const ExecSpace& space, const XView& x, const WRange& ws, const YRange& ys,
+                      const SView& act_scratch) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(x.data())>::type>::type;
+  const void* wp[16];
+  void* yp[16];
+  std::size_t n = 0, rows = 0, cols = 0;
+  std::uint32_t dtype = 0;
+  for (const auto& w : ws) {
+    if (n == 16) throw std::invalid_argument("quant_gemv_multi: at most 16 matrices per call");
+    if (n == 0) { rows = w.rows; cols = w.cols; dtype = static_cast<std::uint32_t>(w.dtype); }
+    if (w.rows != rows || w.cols != cols || static_cast<std::uint32_t>(w.dtype) != dtype)
+      throw std::invalid_argument("quant_gemv_multi: matrices of one format and shape");
+    wp[n++] = w.data.data();
+  }
+  std::size_t m = 0;
+  for (const auto& y : ys) {
+    if (m == n) break;
+    if (y.extent(0) != rows) throw std::invalid_argument("quant_gemv_multi: dimension mismatch");
+    if (y.stride(0) != 1) return false;
+    yp[m++] = y.data();
+  }
+  if (m != n || x.extent(0) != cols) throw std::invalid_argument("quant_gemv_multi: dimension mismatch");
+  if (n == 0 || rows == 0 || cols == 0) return true;
+  if (scalar_tag<Scalar>() < 0 || x.stride(0) != 1) return false;
+  const int rc = kdnn_b200_quant_gemv_multi(dtype, n, wp, rows, cols, x.data(), scalar_tag<Scalar>(), yp,
+                                            scalar_tag<Scalar>(), act_scratch.data(), act_scratch.extent(0), nullptr,
+                                            StreamOf<ExecSpace>::get(space));
+  throw_on_error(rc, "quant_gemv_multi");
+  return rc == KDNN_OK;
+}
+
 // Gguf::quant_gemv(handle, x, w, y) without staging (fp path), src/KokkosDNN_GGUF.hpp:2394-2493.
 template <class ExecSpace, class XView, class QuantWeight, class YView>
 void quant_gemv_fp(const ExecSpace& space, const XView& x, const QuantWeight& w, const YView& y) {
@@ -266,6 +302,39 @@ void moe_ffn(const ExecSpace& space, const XView& X, const Table& gate, const Ta
                  "moe_ffn");
 }
 
+
+// The model's MoE block for a chunk of tokens in ONE call (router product, moe_route / moe_route_sigmoid, experts,
+// residual add, the next block's un-scaled RMS norm; models/lfm2_5/KokkosDNN_LFM25Model.hpp:770-816):
+//   h_out = h + MoE(x),  x_next = rmsnorm_noscale(h_out).
+// x, h, h_out, x_next: [tokens, H] Scalar views; router_w [E, H]; router_bias [E] or a view of extent 0.
+// `workspace`: caller-owned bytes, kdnn_b200_moe_block_workspace_bytes(tokens, 1, S, H, F, E, 1), 256-byte aligned,
+// zeroed once; one workspace per stream. `exchange` (null: one GPU) as kdnn_b200.h describes.
+// Returns false when the call is not covered (tables other than Q4_K): compose moe_route + moe_ffn instead.
+template <class ExecSpace, class XView, class RView, class BView, class Table, class HView, class WsView>
+bool moe_block(const ExecSpace& space, const XView& x, const RView& router_w, const BView& router_bias, int top_k,
+               bool norm_topk, float routed_scale, bool sigmoid, const Table& gate, const Table& up, const Table& down,
+               const HView& h, const HView& h_out, const XView& x_next, float eps, const WsView& workspace,
+               const kdnn_b200_moe_exchange* exchange = nullptr, std::size_t expert_first = 0,
+               std::size_t expert_count = static_cast<std::size_t>(-1), const void* tma_gate = nullptr,
+               const void* tma_up = nullptr, const void* tma_down = nullptr) {
+  using Scalar = typename std::remove_cv<typename std::remove_pointer<decltype(x.data())>::type>::type;
+  const std::size_t T = x.extent(0), H = x.extent(1);
+  if (h.extent(0) != T || h.extent(1) != H || h_out.extent(0) != T || h_out.extent(1) != H ||
+      x_next.extent(0) != T || x_next.extent(1) != H || router_w.extent(1) != H || router_w.extent(0) != gate.size())
+    throw std::invalid_argument("moe_block: dimension mismatch");
+  if (scalar_tag<Scalar>() < 0) throw std::invalid_argument("moe_block: Scalar must be float or bhalf_t");
+  kdnn_b200_weight_table g = table_of(gate), u = table_of(up), d = table_of(down);
+  g.tma = tma_gate; u.tma = tma_up; d.tma = tma_down;
+  if (expert_count == static_cast<std::size_t>(-1)) expert_count = gate.size() - expert_first;
+  const int rc = kdnn_b200_moe_block(x.data(), x.stride(0), T, scalar_tag<Scalar>(), router_w.data(), router_w.stride(0),
+                                     router_bias.extent(0) ? router_bias.data() : nullptr, top_k, norm_topk ? 1 : 0,
+                                     routed_scale, sigmoid ? 1 : 0, &g, &u, &d, expert_first, expert_count, nullptr, 0,
+                                     h.data(), h.stride(0), h_out.data(), h_out.stride(0), x_next.data(),
+                                     x_next.stride(0), eps, exchange, workspace.data(), workspace.extent(0),
+                                     StreamOf<ExecSpace>::get(space));
+  throw_on_error(rc, "moe_block");
+  return rc == KDNN_OK;
+}
 
 // ---- the reference's own signatures -------------------------------------------------------------------
 // Gguf::quant_gemv / quant_gemm / quant_moe_decode exactly as the reference declares them

@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <cstring>
 #include <random>
+#include <array>
 #include <vector>
 
 #include "KokkosDNN_B200.hpp"
@@ -137,6 +138,37 @@ int main() {
     CHECK(threw);
   }
 
+  // ---- quant_gemv_multi: two projections of one row in one call, each equal to the checker ----
+  {
+    const size_t N = 130, K = 1024;
+    auto r0 = payload(GgmlType::Q4_K, N, K, 51), r1 = payload(GgmlType::Q4_K, N, K, 52);
+    std::vector<float> x(K);
+    for (auto& v : x) v = nd(rng);
+    std::array<QuantWeight, 2> ws = {QuantWeight{V1<uint8_t>(upload(r0), r0.size()), GgmlType::Q4_K, N, K},
+                                     QuantWeight{V1<uint8_t>(upload(r1), r1.size()), GgmlType::Q4_K, N, K}};
+    std::array<V1<float>, 2> ys = {V1<float>(dmalloc<float>(N), N), V1<float>(dmalloc<float>(N), N)};
+    V1<float> xv(upload(x), K);
+    V1<uint8_t> scratch(dmalloc<uint8_t>(B::quant_gemv_int8_scratch_bytes(K)), B::quant_gemv_int8_scratch_bytes(K));
+    CHECK(B::quant_gemv_multi(space, xv, ws, ys, scratch));
+    cudaDeviceSynchronize();
+    std::vector<uint8_t> hs(ko_act_q8_bytes(K) + 64);
+    uint8_t* hsa = hs.data() + ((64 - (reinterpret_cast<uintptr_t>(hs.data()) & 63)) & 63);
+    for (int i = 0; i < 2; ++i) {
+      std::vector<float> ref(N);
+      ko_gemv_int8(12, i ? r1.data() : r0.data(), N, K, x.data(), ref.data(), hsa);
+      auto got = download(ys[i].data(), N);
+      float err = 0;
+      for (size_t j = 0; j < N; ++j) err = std::fmax(err, std::fabs(got[j] - ref[j]));
+      CHECK(err <= 1e-3f * max_abs(ref));
+    }
+    bool threw = false;
+    try {
+      std::array<V1<float>, 2> bad = {ys[0], V1<float>(ys[1].data(), N - 1)};
+      B::quant_gemv_multi(space, xv, ws, bad, scratch);
+    } catch (const std::invalid_argument&) { threw = true; }
+    CHECK(threw);
+  }
+
   // ---- quant_moe_decode: one token, dead slot, argument errors (Test_MoeDecode.cpp:368-455) ----
   {
     const size_t E = 3, H = 512, F = 256, S = 3;
@@ -178,6 +210,56 @@ int main() {
     try { V2<float> small(act.data(), 1, F); B::quant_moe_decode(space, X, tg, tu, td, iv, wv, small, Y, ws); }
     catch (const std::invalid_argument&) { threw = true; }
     CHECK(threw);
+  }
+  // ---- moe_block: router + experts + residual + norm in one call; the experts' part against the checker fed with
+  // the routing the block produced ----
+  {
+    const size_t E = 4, H = 512, F = 256, S = 2, T = 5;
+    std::vector<std::vector<uint8_t>> g(E), u(E), d(E);
+    std::vector<uintptr_t> gp(E), up(E), dp(E);
+    std::vector<const uint8_t*> gh(E), uh(E), dh(E);
+    for (size_t e = 0; e < E; ++e) {
+      g[e] = payload(GgmlType::Q4_K, F, H, 400 + e); u[e] = payload(GgmlType::Q4_K, F, H, 500 + e);
+      d[e] = payload(GgmlType::Q4_K, H, F, 600 + e);
+      gp[e] = (uintptr_t)upload(g[e]); up[e] = (uintptr_t)upload(u[e]); dp[e] = (uintptr_t)upload(d[e]);
+      gh[e] = g[e].data(); uh[e] = u[e].data(); dh[e] = d[e].data();
+    }
+    QuantWeightTable tg{V1<uintptr_t>(upload(gp), E), GgmlType::Q4_K, F, H, H / 256 * 144};
+    QuantWeightTable tu{V1<uintptr_t>(upload(up), E), GgmlType::Q4_K, F, H, H / 256 * 144};
+    QuantWeightTable td{V1<uintptr_t>(upload(dp), E), GgmlType::Q4_K, H, F, F / 256 * 144};
+    std::vector<float> x(T * H), h(T * H), rw(E * H);
+    for (auto& v : x) v = nd(rng);
+    for (auto& v : h) v = nd(rng);
+    for (auto& v : rw) v = nd(rng) / std::sqrt((float)H);
+    V2<float> X(upload(x), T, H), Hin(upload(h), T, H), Hout(dmalloc<float>(T * H), T, H), Xn(dmalloc<float>(T * H), T, H);
+    V2<float> RW(upload(rw), E, H);
+    V1<float> nobias(nullptr, 0);
+    const size_t wsb = kdnn_b200_moe_block_workspace_bytes(T, 1, S, H, F, E, 1);
+    V1<uint8_t> ws(dmalloc<uint8_t>(wsb), wsb);
+    cudaMemset(ws.data(), 0, wsb);
+    CHECK(B::moe_block(space, X, RW, nobias, (int)S, true, 1.0f, false, tg, tu, td, Hin, Hout, Xn, 1e-6f, ws));
+    V2<int> iv(dmalloc<int>(T * S), T, S);
+    V2<float> wv(dmalloc<float>(T * S), T, S);
+    CHECK(kdnn_b200_moe_block_routing(nullptr, ws.data(), T, 1, S, H, F, E, iv.data(), wv.data(), nullptr) == KDNN_OK);
+    cudaDeviceSynchronize();
+    auto idx = download(iv.data(), T * S);
+    auto wts = download(wv.data(), T * S);
+    std::vector<float> yref(T * H);
+    ko_moe_ffn_int8(x.data(), T, H, F, E, 12, 12, 12, gh.data(), uh.data(), dh.data(), idx.data(), wts.data(), S, 0,
+                    yref.data(), nullptr);
+    auto hout = download(Hout.data(), T * H);
+    auto xn = download(Xn.data(), T * H);
+    float err = 0;
+    for (size_t i = 0; i < T * H; ++i) err = std::fmax(err, std::fabs((hout[i] - h[i]) - yref[i]));
+    CHECK(err <= 1e-3f * max_abs(yref) + 1e-5f * max_abs(h));
+    for (size_t t = 0; t < T; ++t) {   // un-scaled RMS norm of the new residual row
+      double ss = 0;
+      for (size_t k = 0; k < H; ++k) ss += (double)hout[t * H + k] * hout[t * H + k];
+      const float inv = (float)(1.0 / std::sqrt(ss / H + 1e-6));
+      float e2 = 0;
+      for (size_t k = 0; k < H; ++k) e2 = std::fmax(e2, std::fabs(xn[t * H + k] - hout[t * H + k] * inv));
+      CHECK(e2 <= 1e-5f * (1.0f + std::fabs(inv) * max_abs(hout)));
+    }
   }
   CHECK(kdnn_b200_device_status() == 0);
   std::printf(failures ? "dropin_test: %d FAILURES\n" : "dropin_test: all checks passed\n", failures);
