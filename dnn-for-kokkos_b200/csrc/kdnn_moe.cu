@@ -1295,6 +1295,7 @@ __global__ void __launch_bounds__(512) moe_combine_norm_kernel(const CombinePara
       for (int s = 0; s < p.S; ++s) nlive += (s_e[s] >= p.e_lo && s_e[s] < p.e_hi && s_w[s] != 0.0f);
       if (nlive > 0) mbar_expect_tx(bar, row_bytes * static_cast<uint32_t>(nlive));
     }
+    __syncthreads();   // the bytes are expected before any warp can have them arrive
     if ((threadIdx.x & 31) == 0 && static_cast<int>(threadIdx.x >> 5) < p.world) {   // one WARP per rank: they do not wait for one another
       const int r = static_cast<int>(threadIdx.x >> 5);
       if (!wait_epoch(p.oflag + r, *p.epoch, p.wait_ns)) atomicExch(p.status, KDNN_ERR_DEVICE_WAIT);
