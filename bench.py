@@ -290,6 +290,8 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        print(f"[bench] rank {rank}/{world} on cuda:{local} ({torch.cuda.get_device_name(local)}), NCCL "
+              f"{'.'.join(str(v) for v in torch.cuda.nccl.version())}, backend {dist.get_backend()}", file=sys.stderr, flush=True)
 
     import __graft_entry__ as ge
     kd = ge.load_package()
