@@ -520,8 +520,9 @@ static cudaError_t moe_prep_launch(const PrepParams& p, int xs, cudaStream_t st)
     qctas = max(1, min(4 * device_sm_count(), (items + 31) / 32));
   }
   auto kern = xs == KDNN_F32 ? moe_prep_kernel<float> : moe_prep_kernel<__nv_bfloat16>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (smem > 48 * 1024) {   // once per device, at the largest size this kernel is ever given (kPrepSmemLimit)
+    static SmemAttrOnce once[2];
+    const cudaError_t e = set_max_smem_once(once[xs == KDNN_F32], kern, 160 * 1024);
     if (e != cudaSuccess) return e;
   }
   return launch_chained(kern, dim3(1 + qctas), dim3(1024), smem, st, p);
@@ -1488,8 +1489,9 @@ cudaError_t moe_block_launch(const BlockArgs& a, cudaStream_t st) {
                     : tpc == 4 ? (f32 ? moe_gate_kernel<float, 4> : moe_gate_kernel<__nv_bfloat16, 4>)
                     : tpc == 2 ? (f32 ? moe_gate_kernel<float, 2> : moe_gate_kernel<__nv_bfloat16, 2>)
                                : (f32 ? moe_gate_kernel<float, 1> : moe_gate_kernel<__nv_bfloat16, 1>);
-  if (gsm > 48 * 1024) {
-    err = cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsm);
+  if (gsm > 48 * 1024) {   // once per device and kernel, at the cap the token count is trimmed to above
+    static SmemAttrOnce once[2][4];
+    err = set_max_smem_once(once[f32][tpc == 8 ? 3 : tpc == 4 ? 2 : tpc == 2 ? 1 : 0], gk, 200 * 1024 + 8 * 1024);
     if (err != cudaSuccess) return err;
   }
   err = launch_chained_cluster(gk, dim3((unsigned)((a.Tl + tpc - 1) / tpc) * kGateCluster), dim3(kGateThreads), gsm,
