@@ -657,10 +657,23 @@ class MoeExchange:
     order (what ``all_gather`` of ``local_handle`` gives); the single-process form (``MoeExchange.local``) maps
     plain device buffers and is what the tests use to stand in for peers that never answer."""
 
-    def __init__(self, rank: int, world: int, regions: Sequence[int], wait_ns: int = 0, owner=None):
+    def __init__(self, rank: int, world: int, regions: Sequence[int], wait_ns: int = 0, owner=None, ipc: bool = False):
         self.rank, self.world, self.regions, self.wait_ns, self._owner = rank, world, list(regions), wait_ns, owner
         self._arr = (C.c_void_p * world)(*self.regions)
         self.c = MoeExchangeC(rank, world, self._arr, wait_ns)
+        self._ipc = ipc          # regions came from alloc() / open(): close() gives them back
+
+    def close(self) -> None:
+        """Closes the peers' mappings and frees this rank's region (only for regions made by alloc() / open()).
+        Call it on every rank after a device synchronisation and a barrier: no peer may still be using them."""
+        if not self._ipc:
+            return
+        self._ipc = False
+        for r, ptr in enumerate(self.regions):
+            if r == self.rank:
+                _check(lib.kdnn_b200_peer_free(ptr), "peer_free")
+            else:
+                _check(lib.kdnn_b200_peer_close(ptr), "peer_close")
 
     @staticmethod
     def region_bytes(tokens_local: int, world: int, top_k: int, H: int) -> int:

@@ -88,7 +88,7 @@ def make_exchange(kd, rank: int, world: int, tokens_local: int, top_k: int, hidd
     dist.all_gather_object(handles, handle)
     regions = [ptr if r == rank else kd.MoeExchange.open(handles[r]) for r in range(world)]
     dist.barrier()
-    return kd.MoeExchange(rank, world, regions, wait_ns)
+    return kd.MoeExchange(rank, world, regions, wait_ns, ipc=True)
 
 
 class MoeStack:
@@ -165,6 +165,19 @@ class MoeStack:
         kd.residual_rmsnorm(h, self.y, x2)
         return h2, x2
 
+    def close(self) -> None:
+        """Gives the exchange regions back. Collective: every rank calls it, after its last forward."""
+        ex = getattr(self, "ex", None)
+        if ex is None:
+            return
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=self.group)     # nobody reads or writes a peer's region after this
+            torch.cuda.synchronize(self.dev)
+        ex.close()
+        self.ex = None
+
     def forward(self, h0: torch.Tensor) -> torch.Tensor:
         """h0: the full [tokens, hidden] block (identical on every rank). Returns the final residual stream of
         this rank's tokens (push) or of all tokens (allreduce)."""
@@ -226,6 +239,8 @@ def bench_moe_stack(kd, dev, rank: int, world: int, steps: int = 5, warmup: int 
     finite = bool(torch.isfinite(out.float()).all().item())
     status = kd.device_status()
     kd.tile_kind(prev_kind)
+    del graph          # its kernels name the exchange regions
+    stack.close()
     layer_bytes = cfg.layer_bytes()
     names = {3: "auto (mma.sync for the MoE tiles)", 2: "tcgen05 + TMEM", 1: "mma.sync", 0: "dp4a"}
     return {
@@ -272,6 +287,7 @@ def check_multi_rank(kd, dev, rank: int, world: int, layers: int = 2, cfg: Optio
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         out[mode] = float(t.item())
+        stack.close()
         del stack
     out["device_status"] = kd.device_status()
     return out
